@@ -1,0 +1,227 @@
+"""ctypes bindings of the CUDA kernels.
+
+Every method takes torch CUDA tensors, launches on torch's current stream and
+raises `KernelError` when the entry point refuses its arguments or the launch
+fails.  There is no CPU path: without a CUDA device, or without the compiled
+library, `get_kernels()` raises.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_int, c_longlong, c_float, c_void_p, c_char_p
+from typing import Optional
+
+import torch
+
+from . import build
+
+F32, BF16 = 0, 1
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    if dt == torch.float32:
+        return F32
+    if dt == torch.bfloat16:
+        return BF16
+    raise KernelError(f"unsupported element type {dt}; the kernels take float32 and bfloat16")
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+class Kernels:
+    """The loaded kernel library.  One instance per process (`get_kernels`)."""
+
+    def __init__(self, verbose: bool = True) -> None:
+        if not torch.cuda.is_available():
+            raise KernelError("no CUDA device: braidinfer_b200 runs on an NVIDIA B200 (sm_100a) only "
+                              "and has no CPU path")
+        major, minor = torch.cuda.get_device_capability()
+        if major != 10:
+            raise KernelError(f"the kernels are built for sm_100a; this device is sm_{major}{minor}")
+        path = build.core_library(verbose=verbose)
+        self.lib = ctypes.CDLL(str(path))
+        self.path = str(path)
+        self.launches = 0          # kernels launched through this object (for measurements)
+        self._declare()
+        self._error_flag = torch.zeros(4, dtype=torch.int32, device="cuda")
+        self._tc_workspace: Optional[torch.Tensor] = None
+
+    # ------------------------------------------------------------------ plumbing
+    def _declare(self) -> None:
+        L = self.lib
+        L.braid_last_error.restype = c_char_p
+        L.braid_embed.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
+        L.braid_rmsnorm.argtypes = [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_void_p]
+        L.braid_silu_mul.argtypes = [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
+        L.braid_residual_add.argtypes = [c_void_p, c_void_p, c_int, c_longlong, c_void_p]
+        L.braid_rope_kv_write.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                          c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                          c_void_p, c_void_p]
+        L.braid_cast.argtypes = [c_void_p, c_int, c_void_p, c_int, c_longlong, c_void_p]
+        L.braid_attn_simple.argtypes = [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                                        c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                        c_float, c_void_p]
+        L.braid_gemm_simt.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                                      c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_void_p]
+        L.braid_gemm_tc.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                    c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_int, c_int,
+                                    c_void_p, c_void_p]
+        L.braid_gemm_tc_workspace_bytes.argtypes = [c_int, c_int, c_int]
+        L.braid_gemm_tc_workspace_bytes.restype = c_longlong
+        L.braid_argmax.argtypes = [c_void_p, c_longlong, c_void_p, c_int, c_int, c_void_p, c_void_p]
+        L.braid_sample.argtypes = [c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_int] + [c_void_p] * 12 + \
+                                  [c_void_p, c_void_p]
+        for name in ("braid_embed", "braid_rmsnorm", "braid_silu_mul", "braid_residual_add",
+                     "braid_rope_kv_write", "braid_cast", "braid_attn_simple", "braid_gemm_simt",
+                     "braid_gemm_tc", "braid_argmax", "braid_sample"):
+            getattr(L, name).restype = c_int
+
+    def _check(self, rc: int, what: str) -> None:
+        if rc != 0:
+            msg = self.lib.braid_last_error().decode(errors="replace")
+            raise KernelError(f"{what}: {msg} (code {rc})")
+
+    @staticmethod
+    def _stream():
+        return torch.cuda.current_stream().cuda_stream
+
+    def check_device_errors(self) -> None:
+        """Read the flags that kernels raise (a cache write outside its pages, a
+        tensor-core kernel whose bounded wait ran out, NaN logits) and raise on any.
+        It synchronises the stream, so the step calls it where it reads results."""
+        flags = self._error_flag.tolist()
+        if any(flags):
+            self._error_flag.zero_()
+            names = ["cache write outside the sequence's pages", "tensor-core GEMM wait ran out",
+                     "NaN among the logits", "attention kernel wait ran out"]
+            raise KernelError("device error: " + "; ".join(n for n, f in zip(names, flags) if f))
+
+    # ------------------------------------------------------------------ row-wise kernels
+    def embed(self, table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> None:
+        n, hidden = out.shape
+        self.launches += 1
+        self._check(self.lib.braid_embed(table.data_ptr(), dtype_code(table.dtype), ids.data_ptr(), out.data_ptr(),
+                                         n, hidden, table.shape[0], self._stream()), "embed")
+
+    def rmsnorm(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, eps: float,
+                row_index: Optional[torch.Tensor] = None) -> None:
+        rows, width = out.shape
+        if x.dtype != torch.float32:
+            raise KernelError("rmsnorm reads the float32 residual stream")
+        self.launches += 1
+        self._check(self.lib.braid_rmsnorm(x.data_ptr(), w.data_ptr(), dtype_code(w.dtype), out.data_ptr(),
+                                           dtype_code(out.dtype), _ptr(row_index), rows, width, float(eps),
+                                           self._stream()), "rmsnorm")
+
+    def silu_mul(self, gu: torch.Tensor, out: torch.Tensor) -> None:
+        rows, inter = out.shape
+        self.launches += 1
+        self._check(self.lib.braid_silu_mul(gu.data_ptr(), out.data_ptr(), dtype_code(out.dtype), rows, inter,
+                                            self._stream()), "silu_mul")
+
+    def residual_add(self, h: torch.Tensor, delta: torch.Tensor) -> None:
+        self.launches += 1
+        self._check(self.lib.braid_residual_add(h.data_ptr(), delta.data_ptr(), dtype_code(delta.dtype),
+                                                h.numel(), self._stream()), "residual_add")
+
+    def cast(self, src: torch.Tensor, dst: torch.Tensor) -> None:
+        self.launches += 1
+        self._check(self.lib.braid_cast(src.data_ptr(), dtype_code(src.dtype), dst.data_ptr(),
+                                        dtype_code(dst.dtype), src.numel(), self._stream()), "cast")
+
+    def rope_kv_write(self, qkv: torch.Tensor, inv_freq: torch.Tensor, positions: torch.Tensor,
+                      token_seq: torch.Tensor, page_table: Optional[torch.Tensor], cache: Optional[torch.Tensor],
+                      nqh: int, nkh: int, hd: int, rope_dim: int, adjacent: bool, page_size: int) -> None:
+        rows = qkv.shape[0]
+        cols = page_table.shape[1] if page_table is not None else 0
+        num_pages = cache.shape[0] if cache is not None else 0
+        self.launches += 1
+        self._check(self.lib.braid_rope_kv_write(
+            qkv.data_ptr(), dtype_code(qkv.dtype), inv_freq.data_ptr(), positions.data_ptr(), token_seq.data_ptr(),
+            _ptr(page_table), _ptr(cache), rows, nqh, nkh, hd, rope_dim, int(adjacent), page_size, cols, num_pages,
+            self._error_flag.data_ptr(), self._stream()), "rope_kv_write")
+
+    def attn_simple(self, q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, page_table: torch.Tensor,
+                    positions: torch.Tensor, token_seq: torch.Tensor, nqh: int, nkh: int, hd: int,
+                    page_size: int, window: Optional[int], scale: float) -> None:
+        """q: [rows, >= nqh*hd] (a view of the qkv rows is fine), out: [rows, nqh*hd]."""
+        rows = out.shape[0]
+        self.launches += 1
+        self._check(self.lib.braid_attn_simple(
+            q.data_ptr(), out.data_ptr(), dtype_code(out.dtype), cache.data_ptr(), page_table.data_ptr(),
+            positions.data_ptr(), token_seq.data_ptr(), q.stride(0), out.stride(0), rows, nqh, nkh, hd,
+            page_size, page_table.shape[1], cache.shape[0], int(window or 0), float(scale), self._stream()),
+            "attn_simple")
+
+    # ------------------------------------------------------------------ matrix products
+    def gemm_simt(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, residual: Optional[torch.Tensor] = None) -> None:
+        n, k = x.shape
+        m = w.shape[0]
+        mode = 1 if residual is not None else 0
+        self.launches += 1
+        self._check(self.lib.braid_gemm_simt(x.data_ptr(), w.data_ptr(), out.data_ptr(), _ptr(residual),
+                                             dtype_code(x.dtype), dtype_code(out.dtype), mode, n, m, k,
+                                             x.stride(0), w.stride(0), out.stride(0), self._stream()), "gemm_simt")
+
+    def tc_workspace(self, nbytes: int) -> torch.Tensor:
+        if self._tc_workspace is None or self._tc_workspace.numel() * 4 < nbytes:
+            self._tc_workspace = torch.empty((nbytes + 3) // 4, dtype=torch.float32, device="cuda")
+        return self._tc_workspace
+
+    def gemm_tc(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, residual: Optional[torch.Tensor] = None,
+                swiglu: bool = False, block_n: int = 0, splits: int = 1) -> None:
+        """bfloat16 x [n, k] times w [m, k]^T on the tensor cores.  With `swiglu`, w holds
+        gate rows then up rows and out is [n, m/2]."""
+        n, k = x.shape
+        w_rows = w.shape[0]
+        m = w_rows // 2 if swiglu else w_rows
+        mode = 2 if swiglu else (1 if residual is not None else 0)
+        ws = None
+        if splits > 1:
+            ws = self.tc_workspace(self.lib.braid_gemm_tc_workspace_bytes(n, w_rows, splits))
+            self.launches += 1
+        self.launches += 1
+        self._check(self.lib.braid_gemm_tc(x.data_ptr(), w.data_ptr(), out.data_ptr(), _ptr(residual), _ptr(ws),
+                                           dtype_code(out.dtype), mode, n, m, k, x.stride(0), w.stride(0),
+                                           out.stride(0), block_n, splits,
+                                           self._error_flag.data_ptr() + 4, self._stream()), "gemm_tc")
+
+    @staticmethod
+    def gemm_tc_eligible(x: torch.Tensor, w: torch.Tensor) -> bool:
+        return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.stride(1) == 1 and w.stride(1) == 1
+                and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
+                and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+    # ------------------------------------------------------------------ token choice
+    def argmax(self, logits: torch.Tensor, out: torch.Tensor) -> None:
+        rows, vocab = logits.shape
+        self.launches += 1
+        self._check(self.lib.braid_argmax(logits.data_ptr(), logits.stride(0), out.data_ptr(), rows, vocab,
+                                          self._error_flag.data_ptr() + 8, self._stream()), "argmax")
+
+    def sample(self, logits: torch.Tensor, work: torch.Tensor, out: torch.Tensor, temperature: torch.Tensor,
+               uniform: torch.Tensor, top_k=None, top_p=None, min_p=None, rep_penalty=None,
+               hist_off=None, hist_tok=None, hist_cnt=None, bias_off=None, bias_tok=None, bias_val=None) -> None:
+        rows, vocab = logits.shape
+        self.launches += 1
+        self._check(self.lib.braid_sample(
+            logits.data_ptr(), work.data_ptr(), logits.stride(0), out.data_ptr(), rows, vocab,
+            temperature.data_ptr(), _ptr(top_k), _ptr(top_p), _ptr(min_p), _ptr(rep_penalty), uniform.data_ptr(),
+            _ptr(hist_off), _ptr(hist_tok), _ptr(hist_cnt), _ptr(bias_off), _ptr(bias_tok), _ptr(bias_val),
+            self._error_flag.data_ptr() + 8, self._stream()), "sample")
+
+
+_KERNELS: Optional[Kernels] = None
+
+
+def get_kernels(verbose: bool = True) -> Kernels:
+    global _KERNELS
+    if _KERNELS is None:
+        _KERNELS = Kernels(verbose=verbose)
+    return _KERNELS

@@ -1,0 +1,230 @@
+// Row-wise kernels: embedding gather, RMSNorm, SiLU*up, residual add, rotary encoding
+// with the write of keys and values into the paged cache.
+//
+// Formulas follow the reference ops they replace (by that project's paths):
+//   embedding      kernels/megakernel_ops.hip:1757-1768
+//   rmsnorm        kernels/megakernel_ops.hip:862-904
+//   silu * up      kernels/megakernel_ops.hip:374-407
+//   residual add   kernels/megakernel_ops.hip:1185-1212
+//   rotation       kernels/megakernel_ops.hip:2019-2030 (adjacent pairs)
+//   cache write    kernels/op_kv_write_paged_batch.hip:38-78
+// The residual stream is float32 in both run modes; sums of squares, rsqrt, angles,
+// sin/cos and the residual sum are float32.
+#include "common.cuh"
+
+// ------------------------------------------------------------------ embedding
+template <typename T>
+__global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids,
+                             float* __restrict__ out, int n_tokens, int hidden, int vocab) {
+    const int t = blockIdx.x;
+    if (t >= n_tokens) return;
+    int id = ids[t];
+    const bool valid = (id >= 0 && id < vocab);
+    const T* row = table + (size_t)(valid ? id : 0) * hidden;
+    float* o = out + (size_t)t * hidden;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = valid ? to_f32(row[i]) : 0.f;
+}
+
+extern "C" int braid_embed(const void* table, int table_dtype, const int* ids, float* out,
+                           int n_tokens, int hidden, int vocab, void* stream) {
+    if (n_tokens <= 0) return BRAID_OK;
+    if (hidden <= 0 || vocab <= 0) BRAID_REFUSE("embed: hidden=%d vocab=%d must be positive", hidden, vocab);
+    cudaStream_t s = (cudaStream_t)stream;
+    const int threads = hidden >= 1024 ? 256 : 128;
+    if (table_dtype == BRAID_F32)
+        embed_kernel<float><<<n_tokens, threads, 0, s>>>((const float*)table, ids, out, n_tokens, hidden, vocab);
+    else if (table_dtype == BRAID_BF16)
+        embed_kernel<__nv_bfloat16><<<n_tokens, threads, 0, s>>>((const __nv_bfloat16*)table, ids, out, n_tokens, hidden, vocab);
+    else
+        BRAID_REFUSE("embed: unknown table dtype code %d", table_dtype);
+    BRAID_LAUNCH_CHECK();
+}
+
+// ------------------------------------------------------------------ rmsnorm
+// One block per output row.  `row_index` (may be null) picks the input row of each
+// output row, which gathers the rows whose logits are wanted before the final norm.
+template <typename TW, typename TO>
+__global__ void rmsnorm_kernel(const float* __restrict__ x, const TW* __restrict__ w, TO* __restrict__ out,
+                               const int* __restrict__ row_index, int rows, int width, float eps) {
+    __shared__ float red[32];
+    const int r = blockIdx.x;
+    if (r >= rows) return;
+    const int src = row_index ? row_index[r] : r;
+    TO* o = out + (size_t)r * width;
+    if (src < 0) {
+        for (int i = threadIdx.x; i < width; i += blockDim.x) o[i] = from_f32<TO>(0.f);
+        return;
+    }
+    const float* xr = x + (size_t)src * width;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float v = xr[i];
+        ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, red);
+    const float scale = rsqrtf(ss / (float)width + eps);
+    for (int i = threadIdx.x; i < width; i += blockDim.x) o[i] = from_f32<TO>(xr[i] * scale * to_f32(w[i]));
+}
+
+extern "C" int braid_rmsnorm(const float* x, const void* w, int w_dtype, void* out, int out_dtype,
+                             const int* row_index, int rows, int width, float eps, void* stream) {
+    if (rows <= 0) return BRAID_OK;
+    if (width <= 0) BRAID_REFUSE("rmsnorm: width=%d must be positive", width);
+    cudaStream_t s = (cudaStream_t)stream;
+    const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
+#define BRAID_RMS(TW, TO) rmsnorm_kernel<TW, TO><<<rows, threads, 0, s>>>(x, (const TW*)w, (TO*)out, row_index, rows, width, eps)
+    if (w_dtype == BRAID_F32 && out_dtype == BRAID_F32) BRAID_RMS(float, float);
+    else if (w_dtype == BRAID_F32 && out_dtype == BRAID_BF16) BRAID_RMS(float, __nv_bfloat16);
+    else if (w_dtype == BRAID_BF16 && out_dtype == BRAID_F32) BRAID_RMS(__nv_bfloat16, float);
+    else if (w_dtype == BRAID_BF16 && out_dtype == BRAID_BF16) BRAID_RMS(__nv_bfloat16, __nv_bfloat16);
+    else BRAID_REFUSE("rmsnorm: unknown dtype codes w=%d out=%d", w_dtype, out_dtype);
+#undef BRAID_RMS
+    BRAID_LAUNCH_CHECK();
+}
+
+// ------------------------------------------------------------------ silu(gate) * up
+// gu is [rows, 2*inter]: gate in columns [0, inter), up in [inter, 2*inter).
+template <typename T>
+__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, long long total, int inter) {
+    long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const long long r = i / inter;
+    const int c = (int)(i - r * inter);
+    const float g = to_f32(gu[r * 2 * inter + c]);
+    const float u = to_f32(gu[r * 2 * inter + inter + c]);
+    out[i] = from_f32<T>(g / (1.f + expf(-g)) * u);
+}
+
+extern "C" int braid_silu_mul(const void* gu, void* out, int dtype, int rows, int inter, void* stream) {
+    if (rows <= 0) return BRAID_OK;
+    if (inter <= 0) BRAID_REFUSE("silu_mul: inter=%d must be positive", inter);
+    const long long total = (long long)rows * inter;
+    const int threads = 256;
+    const long long blocks = (total + threads - 1) / threads;
+    if (blocks > 0x7fffffffLL) BRAID_REFUSE("silu_mul: %lld elements exceed one launch", total);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == BRAID_F32) silu_mul_kernel<float><<<(int)blocks, threads, 0, s>>>((const float*)gu, (float*)out, total, inter);
+    else if (dtype == BRAID_BF16) silu_mul_kernel<__nv_bfloat16><<<(int)blocks, threads, 0, s>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, total, inter);
+    else BRAID_REFUSE("silu_mul: unknown dtype code %d", dtype);
+    BRAID_LAUNCH_CHECK();
+}
+
+// ------------------------------------------------------------------ residual add
+template <typename T>
+__global__ void residual_add_kernel(float* __restrict__ h, const T* __restrict__ delta, long long total) {
+    long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < total) h[i] = h[i] + to_f32(delta[i]);
+}
+
+extern "C" int braid_residual_add(float* h, const void* delta, int delta_dtype, long long total, void* stream) {
+    if (total <= 0) return BRAID_OK;
+    const int threads = 256;
+    const long long blocks = (total + threads - 1) / threads;
+    if (blocks > 0x7fffffffLL) BRAID_REFUSE("residual_add: %lld elements exceed one launch", total);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (delta_dtype == BRAID_F32) residual_add_kernel<float><<<(int)blocks, threads, 0, s>>>(h, (const float*)delta, total);
+    else if (delta_dtype == BRAID_BF16) residual_add_kernel<__nv_bfloat16><<<(int)blocks, threads, 0, s>>>(h, (const __nv_bfloat16*)delta, total);
+    else BRAID_REFUSE("residual_add: unknown dtype code %d", delta_dtype);
+    BRAID_LAUNCH_CHECK();
+}
+
+// ------------------------------------------------------------------ rotary + cache write
+// qkv: [rows, (nqh + 2*nkh) * hd], heads in the order q..., k..., v....
+// Queries are rotated in place.  Keys are rotated and written to the cache (and in
+// place); values are copied to the cache.  A row whose token_seq is negative is
+// padding and is left alone.  Cache of one layer: [page][2][nkh][page_size][hd].
+struct RopeKvArgs {
+    void* qkv;
+    const float* inv_freq;       // [rope_dim / 2]
+    const int* positions;        // [rows]
+    const int* token_seq;        // [rows], index into the step's sequences, or -1
+    const int* page_table;       // [n_seqs, table_cols], page of each logical block
+    void* cache;                 // base of the layer's pool, or null (no write)
+    int rows, nqh, nkh, hd, rope_dim, adjacent;
+    int page_size, table_cols, num_pages;
+    int* error_flag;
+};
+
+template <typename T>
+__global__ void rope_kv_kernel(RopeKvArgs a) {
+    const int row = blockIdx.x;
+    const int seq = a.token_seq[row];
+    if (seq < 0) return;
+    const int head = blockIdx.y;                     // [0, nqh + 2 nkh)
+    const int pos = a.positions[row];
+    const int width = (a.nqh + 2 * a.nkh) * a.hd;
+    T* src = (T*)a.qkv + (size_t)row * width + (size_t)head * a.hd;
+    const bool is_q = head < a.nqh;
+    const bool is_k = !is_q && head < a.nqh + a.nkh;
+    T* dst = nullptr;
+    if (!is_q && a.cache) {
+        const int kvh = is_k ? head - a.nqh : head - a.nqh - a.nkh;
+        const int block = pos / a.page_size, off = pos - block * a.page_size;
+        int page = (block < a.table_cols) ? a.page_table[(size_t)seq * a.table_cols + block] : -1;
+        if (page < 0 || page >= a.num_pages) {
+            if (threadIdx.x == 0) atomicExch(a.error_flag, 1);
+            page = -1;
+        }
+        if (page >= 0)
+            dst = (T*)a.cache + ((((size_t)page * 2 + (is_k ? 0 : 1)) * a.nkh + kvh) * a.page_size + off) * a.hd;
+    }
+    const int half = a.rope_dim / 2;
+    if (is_q || is_k) {
+        for (int p = threadIdx.x; p < half; p += blockDim.x) {
+            const int i0 = a.adjacent ? 2 * p : p;
+            const int i1 = a.adjacent ? 2 * p + 1 : p + half;
+            const float ang = (float)pos * a.inv_freq[p];
+            float sn, cs;
+            sincosf(ang, &sn, &cs);
+            const float x0 = to_f32(src[i0]), x1 = to_f32(src[i1]);
+            const T y0 = from_f32<T>(x0 * cs - x1 * sn);
+            const T y1 = from_f32<T>(x0 * sn + x1 * cs);
+            src[i0] = y0;
+            src[i1] = y1;
+            if (dst) { dst[i0] = y0; dst[i1] = y1; }
+        }
+        if (dst)
+            for (int i = a.rope_dim + threadIdx.x; i < a.hd; i += blockDim.x) dst[i] = src[i];
+    } else if (dst) {
+        for (int i = threadIdx.x; i < a.hd; i += blockDim.x) dst[i] = src[i];
+    }
+}
+
+extern "C" int braid_rope_kv_write(void* qkv, int dtype, const float* inv_freq, const int* positions,
+                                   const int* token_seq, const int* page_table, void* cache,
+                                   int rows, int nqh, int nkh, int hd, int rope_dim, int adjacent,
+                                   int page_size, int table_cols, int num_pages, int* error_flag,
+                                   void* stream) {
+    if (rows <= 0) return BRAID_OK;
+    if (nqh <= 0 || nkh <= 0 || hd <= 0) BRAID_REFUSE("rope_kv_write: heads/head_dim must be positive");
+    if (rope_dim < 0 || rope_dim > hd || (rope_dim & 1)) BRAID_REFUSE("rope_kv_write: rope_dim=%d must be even and <= head_dim=%d", rope_dim, hd);
+    if (nqh + 2 * nkh > 65535) BRAID_REFUSE("rope_kv_write: %d heads exceed the grid limit", nqh + 2 * nkh);
+    RopeKvArgs a{qkv, inv_freq, positions, token_seq, page_table, cache, rows, nqh, nkh, hd, rope_dim, adjacent,
+                 page_size, table_cols, num_pages, error_flag};
+    dim3 grid(rows, nqh + 2 * nkh);
+    const int threads = hd >= 128 ? 64 : 32;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == BRAID_F32) rope_kv_kernel<float><<<grid, threads, 0, s>>>(a);
+    else if (dtype == BRAID_BF16) rope_kv_kernel<__nv_bfloat16><<<grid, threads, 0, s>>>(a);
+    else BRAID_REFUSE("rope_kv_write: unknown dtype code %d", dtype);
+    BRAID_LAUNCH_CHECK();
+}
+
+// ------------------------------------------------------------------ casts
+template <typename TI, typename TO>
+__global__ void cast_kernel(const TI* __restrict__ in, TO* __restrict__ out, long long total) {
+    long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < total) out[i] = from_f32<TO>(to_f32(in[i]));
+}
+
+extern "C" int braid_cast(const void* in, int in_dtype, void* out, int out_dtype, long long total, void* stream) {
+    if (total <= 0) return BRAID_OK;
+    const int threads = 256;
+    const long long blocks = (total + threads - 1) / threads;
+    if (blocks > 0x7fffffffLL) BRAID_REFUSE("cast: %lld elements exceed one launch", total);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (in_dtype == BRAID_F32 && out_dtype == BRAID_BF16) cast_kernel<float, __nv_bfloat16><<<(int)blocks, threads, 0, s>>>((const float*)in, (__nv_bfloat16*)out, total);
+    else if (in_dtype == BRAID_BF16 && out_dtype == BRAID_F32) cast_kernel<__nv_bfloat16, float><<<(int)blocks, threads, 0, s>>>((const __nv_bfloat16*)in, (float*)out, total);
+    else BRAID_REFUSE("cast: unsupported dtype codes %d -> %d", in_dtype, out_dtype);
+    BRAID_LAUNCH_CHECK();
+}

@@ -1,0 +1,398 @@
+// bfloat16 matrix product on the 5th-generation tensor cores (tcgen05) of sm_100a:
+//   out[n, m] = sum_k x[n, k] * w[m, k],   float32 accumulation in tensor memory.
+//
+// The weight matrix is the UMMA "A" operand (128 output features per CTA fill the 128
+// lanes of tensor memory), the tokens are the "B" operand (BLOCK_N of them, 16..256),
+// so the same kernel streams weights for a handful of decoded tokens and tiles a long
+// prompt.  Both operands are K-major in global memory, as model folders store weights
+// ([out, in]) and as activations are laid out ([tokens, in]), so neither is transposed.
+//
+//   warp 0      one lane issues TMA loads (cp.async.bulk.tensor, no multicast) of
+//               [128 x 64] weight and [BLOCK_N x 64] token tiles, 128-byte swizzled,
+//               into a ring of shared-memory stages, signalling `full` mbarriers;
+//   warp 1      allocates tensor memory; one lane issues tcgen05.mma (K = 16 each, four
+//               per stage) and tcgen05.commit, which frees the stage (`empty`) and at
+//               the end signals `acc_full`;
+//   warps 2..5  epilogue: tcgen05.ld of their 32 lanes, then one of
+//                 0  store in bfloat16 or float32,
+//                 1  float32 residual sum: out = res + product,
+//                 2  SwiGLU: w holds gate rows [0, I) and up rows [I, 2I); two
+//                    accumulators share the token tile; out = silu(gate) * up,
+//                 3  float32 partial sums of one slice of k (split-k), reduced by
+//                    braid_gemm_splitk_reduce with one of the epilogues above.
+//
+// Every wait on an mbarrier is bounded; a wait that runs out sets *error_flag, tells the
+// other warps to stop, and the kernel frees its tensor memory and returns.
+//
+// Replaces the reference's per-row GEMV ops (kernels/megakernel_ops.hip:168-276 linear,
+// :1474-1602 feed-forward, :1783-1842 output head), which run on scalar FMA.
+#include "common.cuh"
+#include <cuda.h>
+
+#define TC_BLOCK_M 128
+#define TC_BLOCK_K 64
+#define TC_UMMA_K 16
+#define TC_THREADS 192
+#define TC_SPIN_LIMIT (1u << 24)
+
+// ------------------------------------------------------------------ PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait.  Returns false when it gave up or another warp already had.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+    for (uint32_t i = 0; i < TC_SPIN_LIMIT; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 1023u) == 1023u && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(const CUtensorMap* map, uint64_t* bar, void* dst, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
+    uint32_t r[16];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, swizzled
+// by 128 bytes: groups of 8 rows lie 1024 bytes apart (SBO), version 1, layout 2.
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t saddr) {
+    return (uint64_t)((saddr & 0x3FFFFu) >> 4) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+// Instruction descriptor: float32 accumulator, bfloat16 A and B, both K-major, M x N.
+__host__ __device__ constexpr uint32_t umma_idesc_bf16(int m, int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+struct GemmTcArgs {
+    void* out;                 // mode 0: [n, ldo] bf16/f32; 1: f32; 2: bf16/f32 [n, ldo]; 3: f32 [splits][n_rows][m_out]
+    const float* res;          // mode 1
+    int n_rows, m_out, k_in;   // mode 2: m_out is the number of gate rows (w has 2 * m_out rows)
+    long long ldo;
+    int out_dtype;
+    int kb_per_split;          // 64-wide k blocks handled by one blockIdx.z
+    int* error_flag;
+};
+
+template <int BLOCK_N, int MODE>
+struct TcCfg {
+    static constexpr int kAccs = (MODE == 2) ? 2 : 1;
+    static constexpr int kABytes = TC_BLOCK_M * TC_BLOCK_K * 2 * kAccs;
+    static constexpr int kBBytes = BLOCK_N * TC_BLOCK_K * 2;
+    static constexpr int kStageBytes = kABytes + kBBytes;
+    static constexpr int kBudget = 200 * 1024;
+    static constexpr int kStagesRaw = kBudget / kStageBytes;
+    static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
+    static constexpr int kTmemCols = (BLOCK_N * kAccs) < 32 ? 32 : (BLOCK_N * kAccs);
+    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /* alignment */ + 256 /* barriers */;
+};
+
+template <int BLOCK_N, int MODE>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, GemmTcArgs a) {
+    using Cfg = TcCfg<BLOCK_N, MODE>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* bars = (uint64_t*)(smem + Cfg::kStages * Cfg::kStageBytes);
+    uint64_t* full = bars;
+    uint64_t* empty = bars + Cfg::kStages;
+    uint64_t* acc_full = bars + 2 * Cfg::kStages;
+    uint32_t* tmem_slot = (uint32_t*)(bars + 2 * Cfg::kStages + 1);
+    volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m0 = blockIdx.x * TC_BLOCK_M;
+    const int n0 = blockIdx.y * BLOCK_N;
+    const int total_kb = (a.k_in + TC_BLOCK_K - 1) / TC_BLOCK_K;
+    const int kb_begin = blockIdx.z * a.kb_per_split;
+    const int kb_end = min(total_kb, kb_begin + a.kb_per_split);
+    const int num_kb = max(0, kb_end - kb_begin);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < Cfg::kStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        mbar_init(acc_full, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc(tmem_slot, Cfg::kTmemCols);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            for (int i = 0; i < num_kb; ++i) {
+                const int s = i % Cfg::kStages;
+                const uint32_t ph = (uint32_t)(i / Cfg::kStages) & 1u;
+                if (!mbar_wait(&empty[s], ph ^ 1u, abort_flag)) break;
+                uint8_t* sa = smem + s * Cfg::kStageBytes;
+                uint8_t* sb = sa + Cfg::kABytes;
+                mbar_expect_tx(&full[s], Cfg::kStageBytes);
+                const int kx = (kb_begin + i) * TC_BLOCK_K;
+                tma_load_2d(&map_w, &full[s], sa, kx, m0);
+                if (MODE == 2) tma_load_2d(&map_w, &full[s], sa + TC_BLOCK_M * TC_BLOCK_K * 2, kx, a.m_out + m0);
+                tma_load_2d(&map_x, &full[s], sb, kx, n0);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc_bf16(TC_BLOCK_M, BLOCK_N);
+            bool ok = true;
+            for (int i = 0; i < num_kb && ok; ++i) {
+                const int s = i % Cfg::kStages;
+                const uint32_t ph = (uint32_t)(i / Cfg::kStages) & 1u;
+                ok = mbar_wait(&full[s], ph, abort_flag);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t sa = smem_u32(smem + s * Cfg::kStageBytes);
+                const uint32_t sb = sa + Cfg::kABytes;
+#pragma unroll
+                for (int k = 0; k < TC_BLOCK_K / TC_UMMA_K; ++k) {
+                    const uint32_t koff = k * TC_UMMA_K * 2;     // bytes along the 128-byte row
+                    const uint32_t accum = (i > 0 || k > 0) ? 1u : 0u;
+                    umma_bf16(tmem_base, umma_desc_sw128(sa + koff), umma_desc_sw128(sb + koff), idesc, accum);
+                    if (MODE == 2)
+                        umma_bf16(tmem_base + BLOCK_N, umma_desc_sw128(sa + TC_BLOCK_M * TC_BLOCK_K * 2 + koff),
+                                  umma_desc_sw128(sb + koff), idesc, accum);
+                }
+                umma_commit(&empty[s]);
+            }
+            if (ok) umma_commit(acc_full);
+        }
+    } else {
+        // epilogue warps: warp w may read tensor-memory lanes 32 * (w % 4) ...
+        const int quarter = warp & 3;
+        const int m = m0 + quarter * 32 + lane;
+        bool ok = true;
+        if (num_kb > 0) ok = mbar_wait(acc_full, 0, abort_flag);
+        tc_fence_after();
+        if (ok) {
+            const uint32_t trow = tmem_base + ((uint32_t)(quarter * 32) << 16);
+#pragma unroll 1
+            for (int c0 = 0; c0 < BLOCK_N; c0 += 16) {
+                if (n0 + c0 >= a.n_rows) break;
+                float v[16];
+                if (num_kb > 0) tmem_ld16(trow + c0, v);
+                else {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) v[i] = 0.f;
+                }
+                if (MODE == 2) {
+                    float u[16];
+                    tmem_ld16(trow + BLOCK_N + c0, u);
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) v[i] = v[i] / (1.f + expf(-v[i])) * u[i];
+                }
+                if (m < a.m_out) {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        const int n = n0 + c0 + i;
+                        if (n >= a.n_rows) break;
+                        if (MODE == 3) {
+                            ((float*)a.out)[((size_t)blockIdx.z * a.n_rows + n) * a.m_out + m] = v[i];
+                        } else {
+                            const size_t o = (size_t)n * a.ldo + m;
+                            if (MODE == 1) ((float*)a.out)[o] = a.res[o] + v[i];
+                            else if (a.out_dtype == BRAID_F32) ((float*)a.out)[o] = v[i];
+                            else ((__nv_bfloat16*)a.out)[o] = __float2bfloat16_rn(v[i]);
+                        }
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (threadIdx.x == 0 && *abort_flag) atomicExch(a.error_flag, 1);
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, Cfg::kTmemCols);
+    }
+}
+
+// ------------------------------------------------------------------ split-k reduce
+// partial: [splits][n_rows][m_cols] float32.  mode 0: store; 1: res + sum (float32);
+// 2: columns [0, I) are gate and [I, 2I) are up, out[n, I] = silu(gate) * up.
+template <int MODE>
+__global__ void splitk_reduce_kernel(const float* __restrict__ partial, void* __restrict__ out,
+                                     const float* __restrict__ res, int splits, int n_rows, int m_cols,
+                                     int m_out, long long ldo, int out_dtype) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long long)n_rows * m_out) return;
+    const int n = (int)(i / m_out), m = (int)(i - (long long)n * m_out);
+    const size_t plane = (size_t)n_rows * m_cols;
+    float s = 0.f;
+    for (int k = 0; k < splits; ++k) s += partial[k * plane + (size_t)n * m_cols + m];
+    if (MODE == 2) {
+        float u = 0.f;
+        for (int k = 0; k < splits; ++k) u += partial[k * plane + (size_t)n * m_cols + m_out + m];
+        s = s / (1.f + expf(-s)) * u;
+    }
+    const size_t o = (size_t)n * ldo + m;
+    if (MODE == 1) ((float*)out)[o] = res[o] + s;
+    else if (out_dtype == BRAID_F32) ((float*)out)[o] = s;
+    else ((__nv_bfloat16*)out)[o] = __float2bfloat16_rn(s);
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    }
+    return fn;
+}
+
+// rows x k bfloat16 matrix with row stride ld (elements); box = box_rows x 64, 128-byte swizzle.
+static int make_map(CUtensorMap* map, const void* base, long long rows, long long k, long long ld, int box_rows) {
+    EncodeTiledFn fn = get_encode_fn();
+    if (!fn) BRAID_REFUSE("gemm_tc: the driver does not export cuTensorMapEncodeTiled");
+    cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {TC_BLOCK_K, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) BRAID_REFUSE("gemm_tc: cuTensorMapEncodeTiled failed with %d (rows=%lld k=%lld ld=%lld)", (int)r, rows, k, ld);
+    return BRAID_OK;
+}
+
+template <int BLOCK_N, int MODE>
+static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const GemmTcArgs& a, dim3 grid, cudaStream_t s) {
+    using Cfg = TcCfg<BLOCK_N, MODE>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BLOCK_N, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+        if (e != cudaSuccess) { braid_set_error("gemm_tc: cannot reserve %d bytes of shared memory: %s", Cfg::kSmemBytes, cudaGetErrorString(e)); return (int)e; }
+        configured = true;
+    }
+    gemm_tc_kernel<BLOCK_N, MODE><<<grid, TC_THREADS, Cfg::kSmemBytes, s>>>(mw, mx, a);
+    BRAID_LAUNCH_CHECK();
+}
+
+template <int MODE>
+static int dispatch_tc(int block_n, const CUtensorMap& mw, const CUtensorMap& mx, const GemmTcArgs& a, dim3 grid, cudaStream_t s) {
+    switch (block_n) {
+        case 16: return launch_tc<16, MODE>(mw, mx, a, grid, s);
+        case 32: return launch_tc<32, MODE>(mw, mx, a, grid, s);
+        case 64: return launch_tc<64, MODE>(mw, mx, a, grid, s);
+        case 128: return launch_tc<128, MODE>(mw, mx, a, grid, s);
+        case 256: return launch_tc<256, MODE>(mw, mx, a, grid, s);
+    }
+    BRAID_REFUSE("gemm_tc: token tile %d is not one of 16, 32, 64, 128, 256", block_n);
+}
+
+// Bytes of float32 scratch that `splits` > 1 needs.
+extern "C" long long braid_gemm_tc_workspace_bytes(int n_rows, int w_rows, int splits) {
+    return splits > 1 ? (long long)splits * n_rows * w_rows * 4 : 0;
+}
+
+// x: [n_rows, k_in] bf16 (row stride ldx); w: [w_rows, k_in] bf16 (row stride ldw), where
+// w_rows = m_out, or 2 * m_out for the SwiGLU epilogue.  splits > 1 slices k and needs
+// `workspace`.  block_n = 0 picks the token tile.
+extern "C" int braid_gemm_tc(const void* x, const void* w, void* out, const float* res, void* workspace,
+                             int out_dtype, int mode, int n_rows, int m_out, int k_in,
+                             long long ldx, long long ldw, long long ldo, int block_n, int splits,
+                             int* error_flag, void* stream) {
+    if (n_rows <= 0 || m_out <= 0) return BRAID_OK;
+    if (mode < 0 || mode > 2) BRAID_REFUSE("gemm_tc: unknown epilogue %d", mode);
+    if (k_in <= 0) BRAID_REFUSE("gemm_tc: k=%d must be positive", k_in);
+    if ((ldx % 8) || (ldw % 8)) BRAID_REFUSE("gemm_tc: row strides (%lld, %lld) must be multiples of 8 elements for TMA", ldx, ldw);
+    if (((uintptr_t)x & 15) || ((uintptr_t)w & 15)) BRAID_REFUSE("gemm_tc: operands must be 16-byte aligned for TMA");
+    if (mode == 1 && (!res || out_dtype != BRAID_F32)) BRAID_REFUSE("gemm_tc: the residual epilogue writes float32 and needs res");
+    if (out_dtype != BRAID_F32 && out_dtype != BRAID_BF16) BRAID_REFUSE("gemm_tc: unknown out dtype code %d", out_dtype);
+    if (!error_flag) BRAID_REFUSE("gemm_tc: error_flag is required");
+    const int w_rows = (mode == 2) ? 2 * m_out : m_out;
+    if (block_n == 0) block_n = n_rows <= 16 ? 16 : n_rows <= 32 ? 32 : n_rows <= 64 ? 64 : n_rows <= 128 ? 128 : 256;
+    const int total_kb = (k_in + TC_BLOCK_K - 1) / TC_BLOCK_K;
+    if (splits < 1) splits = 1;
+    if (splits > total_kb) splits = total_kb;
+    if (splits > 1 && !workspace) BRAID_REFUSE("gemm_tc: split-k needs a workspace");
+    const int kb_per_split = (total_kb + splits - 1) / splits;
+    splits = (total_kb + kb_per_split - 1) / kb_per_split;
+    cudaStream_t s = (cudaStream_t)stream;
+
+    CUtensorMap mw, mx;
+    int rc = make_map(&mw, w, w_rows, k_in, ldw, TC_BLOCK_M);
+    if (rc) return rc;
+    rc = make_map(&mx, x, n_rows, k_in, ldx, block_n);
+    if (rc) return rc;
+    const unsigned n_tiles = (n_rows + block_n - 1) / block_n;
+    if (n_tiles > 65535) BRAID_REFUSE("gemm_tc: %d rows exceed the grid limit", n_rows);
+
+    if (splits == 1) {
+        GemmTcArgs a{out, res, n_rows, m_out, k_in, ldo, out_dtype, kb_per_split, error_flag};
+        dim3 grid((m_out + TC_BLOCK_M - 1) / TC_BLOCK_M, n_tiles, 1);
+        if (mode == 0) return dispatch_tc<0>(block_n, mw, mx, a, grid, s);
+        if (mode == 1) return dispatch_tc<1>(block_n, mw, mx, a, grid, s);
+        return dispatch_tc<2>(block_n, mw, mx, a, grid, s);
+    }
+    GemmTcArgs a{workspace, nullptr, n_rows, w_rows, k_in, 0, BRAID_F32, kb_per_split, error_flag};
+    dim3 grid((w_rows + TC_BLOCK_M - 1) / TC_BLOCK_M, n_tiles, splits);
+    rc = dispatch_tc<3>(block_n, mw, mx, a, grid, s);
+    if (rc) return rc;
+    const long long total = (long long)n_rows * m_out;
+    const int threads = 256;
+    const long long blocks = (total + threads - 1) / threads;
+    if (blocks > 0x7fffffffLL) BRAID_REFUSE("gemm_tc: %lld outputs exceed one reduce launch", total);
+    const float* p = (const float*)workspace;
+    if (mode == 0) splitk_reduce_kernel<0><<<(int)blocks, threads, 0, s>>>(p, out, res, splits, n_rows, w_rows, m_out, ldo, out_dtype);
+    else if (mode == 1) splitk_reduce_kernel<1><<<(int)blocks, threads, 0, s>>>(p, out, res, splits, n_rows, w_rows, m_out, ldo, out_dtype);
+    else splitk_reduce_kernel<2><<<(int)blocks, threads, 0, s>>>(p, out, res, splits, n_rows, w_rows, m_out, ldo, out_dtype);
+    BRAID_LAUNCH_CHECK();
+}

@@ -1,0 +1,153 @@
+"""The engine: a loaded model, its cache and the step function.
+
+`Engine.open()` takes a slot for a sequence, `Engine.step()` runs the tokens that
+sequences bring and returns logits at the wanted places, `Engine.close()` gives the
+slot and its pages back.  Generation, the command line and trace replay all drive
+this one object.
+"""
+from __future__ import annotations
+
+import os
+from typing import Dict, List, Mapping, Optional, Sequence, Tuple, Union
+
+import torch
+
+from ..cache import CacheError, CacheManager, PAGE_SIZE
+from ..config import read_config_json
+from ..models import DecoderModel, architecture_for
+from ..parts.runtime import Runtime
+from ..weights import draw_tensors, load_tensors, tensor_specs_of
+from .step import StepContext, StepPacker
+
+_DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32,
+           "f32": torch.float32}
+
+
+def parse_dtype(name: Union[str, torch.dtype]) -> torch.dtype:
+    if isinstance(name, torch.dtype):
+        if name not in (torch.bfloat16, torch.float32):
+            raise ValueError(f"the engine runs in bfloat16 or float32, not {name}")
+        return name
+    if name not in _DTYPES:
+        raise ValueError(f"unknown dtype {name!r}; choose bfloat16 or float32")
+    return _DTYPES[name]
+
+
+class Engine:
+    def __init__(self, config_dict: Mapping, tensors_or_folder, *, dtype="bfloat16", max_tokens: int = 8192,
+                 max_slots: Optional[int] = None, device: str = "cuda:0", gemm_backend: str = "auto",
+                 attention_backend: str = "auto", row_multiple: int = 1, verbose: bool = True) -> None:
+        from ..csrc.api import get_kernels
+        self.dtype = parse_dtype(dtype)
+        self.device = torch.device(device)
+        torch.cuda.set_device(self.device)
+        self.kernels = get_kernels(verbose=verbose)
+        self.arch = architecture_for(config_dict)
+        self.config = self.arch.config_from_dict(config_dict)
+        self.spec = self.arch.build_spec(self.config)
+        self.rt = Runtime(act_dtype=self.dtype, device=self.device, kernels=self.kernels,
+                          gemm_backend=gemm_backend, attention_backend=attention_backend)
+        self.model = DecoderModel(self.spec, self.rt)
+        specs = self.model.tensor_specs()
+        if isinstance(tensors_or_folder, (str, os.PathLike)):
+            tensors = load_tensors(str(tensors_or_folder), specs, self.dtype, self.device)
+        else:
+            tensors = tensors_or_folder
+        self.weight_bytes = sum(t.numel() * t.element_size() for t in tensors.values())
+        self.model.load(tensors)
+        del tensors
+        self.max_tokens = int(max_tokens)
+        n_pages = -(-self.max_tokens // PAGE_SIZE)
+        self.max_slots = int(max_slots) if max_slots else max(1, min(n_pages, 1024))
+        self.cache = CacheManager(self.model.cache_plan(), self.max_tokens, self.max_slots, self.dtype, self.device)
+        self.packer = StepPacker(self.device, row_multiple=row_multiple)
+        self.vocab_size = self.spec.vocab_size
+        self.steps_run = 0
+
+    # ------------------------------------------------------------------ construction
+    @classmethod
+    def from_folder(cls, folder: str, **kw) -> "Engine":
+        """A model folder: config.json picks the architecture, safetensors hold the weights."""
+        return cls(read_config_json(folder), folder, **kw)
+
+    @classmethod
+    def from_random(cls, config_dict: Mapping, seed: int = 0, *, dtype="bfloat16", device: str = "cuda:0",
+                    on_device: bool = False, **kw) -> "Engine":
+        """Random weights without a folder.  By default the tensors are the ones
+        `write_random_model` would store (CPU draw, same seed, same values); with
+        `on_device` they are drawn on the GPU instead, which large sizes need for speed
+        (other values, same distributions)."""
+        run_dtype = parse_dtype(dtype)
+        arch = architecture_for(config_dict)
+        spec = arch.build_spec(arch.config_from_dict(config_dict))
+        specs = tensor_specs_of(spec)
+        dev = torch.device(device)
+        if on_device:
+            torch.cuda.set_device(dev)
+            g = torch.Generator(device=dev)
+            g.manual_seed(int(seed))
+            tensors = {}
+            for name, ts in specs.items():
+                x = torch.empty(ts.shape, dtype=torch.bfloat16, device=dev)
+                x.normal_(0.0, ts.std, generator=g)
+                if ts.init == "one_plus_normal":
+                    x += 1.0
+                tensors[name] = x if run_dtype == torch.bfloat16 else x.float()
+        else:
+            drawn = draw_tensors(specs, seed, torch.bfloat16)
+            tensors = {n: (t.to(dev) if run_dtype == torch.bfloat16 else t.to(dev).float()) for n, t in drawn.items()}
+        return cls(config_dict, tensors, dtype=dtype, device=device, **kw)
+
+    # ------------------------------------------------------------------ sequences
+    def open(self) -> int:
+        """Take a slot for a new sequence (its cache is empty, its state zero)."""
+        return self.cache.alloc_slot()
+
+    def close(self, slot: int) -> None:
+        """Give a sequence's slot and pages back."""
+        self.cache.free_slot(slot)
+
+    def length(self, slot: int) -> int:
+        return self.cache.length(slot)
+
+    # ------------------------------------------------------------------ the step
+    def step(self, entries: Sequence[Tuple[int, Sequence[int]]],
+             want: Union[str, Sequence[Sequence[int]], None] = "last") -> Optional[torch.Tensor]:
+        """Run `entries` = [(slot, tokens), ...] as one batch.
+
+        `want` says whose logits come back: "last" (each sequence's last token), "all",
+        None, or for each sequence a list of places among the tokens it brings.
+        Returns float32 logits [wanted, vocab] on the device, in the order of the
+        entries and of their wanted places (None if nothing is wanted)."""
+        if not entries:
+            return None
+        slots = [int(s) for s, _ in entries]
+        tokens = [list(t) for _, t in entries]
+        for s, t in zip(slots, tokens):
+            if len(t) == 0:
+                raise ValueError(f"sequence in slot {s} brings no token")
+            lo, hi = min(t), max(t)
+            if lo < 0 or hi >= self.vocab_size:
+                raise ValueError(f"token id {lo if lo < 0 else hi} is outside the vocabulary of {self.vocab_size}")
+        if want == "last":
+            want_l = [[len(t) - 1] for t in tokens]
+        elif want == "all":
+            want_l = [list(range(len(t))) for t in tokens]
+        elif want is None:
+            want_l = [[] for _ in tokens]
+        else:
+            want_l = [list(w) for w in want]
+            if len(want_l) != len(tokens):
+                raise ValueError("want must have one list per entry")
+        before = [self.cache.length(s) for s in slots]
+        n_new = [len(t) for t in tokens]
+        tables = self.cache.begin_step(slots, n_new)
+        ctx = self.packer.pack(slots, tokens, before, want_l, tables)
+        logits = self.model.forward(ctx, self.cache)
+        self.cache.end_step(slots, n_new)
+        self.steps_run += 1
+        return logits
+
+    def check(self) -> None:
+        """Raise if a kernel flagged an error since the last check (synchronises)."""
+        self.kernels.check_device_errors()

@@ -1,0 +1,124 @@
+"""The step function: run the tokens that a batch of sequences brings, from the
+cache, and return logits at the wanted places.
+
+A step packs its sequences one after another into rows ([sum of lengths, width]);
+each row knows its sequence and its position (cache length + offset).  Prompts of
+unequal lengths go in one step, later steps bring one token each; a prompt may also
+be cut into chunks, because attention always reads keys and values from the cache,
+where the step's own tokens were just written.  Rows added as padding belong to no
+sequence: they write nothing to the cache and nobody reads them.
+
+The reference has one sequence per model and two entry points, prefill(tokens) and
+decode_step(token, position), both returning the last token's logits
+(crates/braidinfer-runtime/src/model/state.rs:39-50, model/mod.rs:279-286).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+
+@dataclass
+class StepContext:
+    """Device-side description of one step, read by the kernels."""
+    rows: int                         # rows including padding
+    n_tokens: int
+    n_seqs: int
+    token_ids: torch.Tensor           # [rows] int32
+    positions: torch.Tensor           # [rows] int32
+    token_seq: torch.Tensor           # [rows] int32, sequence index in this step or -1 (padding)
+    q_start: torch.Tensor             # [n_seqs] first row of each sequence
+    q_len: torch.Tensor               # [n_seqs] rows of each sequence
+    kv_before: torch.Tensor           # [n_seqs] cache length before the step
+    slot_ids: torch.Tensor            # [n_seqs] slot of each sequence (state area index)
+    page_tables: List[torch.Tensor]   # per cache group [n_seqs, blocks] int32
+    want_rows: Optional[torch.Tensor]  # [n_want] rows whose logits are wanted
+    n_want: int
+    max_q_len: int
+    max_kv_len: int
+    all_decode: bool                  # every sequence brings exactly one token
+    # host copies, for parts written in Python (tests' toy parts) and for launch shaping
+    host_q_len: Tuple[int, ...] = ()
+    host_kv_before: Tuple[int, ...] = ()
+    host_slots: Tuple[int, ...] = ()
+
+
+class StepPacker:
+    """Builds a step's integer tables on the host and moves them to the device in one copy."""
+
+    def __init__(self, device, row_multiple: int = 1) -> None:
+        self.device = device
+        self.row_multiple = max(1, int(row_multiple))
+        self._pinned: Optional[torch.Tensor] = None
+        self._dev: Optional[torch.Tensor] = None
+        self._copied: Optional[torch.cuda.Event] = None
+        self.h2d_bytes_last = 0
+
+    def _buffers(self, n: int) -> Tuple[torch.Tensor, torch.Tensor]:
+        if self._pinned is None or self._pinned.numel() < n:
+            cap = max(4096, 1 << (n - 1).bit_length())
+            if self._copied is not None:
+                self._copied.synchronize()
+            self._pinned = torch.empty(cap, dtype=torch.int32, pin_memory=True)
+            self._dev = torch.empty(cap, dtype=torch.int32, device=self.device)
+        return self._pinned, self._dev
+
+    def pack(self, slots: Sequence[int], tokens: Sequence[Sequence[int]], kv_before: Sequence[int],
+             want: Sequence[Sequence[int]], tables: Sequence[np.ndarray]) -> StepContext:
+        n_seqs = len(slots)
+        q_len = [len(t) for t in tokens]
+        n_tokens = sum(q_len)
+        rows = -(-n_tokens // self.row_multiple) * self.row_multiple
+        token_ids = np.zeros(rows, dtype=np.int32)
+        positions = np.zeros(rows, dtype=np.int32)
+        token_seq = np.full(rows, -1, dtype=np.int32)
+        q_start = np.zeros(n_seqs, dtype=np.int32)
+        want_rows: List[int] = []
+        r = 0
+        for i, (t, before) in enumerate(zip(tokens, kv_before)):
+            n = len(t)
+            q_start[i] = r
+            token_ids[r:r + n] = t
+            positions[r:r + n] = np.arange(before, before + n, dtype=np.int32)
+            token_seq[r:r + n] = i
+            for w in want[i]:
+                if not (0 <= w < n):
+                    raise IndexError(f"wanted place {w} is outside the {n} tokens that sequence {i} brings")
+                want_rows.append(r + w)
+            r += n
+        parts = [token_ids, positions, token_seq, q_start, np.asarray(q_len, dtype=np.int32),
+                 np.asarray(kv_before, dtype=np.int32), np.asarray(slots, dtype=np.int32),
+                 np.asarray(want_rows, dtype=np.int32)] + [t.reshape(-1) for t in tables]
+        # every table starts on a 16-byte boundary
+        offs, total = [], 0
+        for p in parts:
+            offs.append(total)
+            total += -(-p.size // 4) * 4
+        pinned, dev = self._buffers(max(total, 4))
+        if self._copied is not None:
+            self._copied.synchronize()          # the last copy out of the pinned buffer is done
+        pn = pinned.numpy()
+        for p, o in zip(parts, offs):
+            pn[o:o + p.size] = p
+        dev[:total].copy_(pinned[:total], non_blocking=True)
+        self._copied = torch.cuda.Event()
+        self._copied.record()
+        self.h2d_bytes_last = total * 4
+
+        def view(k: int, shape=None) -> torch.Tensor:
+            v = dev[offs[k]:offs[k] + parts[k].size]
+            return v if shape is None else v.view(shape)
+
+        return StepContext(
+            rows=rows, n_tokens=n_tokens, n_seqs=n_seqs,
+            token_ids=view(0), positions=view(1), token_seq=view(2), q_start=view(3), q_len=view(4),
+            kv_before=view(5), slot_ids=view(6),
+            page_tables=[view(8 + g, tables[g].shape) for g in range(len(tables))],
+            want_rows=view(7) if want_rows else None, n_want=len(want_rows),
+            max_q_len=max(q_len) if q_len else 0,
+            max_kv_len=max((b + n for b, n in zip(kv_before, q_len)), default=0),
+            all_decode=all(n == 1 for n in q_len),
+            host_q_len=tuple(q_len), host_kv_before=tuple(kv_before), host_slots=tuple(slots))

@@ -1,0 +1,126 @@
+"""Interfaces of the parts a layer is made of, and the registries that map a
+part's name to its class.
+
+A part gets its sizes and constants as parameters, the prefix of its tensor
+names, and the runtime (dtype, device, kernels).  It never learns which model
+it belongs to.  A new part is a subclass registered under a new name; the
+model description (`PartSpec.kind`) then picks it layer by layer.
+"""
+from __future__ import annotations
+
+from typing import Callable, Dict, Optional, Type
+
+import torch
+
+from .spec import CacheRequest, PartSpec, TensorSpec
+
+
+class Part:
+    """Common base: tensors in, nothing else assumed."""
+
+    def __init__(self, params: dict, prefix: str, runtime) -> None:
+        self.params = dict(params)
+        self.prefix = prefix
+        self.rt = runtime
+
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        """Full tensor names (prefix included) that the part needs, with shapes."""
+        return {}
+
+    def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        """Take the device tensors named by `tensor_specs` (already in run dtype)."""
+
+
+class Norm(Part):
+    def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
+        """x: residual stream [rows, width] float32 -> normalised rows in the run dtype."""
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    """Holds the constants of a position encoding; mixers ask it to encode
+    queries and keys in place given each token's position."""
+
+    def encode(self, q, k, positions, ctx) -> None:
+        raise NotImplementedError
+
+
+class Mixer(Part):
+    """Mixes information across the tokens of a sequence (attention, or a
+    recurrence with state)."""
+
+    def cache_request(self) -> Optional[CacheRequest]:
+        """Keys/values the mixer wants kept, or None."""
+        return None
+
+    def state_bytes(self) -> int:
+        """Bytes of fixed-size state per sequence (zeroed when a slot is taken)."""
+        return 0
+
+    def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx, cache, state) -> torch.Tensor:
+        """x: normed tokens [rows, width] (run dtype); residual: [rows, width] float32.
+
+        Returns residual + mix(x) as float32 (it may write into `residual`).
+        `cache` is this run's `LayerCache` view or None; `state` is a uint8
+        tensor [slots, state_bytes] for this layer or None.  Rows are the
+        step's tokens packed sequence after sequence, padded rows last.
+        """
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx) -> torch.Tensor:
+        """Returns residual + f(x), float32, rows independent of one another."""
+        raise NotImplementedError
+
+
+class Block:
+    """The arrangement of a layer's parts."""
+
+    def __init__(self, mixer: Mixer, mixer_norm: Norm, feed_forward: Optional[FeedForward],
+                 feed_forward_norm: Optional[Norm]) -> None:
+        self.mixer = mixer
+        self.mixer_norm = mixer_norm
+        self.feed_forward = feed_forward
+        self.feed_forward_norm = feed_forward_norm
+
+    def parts(self):
+        return [p for p in (self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward)
+                if p is not None]
+
+    def forward(self, h: torch.Tensor, ctx, cache, state) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class Registry:
+    """Name -> class, with a clear error that lists what is known."""
+
+    def __init__(self, what: str) -> None:
+        self.what = what
+        self._items: Dict[str, type] = {}
+
+    def register(self, name: str, cls: Optional[type] = None):
+        def put(c):
+            self._items[name] = c
+            return c
+        return put(cls) if cls is not None else put
+
+    def unregister(self, name: str) -> None:
+        self._items.pop(name, None)
+
+    def get(self, name: str) -> type:
+        if name not in self._items:
+            raise KeyError(f"unknown {self.what} '{name}'; known: {sorted(self._items)}")
+        return self._items[name]
+
+    def names(self):
+        return sorted(self._items)
+
+
+MIXERS = Registry("mixer")
+FEED_FORWARDS = Registry("feed-forward")
+NORMS = Registry("norm")
+POSITION_ENCODINGS = Registry("position encoding")
+BLOCKS = Registry("block")
+EMBEDDINGS = Registry("embedding")
+HEADS = Registry("head")

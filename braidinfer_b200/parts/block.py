@@ -1,0 +1,21 @@
+"""Arrangements of a layer's parts.
+
+"prenorm_residual": h = h + mixer(norm(h)); h = h + feed_forward(norm(h)), the
+order of the reference's attention-plus-dense layer
+(crates/braidinfer-runtime/src/megakernel/megakernel_compile.rs:115-236).  The
+residual stream h is float32; mixers and feed-forwards add into it.
+"""
+from __future__ import annotations
+
+from .base import BLOCKS, Block
+
+
+@BLOCKS.register("prenorm_residual")
+class PreNormResidualBlock(Block):
+    def forward(self, h, ctx, cache, state):
+        x = self.mixer_norm.forward(h, ctx)
+        h = self.mixer.forward(x, h, ctx, cache, state)
+        if self.feed_forward is not None:
+            x = self.feed_forward_norm.forward(h, ctx)
+            h = self.feed_forward.forward(x, h, ctx)
+        return h

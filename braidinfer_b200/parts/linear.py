@@ -1,0 +1,100 @@
+"""A linear map y = W x without bias, W stored [out, in] as model folders hold it
+(reference: kernels/megakernel_ops.hip:168-216).  Several named tensors can be
+stacked along `out` at load time (q, k and v; gate and up) so that one product
+serves them all; stacking rows changes no output value.
+
+Not a registered part: mixers, feed-forwards and heads are built from it.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Sequence
+
+import torch
+
+from .spec import TensorSpec
+
+# Launch shaping for few tokens: aim for about this many CTAs so that weight
+# streaming fills the machine, but keep at least this many 64-wide k blocks a slice.
+_TARGET_CTAS = 148 * 2
+_MIN_KB_PER_SPLIT = 4
+
+
+class Linear:
+    def __init__(self, rt, names: Sequence[str], out_features: Sequence[int], in_features: int) -> None:
+        self.rt = rt
+        self.names = list(names)
+        self.out_features = list(out_features)
+        self.in_features = in_features
+        self.weight: Optional[torch.Tensor] = None
+
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        return {n: TensorSpec((o, self.in_features)) for n, o in zip(self.names, self.out_features)}
+
+    def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        parts = [tensors[n] for n in self.names]
+        if len({p.dtype for p in parts}) > 1:
+            parts = [p.float() for p in parts]
+        self.weight = parts[0] if len(parts) == 1 else torch.cat(parts, dim=0).contiguous()
+
+    def share(self, weight: torch.Tensor) -> None:
+        """Use a tensor that another part owns (a tied output head)."""
+        self.weight = weight
+
+    @property
+    def total_out(self) -> int:
+        return sum(self.out_features)
+
+    def _splits(self, rows: int, w_rows: int, k: int, swiglu: bool) -> int:
+        if rows > 64:
+            return 1
+        tiles = (w_rows // (2 if swiglu else 1) + 127) // 128
+        total_kb = (k + 63) // 64
+        want = max(1, _TARGET_CTAS // max(1, tiles))
+        return max(1, min(want, total_kb // _MIN_KB_PER_SPLIT))
+
+    def forward(self, x: torch.Tensor, *, out_dtype: Optional[torch.dtype] = None,
+                residual: Optional[torch.Tensor] = None, swiglu: bool = False) -> torch.Tensor:
+        """x [rows, in].  Plain: returns [rows, out] in `out_dtype` (default x's type).
+        `residual` (float32 [rows, out]): returns residual + product, written in place.
+        `swiglu`: the weight holds gate rows then up rows; returns silu(gate) * up."""
+        K = self.rt.kernels
+        w = self.weight
+        rows = x.shape[0]
+        w_rows = w.shape[0]
+        if w.dtype == torch.float32 and x.dtype != torch.float32:
+            # a weight stored in 32-bit stays so: this product runs in float32
+            x32 = torch.empty(x.shape, dtype=torch.float32, device=x.device)
+            K.cast(x, x32)
+            y = self.forward(x32, out_dtype=torch.float32 if residual is None else None,
+                             residual=residual, swiglu=swiglu)
+            if residual is not None:
+                return y
+            want = out_dtype or x.dtype
+            if want == torch.float32:
+                return y
+            y2 = torch.empty(y.shape, dtype=want, device=y.device)
+            K.cast(y, y2)
+            return y2
+        use_tc = (self.rt.gemm_backend == "auto" and x.dtype == torch.bfloat16 and K.gemm_tc_eligible(x, w))
+        if residual is not None:
+            if use_tc:
+                K.gemm_tc(x, w, residual, residual=residual, splits=self._splits(rows, w_rows, x.shape[1], False))
+            else:
+                K.gemm_simt(x, w, residual, residual=residual)
+            return residual
+        if swiglu:
+            inter = w_rows // 2
+            out = torch.empty((rows, inter), dtype=out_dtype or x.dtype, device=x.device)
+            if use_tc:
+                K.gemm_tc(x, w, out, swiglu=True, splits=self._splits(rows, w_rows, x.shape[1], True))
+            else:
+                gu = torch.empty((rows, w_rows), dtype=x.dtype, device=x.device)
+                K.gemm_simt(x, w, gu)
+                K.silu_mul(gu, out)
+            return out
+        out = torch.empty((rows, w_rows), dtype=out_dtype or x.dtype, device=x.device)
+        if use_tc:
+            K.gemm_tc(x, w, out, splits=self._splits(rows, w_rows, x.shape[1], False))
+        else:
+            K.gemm_simt(x, w, out)
+        return out

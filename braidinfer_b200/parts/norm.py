@@ -1,0 +1,37 @@
+"""RMSNorm: y = x * rsqrt(mean(x^2) + eps) * w, plain w
+(reference: kernels/megakernel_ops.hip:862-904; `1 + w` is another model family's rule,
+crates/braidinfer-runtime/src/config.rs:552).  Reads the float32 residual stream, writes
+the run's element type; the sum of squares and the scale are float32."""
+from __future__ import annotations
+
+from typing import Dict, Optional
+
+import torch
+
+from .base import NORMS, Norm
+from .spec import TensorSpec
+
+
+@NORMS.register("rmsnorm")
+class RMSNorm(Norm):
+    """params: width, eps, name (tensor name under the prefix)."""
+
+    def __init__(self, params, prefix, runtime) -> None:
+        super().__init__(params, prefix, runtime)
+        self.width = int(params["width"])
+        self.eps = float(params["eps"])
+        self.name = prefix + params["name"]
+        self.weight: Optional[torch.Tensor] = None
+
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        return {self.name: TensorSpec((self.width,), init="one_plus_normal")}
+
+    def load(self, tensors) -> None:
+        self.weight = tensors[self.name]
+
+    def forward(self, x: torch.Tensor, ctx=None, row_index: Optional[torch.Tensor] = None,
+                rows: Optional[int] = None) -> torch.Tensor:
+        n = rows if rows is not None else x.shape[0]
+        out = self.rt.empty(n, self.width)
+        self.rt.kernels.rmsnorm(x, self.weight, out, self.eps, row_index=row_index)
+        return out

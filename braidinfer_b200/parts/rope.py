@@ -1,0 +1,43 @@
+"""Rotary position encoding, fused with the write of keys and values into the cache.
+
+inv_freq[p] = theta^(-2p/rd) (reference: crates/braidinfer-runtime/src/weights.rs:743-751);
+each pair (a, b) of a head becomes (a cos - b sin, a sin + b cos) with angle
+pos * inv_freq[p] (kernels/megakernel_ops.hip:2019-2030).  The pair is (x[2p], x[2p+1])
+for pairing "adjacent", as in that kernel, or (x[p], x[p + rd/2]) for "half".  Keys are
+rotated once, before they are stored; attention never rotates a cached key again.
+Angles, sine and cosine are float32.
+"""
+from __future__ import annotations
+
+import torch
+
+from .base import POSITION_ENCODINGS, PositionEncoding
+
+
+@POSITION_ENCODINGS.register("rope")
+class RotaryEncoding(PositionEncoding):
+    """params: head_dim, theta, rope_dim (default head_dim), pairing ("half" | "adjacent")."""
+
+    def __init__(self, params, prefix, runtime) -> None:
+        super().__init__(params, prefix, runtime)
+        self.head_dim = int(params["head_dim"])
+        self.rope_dim = int(params.get("rope_dim", self.head_dim))
+        self.theta = float(params["theta"])
+        self.pairing = params.get("pairing", "half")
+        if self.pairing not in ("half", "adjacent"):
+            raise ValueError(f"rope pairing must be 'half' or 'adjacent', got {self.pairing!r}")
+        if self.rope_dim % 2 or not (0 < self.rope_dim <= self.head_dim):
+            raise ValueError(f"rope_dim={self.rope_dim} must be even and within head_dim={self.head_dim}")
+        p = torch.arange(self.rope_dim // 2, dtype=torch.float64)
+        inv = 1.0 / (self.theta ** (2.0 * p / self.rope_dim))
+        self.inv_freq = inv.to(torch.float32).to(runtime.device)
+
+    def encode_and_store(self, qkv: torch.Tensor, nqh: int, nkh: int, ctx, cache) -> None:
+        """Rotate the query and key heads of qkv [rows, (nqh + 2 nkh) * hd] in place and
+        write keys and values into `cache` (a LayerCache, or None / read-only: no write)."""
+        writable = cache is not None and not cache.read_only
+        self.rt.kernels.rope_kv_write(
+            qkv, self.inv_freq, ctx.positions, ctx.token_seq,
+            cache.page_table if writable else None, cache.storage if writable else None,
+            nqh, nkh, self.head_dim, self.rope_dim, self.pairing == "adjacent",
+            cache.page_size if cache is not None else 1)

@@ -1,0 +1,26 @@
+"""What every part needs to run: the element type of activations, the device and
+the kernel library.  The residual stream and the logits are float32 in every mode."""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Optional
+
+import torch
+
+
+@dataclass
+class Runtime:
+    act_dtype: torch.dtype                 # torch.bfloat16 or torch.float32
+    device: torch.device
+    kernels: Any                           # braidinfer_b200.csrc.api.Kernels
+    # "auto": tensor-core kernels where they apply; "plain": the simple kernels only
+    # (tests compare the two).
+    gemm_backend: str = "auto"
+    attention_backend: str = "auto"
+
+    @property
+    def is_f32(self) -> bool:
+        return self.act_dtype == torch.float32
+
+    def empty(self, *shape, dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+        return torch.empty(*shape, dtype=dtype or self.act_dtype, device=self.device)

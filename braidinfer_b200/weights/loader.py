@@ -1,0 +1,87 @@
+"""Loading a model's tensors by name.
+
+What is asked for comes from the parts (`DecoderModel.tensor_specs`); what is there
+comes from the folder.  The two are compared before anything is copied, and every
+difference is reported in one error: missing tensors, unexpected tensors, wrong
+shapes (the reference reports them one at a time and panics on a size mismatch,
+crates/braidinfer-runtime/src/weights.rs:229-236, :301-307).
+
+Element types: floating tensors stored in 16 bits are kept in bfloat16, a tensor
+stored in 32 bits stays float32, integer tables become int32.  A float32 run widens
+everything floating to float32 (exactly; bfloat16 -> float32 loses nothing).
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Mapping, Optional, Tuple
+
+import torch
+
+from ..parts.spec import TensorSpec
+from .safetensors_io import open_model_folder
+
+
+class WeightsError(ValueError):
+    """The folder's tensors do not fit the model.  Attributes list what is wrong."""
+
+    def __init__(self, folder: str, missing: List[str], unexpected: List[str],
+                 wrong_shape: List[Tuple[str, Tuple[int, ...], Tuple[int, ...]]],
+                 wrong_dtype: List[Tuple[str, str]] = ()) -> None:
+        self.missing = list(missing)
+        self.unexpected = list(unexpected)
+        self.wrong_shape = list(wrong_shape)
+        self.wrong_dtype = list(wrong_dtype)
+        lines = [f"{folder}: the stored tensors do not fit the model"]
+        if self.missing:
+            lines.append(f"  missing ({len(self.missing)}): " + ", ".join(self.missing))
+        if self.unexpected:
+            lines.append(f"  unexpected ({len(self.unexpected)}): " + ", ".join(self.unexpected))
+        if self.wrong_shape:
+            lines.append(f"  wrong shape ({len(self.wrong_shape)}): " + ", ".join(
+                f"{n} is {list(got)}, expected {list(want)}" for n, got, want in self.wrong_shape))
+        if self.wrong_dtype:
+            lines.append(f"  wrong element type ({len(self.wrong_dtype)}): " + ", ".join(
+                f"{n} is {dt}" for n, dt in self.wrong_dtype))
+        super().__init__("\n".join(lines))
+
+
+def target_dtype(stored: torch.dtype, spec: TensorSpec, run_dtype: torch.dtype) -> torch.dtype:
+    if spec.integer or not stored.is_floating_point:
+        return torch.int32
+    if run_dtype == torch.float32:
+        return torch.float32
+    if stored in (torch.float32, torch.float64):
+        return torch.float32
+    return torch.bfloat16
+
+
+def load_tensors(folder: str, specs: Mapping[str, TensorSpec], run_dtype: torch.dtype,
+                 device) -> Dict[str, torch.Tensor]:
+    """Check the folder against `specs`, then copy every asked-for tensor to `device`."""
+    found = open_model_folder(folder)
+    missing = [n for n, s in specs.items() if n not in found and not s.optional]
+    unexpected = [n for n in found if n not in specs]
+    wrong_shape, wrong_dtype = [], []
+    for n, s in specs.items():
+        if n not in found:
+            continue
+        f, key = found[n]
+        dt, shape = f.info(key)
+        if tuple(shape) != tuple(s.shape):
+            wrong_shape.append((n, tuple(shape), tuple(s.shape)))
+        if s.integer == dt.is_floating_point:
+            wrong_dtype.append((n, str(dt)))
+    if missing or unexpected or wrong_shape or wrong_dtype:
+        raise WeightsError(folder, missing, unexpected, wrong_shape, wrong_dtype)
+    out: Dict[str, torch.Tensor] = {}
+    for n, s in specs.items():
+        if n not in found:
+            continue
+        f, key = found[n]
+        t = f.tensor(key)
+        want = target_dtype(t.dtype, s, run_dtype)
+        if t.dtype == want:
+            out[n] = t.to(device, copy=True)
+        else:
+            # convert on the device: the host copy stays a view of the mapped file
+            out[n] = t.to(device).to(want)
+    return out
