@@ -1,0 +1,94 @@
+"""The Python entry point.
+
+The reference is a Rust library with a `generate` binary; its calls are
+`Model::load_with_max_seq_len(dir, device, max_seq_len)`, `prefill(tokens)`,
+`decode_step(token, position)`, `generate_from_ids(...)`, `greedy_generate(...)` and
+`sampling::generate(model, prompt_tokens, params, stop_tokens, max_new_tokens)`
+(crates/braidinfer-runtime/src/model/model_load.rs:55, model/state.rs:39,
+model/mod.rs:279, generate.rs:314, :468, sampling.rs:181).  This module keeps those
+names and meanings and widens them from one sequence to batches.
+"""
+from __future__ import annotations
+
+import os
+from typing import List, Optional, Sequence, Union
+
+from .config import preset, read_config_json
+from .engine.engine import Engine
+from .engine.generate import Completion, GenerationLoop, GenerationStats
+from .sampling import Sampler, SamplingParams
+
+DEFAULT_MAX_SEQ_LEN_CAP = 8192      # the reference's default cap on context (model_load.rs:49, 113-116)
+
+
+class Model:
+    """A loaded model with its cache, ready to generate."""
+
+    def __init__(self, engine: Engine, max_batch: int) -> None:
+        self.engine = engine
+        self.config = engine.config
+        self.sampler = Sampler(engine.kernels, engine.device)
+        self.max_batch = max_batch
+        self.last_stats: Optional[GenerationStats] = None
+
+    # -- batched generation
+    def generate(self, prompts: Union[Sequence[int], Sequence[Sequence[int]]],
+                 params: Union[SamplingParams, Sequence[SamplingParams], None] = None,
+                 stop_tokens: Optional[Sequence[int]] = None, max_new_tokens: Union[int, Sequence[int]] = 64
+                 ) -> Union[List[int], List[Completion]]:
+        """Generate after token-id prompts.  One prompt (a list of ints) returns the new
+        token ids, as the reference's `sampling::generate` does; a list of prompts
+        returns a `Completion` for each.  `stop_tokens` defaults to the model's
+        eos_token_id.  A stop token ends a sequence and is not returned."""
+        single = len(prompts) > 0 and isinstance(prompts[0], int)
+        plist = [list(prompts)] if single else [list(p) for p in prompts]
+        if stop_tokens is None:
+            stop_tokens = self.config.eos_token_id or ()
+        loop = GenerationLoop(self.engine, self.sampler, max_batch=self.max_batch)
+        out = loop.generate(plist, params, max_new_tokens, stop_tokens)
+        self.last_stats = loop.stats
+        return out[0].tokens if single else out
+
+    def generate_from_ids(self, prompt_ids: Sequence[int], max_tokens: int = 64) -> List[int]:
+        """Greedy generation after one prompt (generate.rs:314-439)."""
+        return self.generate(list(prompt_ids), SamplingParams.greedy(), None, max_tokens)
+
+    # -- the step API of the reference, for one sequence at a time
+    def prefill(self, tokens: Sequence[int]):
+        """Start a sequence with its prompt; returns (slot, float32 logits of the last token)."""
+        slot = self.engine.open()
+        return slot, self.engine.step([(slot, list(tokens))], want="last")[0]
+
+    def decode_step(self, slot: int, token: int):
+        """Append one token to a sequence; returns the logits after it."""
+        return self.engine.step([(slot, [int(token)])], want="last")[0]
+
+    def reset_state(self, slot: int) -> None:
+        self.engine.close(slot)
+
+
+def load(model: str, dtype: str = "bfloat16", max_seq_len: Optional[int] = None, max_batch: int = 8,
+         seed: int = 0, device: str = "cuda:0", verbose: bool = True, **engine_options) -> Model:
+    """Load a model folder (config.json + safetensors), or `random:<preset>` for seeded
+    random weights of a named size.  `max_seq_len` caps the context of a sequence
+    (default: the config's max_position_embeddings, at most 8192, as in the
+    reference); the cache is sized for `max_batch` such sequences."""
+    if model.startswith("random:"):
+        cfg_dict = preset(model.split(":", 1)[1])
+        source = None
+    else:
+        if not os.path.isdir(model):
+            raise FileNotFoundError(f"MODEL={model!r} is not a folder (use a model folder or random:<preset>)")
+        cfg_dict = read_config_json(model)
+        source = model
+    if max_seq_len is None:
+        max_seq_len = min(int(cfg_dict.get("max_position_embeddings", 2048)), DEFAULT_MAX_SEQ_LEN_CAP)
+    per_seq = -(-max_seq_len // 64) * 64
+    opts = dict(dtype=dtype, max_tokens=per_seq * max_batch, max_slots=max_batch, device=device, verbose=verbose)
+    opts.update(engine_options)
+    if source is None:
+        big = cfg_dict["hidden_size"] * cfg_dict["num_hidden_layers"] > 1 << 14
+        engine = Engine.from_random(cfg_dict, seed, on_device=big, **opts)
+    else:
+        engine = Engine.from_folder(source, **opts)
+    return Model(engine, max_batch)

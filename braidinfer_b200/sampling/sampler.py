@@ -1,0 +1,75 @@
+"""Chooses the next token of every sequence of a batch on the device.
+
+Rows that are plainly greedy go through the argmax kernel; everything else through
+the sampling kernel, which applies the reference's chain in its order
+(crates/braidinfer-runtime/src/sampling.rs:49-171).  The uniform number of each draw
+comes from `rng.uniform(seed, sequence, step)`.
+"""
+from __future__ import annotations
+
+from collections import Counter
+from typing import List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from .params import SamplingParams
+from .rng import entropy_seed, uniform
+
+
+class Sampler:
+    def __init__(self, kernels, device) -> None:
+        self.K = kernels
+        self.device = device
+
+    def choose(self, logits: torch.Tensor, params: Sequence[SamplingParams], seeds: Sequence[int],
+               sequence_ids: Sequence[int], steps: Sequence[int],
+               histories: Optional[Sequence[Sequence[int]]] = None) -> List[int]:
+        """logits [rows, vocab] float32 on the device -> one token id per row (host ints).
+        `histories[i]` is what the repetition penalty looks at (prompt + generated)."""
+        rows, vocab = logits.shape
+        out = torch.empty(rows, dtype=torch.int32, device=self.device)
+        if all(p.is_plain_greedy for p in params):
+            self.K.argmax(logits, out)
+            return self._read(out)
+        f = np.zeros((5, rows), dtype=np.float32)      # temperature, top_p, min_p, rep_penalty, uniform
+        k = np.zeros(rows, dtype=np.int32)
+        hist_off, hist_tok, hist_cnt = [0], [], []
+        bias_off, bias_tok, bias_val = [0], [], []
+        for i, p in enumerate(params):
+            f[0, i], f[1, i], f[2, i], f[3, i] = p.temperature, p.top_p, p.min_p, p.repetition_penalty
+            f[4, i] = uniform(seeds[i], sequence_ids[i], steps[i])
+            k[i] = p.top_k
+            if p.repetition_penalty != 1.0 and histories is not None:
+                for tok, cnt in Counter(histories[i]).items():
+                    hist_tok.append(tok)
+                    hist_cnt.append(cnt)
+            hist_off.append(len(hist_tok))
+            if p.logit_bias:
+                for tok, delta in p.logit_bias:
+                    bias_tok.append(tok)
+                    bias_val.append(delta)
+            bias_off.append(len(bias_tok))
+        fd = torch.from_numpy(f).to(self.device)
+        ints = np.concatenate([k, np.asarray(hist_off, np.int32), np.asarray(bias_off, np.int32),
+                               np.asarray(hist_tok, np.int32), np.asarray(hist_cnt, np.int32),
+                               np.asarray(bias_tok, np.int32)]).astype(np.int32)
+        idev = torch.from_numpy(ints).to(self.device)
+        o = 0
+        kd = idev[o:o + rows]; o += rows
+        ho = idev[o:o + rows + 1]; o += rows + 1
+        bo = idev[o:o + rows + 1]; o += rows + 1
+        ht = idev[o:o + len(hist_tok)]; o += len(hist_tok)
+        hc = idev[o:o + len(hist_cnt)]; o += len(hist_cnt)
+        bt = idev[o:o + len(bias_tok)]
+        bv = torch.tensor(bias_val, dtype=torch.float32, device=self.device) if bias_val else None
+        work = torch.empty((rows, vocab), dtype=torch.float32, device=self.device)
+        self.K.sample(logits, work, out, fd[0], fd[4], top_k=kd, top_p=fd[1], min_p=fd[2], rep_penalty=fd[3],
+                      hist_off=ho, hist_tok=ht if hist_tok else None, hist_cnt=hc if hist_cnt else None,
+                      bias_off=bo, bias_tok=bt if bias_tok else None, bias_val=bv)
+        return self._read(out)
+
+    def _read(self, out: torch.Tensor) -> List[int]:
+        toks = out.tolist()                    # synchronises: the step's results are complete here
+        self.K.check_device_errors()
+        return toks

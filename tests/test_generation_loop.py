@@ -1,0 +1,112 @@
+"""The generation loop's decisions, on the CPU, with a stand-in engine whose "model"
+is a fixed rule: the next token after token t is (t + 1) % vocab."""
+import pytest
+import torch
+
+from braidinfer_b200.engine.generate import GenerationLoop, plan_batches
+from braidinfer_b200.sampling import SamplingParams
+
+VOCAB = 50
+
+
+class FakeEngine:
+    def __init__(self, max_tokens=64 * 4, max_slots=4):
+        self.max_tokens, self.max_slots = max_tokens, max_slots
+        self.free = list(range(max_slots))
+        self.live = {}
+        self.calls = []
+        self.closed = []
+
+    def open(self):
+        s = self.free.pop(0)
+        self.live[s] = []
+        return s
+
+    def close(self, s):
+        assert s in self.live, "slot freed twice"
+        del self.live[s]
+        self.free.append(s)
+        self.closed.append(s)
+
+    def step(self, entries, want="last"):
+        assert want == "last"
+        self.calls.append([(s, list(t)) for s, t in entries])
+        out = torch.full((len(entries), VOCAB), -1.0)
+        for i, (s, t) in enumerate(entries):
+            self.live[s].extend(t)
+            out[i, (t[-1] + 1) % VOCAB] = 1.0
+        return out
+
+
+class ArgmaxSampler:
+    def choose(self, logits, params, seeds, ids, steps, hist):
+        self.last = (list(ids), list(steps), [list(h) for h in hist])
+        return logits.argmax(-1).tolist()
+
+
+def test_plan_batches_respects_count_and_capacity():
+    assert plan_batches([5, 5, 5], [10, 10, 10], 64 * 8, 2) == [[0, 1], [2]]
+    assert plan_batches([60, 60, 60], [10, 10, 10], 256, 8) == [[0, 1], [2]]      # 128 tokens each after rounding
+    assert plan_batches([], [], 64, 4) == []
+    with pytest.raises(ValueError, match="request 1"):
+        plan_batches([5, 100], [5, 100], 128, 4)
+
+
+def test_prompt_in_one_step_then_one_token_each():
+    eng, smp = FakeEngine(), ArgmaxSampler()
+    out = GenerationLoop(eng, smp).generate([[3, 4, 5], [10]], max_new_tokens=3)
+    assert [o.tokens for o in out] == [[6, 7, 8], [11, 12, 13]]
+    assert all(o.finish_reason == "length" for o in out)
+    assert eng.calls[0] == [(0, [3, 4, 5]), (1, [10])]                # both prompts in the first step
+    assert eng.calls[1] == [(0, [6]), (1, [11])]
+    assert len(eng.calls) == 3                                        # no step after the last token
+    assert not eng.live and sorted(eng.closed) == [0, 1]
+
+
+def test_stop_token_is_not_returned_and_frees_the_slot_at_once():
+    eng = FakeEngine()
+    out = GenerationLoop(eng, ArgmaxSampler()).generate([[1], [20]], max_new_tokens=6, stop_tokens=[4])
+    assert out[0].tokens == [2, 3] and out[0].finish_reason == "stop"
+    assert out[1].tokens == [21, 22, 23, 24, 25, 26] and out[1].finish_reason == "length"
+    assert eng.closed[0] == 0                                          # the shorter one left first
+    assert eng.calls[3] == [(1, [23])]                                 # and the batch went on without it
+    # a stop token as the very first choice: nothing is emitted
+    out = GenerationLoop(FakeEngine(), ArgmaxSampler()).generate([[3]], max_new_tokens=5, stop_tokens=[4])
+    assert out[0].tokens == [] and out[0].finish_reason == "stop"
+
+
+def test_batches_follow_one_another_and_reuse_slots():
+    eng = FakeEngine(max_tokens=64 * 2, max_slots=2)
+    prompts = [[i] for i in range(5)]
+    out = GenerationLoop(eng, ArgmaxSampler(), max_batch=8).generate(prompts, max_new_tokens=[1, 2, 3, 1, 2])
+    assert [o.tokens for o in out] == [[1], [2, 3], [3, 4, 5], [4], [5, 6]]
+    assert [len(c) for c in eng.calls] == [2, 1, 2, 1, 1, 1, 1]
+    assert not eng.live and len(eng.closed) == 5 and set(eng.closed) == {0, 1}
+
+
+def test_per_sequence_step_counters_and_histories_reach_the_sampler():
+    eng, smp = FakeEngine(), ArgmaxSampler()
+    GenerationLoop(eng, smp).generate([[7, 8], [30]], max_new_tokens=[3, 1])
+    ids, steps, hist = smp.last
+    assert ids == [0] and steps == [2] and hist == [[7, 8, 9, 10]]
+
+
+def test_edge_cases():
+    loop = GenerationLoop(FakeEngine(), ArgmaxSampler())
+    with pytest.raises(ValueError, match="empty"):
+        loop.generate([[]])
+    out = loop.generate([[5]], max_new_tokens=0)
+    assert out[0].tokens == [] and out[0].finish_reason == "length"
+    with pytest.raises(ValueError):
+        loop.generate([[5], [6]], params=[SamplingParams.greedy()])
+
+    class Boom(FakeEngine):
+        def step(self, entries, want="last"):
+            if len(self.calls) == 1:
+                raise RuntimeError("boom")
+            return super().step(entries, want)
+
+    eng = Boom()
+    with pytest.raises(RuntimeError):
+        GenerationLoop(eng, ArgmaxSampler()).generate([[1], [2]], max_new_tokens=4)
+    assert not eng.live                                               # nothing stays held after an error
