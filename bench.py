@@ -1,0 +1,266 @@
+#!/usr/bin/env python3
+"""Measures generation on one B200: decode tokens a second at batch 8 (the headline), at
+batch 1 and 64, and prefill of 2,048 tokens, on the Mistral-7B-v0.3 layer sizes with
+random weights and random token ids.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+Prints ONE JSON line.  A step is one decode step of the whole batch.  `value` times K
+steps with CUDA events on the launching stream (engine step + token choice, tokens fed
+back without a host read); `e2e` is the same number through the Python entry point
+(`Model.generate`): host token ids in, host token ids out, every step copying its
+inputs from pinned host memory and reading its chosen tokens back.  Weights (14.5 GB)
+exceed the 126 MB L2, so no L2 flush is needed between steps.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        try:
+            with open(path) as f:
+                d = json.load(f)
+            return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]), "source": "measured"}
+        except Exception:
+            pass
+    return dict(FALLBACK_PEAKS, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int = 0) -> None:
+        self.index = index
+        self.proc = None
+        self.path = None
+
+    def __enter__(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.out = open(self.path, "w")
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=self.out, stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+        return self
+
+    def __exit__(self, *a):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except Exception:
+                self.proc.kill()
+            self.out.close()
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        try:
+            with open(self.path) as f:
+                for line in f:
+                    p = [x.strip() for x in line.split(",")]
+                    if len(p) < 7:
+                        continue
+                    try:
+                        sm.append(float(p[0])); mx.append(float(p[1]))
+                    except ValueError:
+                        continue
+                    for n, v in zip(names, p[3:7]):
+                        if v.lower().startswith("active"):
+                            reasons.add(n)
+            os.unlink(self.path)
+        except Exception:
+            pass
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def model_numbers(cfg, n_layers):
+    """Bytes a decode step reads and FLOPs a prefill does, from the configuration."""
+    hs, I, V = cfg.hidden_size, cfg.intermediate_size, cfg.vocab_size
+    nq, nk, hd = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+    per_layer_params = (nq + 2 * nk) * hd * hs + hs * nq * hd + 3 * I * hs + 2 * hs
+    weight_bytes = 2 * (n_layers * per_layer_params + V * hs + hs)          # layers, head, final norm
+    kv_bytes_per_token = n_layers * 2 * nk * hd * 2
+    return per_layer_params, weight_bytes, kv_bytes_per_token
+
+
+def prefill_flops(cfg, n_layers, T):
+    hs, I, V = cfg.hidden_size, cfg.intermediate_size, cfg.vocab_size
+    nq, nk, hd = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+    lin = 2 * T * ((nq + 2 * nk) * hd * hs + hs * nq * hd + 3 * I * hs)
+    attn = 2 * 2 * nq * hd * (T * (T + 1) // 2)                             # causal QK^T and PV
+    return n_layers * (lin + attn) + 2 * V * hs
+
+
+def device_timed_decode(engine, sampler_kernels, prompts, steps, warmup):
+    """K decode steps of the whole batch, timed with CUDA events; returns (seconds, context at start)."""
+    import torch
+    slots = [engine.open() for _ in prompts]
+    logits = engine.step(list(zip(slots, prompts)), want="last")
+    out = torch.empty(len(prompts), dtype=torch.int32, device=engine.device)
+    sampler_kernels.argmax(logits, out)
+    toks = out.tolist()
+    for _ in range(warmup):
+        logits = engine.step([(s, [t]) for s, t in zip(slots, toks)], want="last")
+        sampler_kernels.argmax(logits, out)
+    toks = out.tolist()
+    ctx0 = engine.length(slots[0])
+    entries = [(s, [t]) for s, t in zip(slots, toks)]
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches0 = engine.kernels.launches
+    e0.record()
+    for _ in range(steps):
+        logits = engine.step(entries, want="last")
+        sampler_kernels.argmax(logits, out)
+    e1.record()
+    torch.cuda.synchronize()
+    engine.check()
+    launches = engine.kernels.launches - launches0
+    for s in slots:
+        engine.close(s)
+    return e0.elapsed_time(e1) / 1e3, ctx0, launches
+
+
+def run_ours(args):
+    import torch
+    from braidinfer_b200.api import Model
+    from braidinfer_b200.config import preset
+    from braidinfer_b200.engine import Engine
+    from braidinfer_b200.sampling import SamplingParams
+
+    pk = peaks()
+    cfg_dict = preset("mistral_7b_v03")
+    full_layers = cfg_dict["num_hidden_layers"]
+    if args.layers:
+        cfg_dict["num_hidden_layers"] = args.layers
+    n_layers = cfg_dict["num_hidden_layers"]
+    B, prompt_len, gen_len, ctx_len = args.batch, 2048, 256, 4096
+    steps, warmup = args.steps, max(3, args.warmup)
+    t0 = time.time()
+    engine = Engine.from_random(cfg_dict, seed=0, dtype="bfloat16", on_device=True, max_tokens=64 * ctx_len,
+                                max_slots=64, verbose=True)
+    cfg = engine.config
+    model = Model(engine, max_batch=64)
+    g = torch.Generator().manual_seed(0)
+
+    def prompts_for(b, n=prompt_len):
+        return [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for _ in range(b)]
+
+    _, weight_bytes, kv_per_tok = model_numbers(cfg, n_layers)
+
+    # ---- prefill of 2,048 tokens (one sequence), timed on the device
+    p1 = prompts_for(1)
+    times = []
+    for i in range(3 + 3):
+        s = engine.open()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        engine.step([(s, p1[0])], want="last")
+        e1.record()
+        torch.cuda.synchronize()
+        engine.close(s)
+        if i >= 3:
+            times.append(e0.elapsed_time(e1))
+    pre_ms = statistics.median(times)
+    pre_flops = prefill_flops(cfg, n_layers, prompt_len)
+    prefill = {"value": prompt_len / (pre_ms / 1e3), "tokens": prompt_len, "ms": pre_ms,
+               "frac": pre_flops / (pre_ms / 1e3) / (pk["bf16_tflops"] * 1e12), "unit": "tokens/s",
+               "peak": f"{pk['bf16_tflops']} TFLOP/s bf16, {pk['source']}"}
+
+    # ---- decode at the headline batch, device-timed, with clocks sampled meanwhile
+    with ClockSampler() as cs:
+        secs, ctx0, launches = device_timed_decode(engine, engine.kernels, prompts_for(B), steps, warmup)
+    clocks = cs.summary()
+    value = B * steps / secs
+    ms_per_step = secs / steps * 1e3
+    avg_ctx = ctx0 + steps / 2
+    step_bytes = weight_bytes + B * avg_ctx * kv_per_tok + B * cfg.hidden_size * 2
+    achieved = step_bytes / (secs / steps) / 1e9
+    roofline = {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                "frac": achieved / pk["hbm_gbs"], "peak_source": pk["source"], "bytes_per_step": step_bytes}
+
+    # ---- the same through the Python entry point: host tokens in, host tokens out
+    outs = model.generate(prompts_for(B), SamplingParams.greedy(), stop_tokens=(), max_new_tokens=min(steps, gen_len) + 1)
+    st = model.last_stats
+    e2e = {"value": st.decode_tokens / st.decode_seconds if st.decode_seconds > 0 else 0.0, "unit": "tokens/s",
+           "h2d_bytes_per_step": engine.packer.h2d_bytes_last, "d2h_bytes_per_step": B * 4 + 16,
+           "prefill_tokens_per_s": st.prompt_tokens / st.prefill_seconds if st.prefill_seconds > 0 else 0.0}
+
+    # ---- other batch sizes
+    points = {}
+    for b in (1, 64):
+        k = min(steps, 64)
+        s2, _, _ = device_timed_decode(engine, engine.kernels, prompts_for(b), k, warmup)
+        points[f"decode_b{b}"] = b * k / s2
+
+    line = {
+        "metric": "decode tokens/s at batch 8, Mistral-7B-v0.3 sizes, bf16 (also batch 1, 64; prefill of 2,048 tokens)",
+        "value": value, "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic: random weights N(0, 0.02) seed 0, uniform random token ids",
+        "impl": "ours",
+        "config": {"model": "Mistral-7B-v0.3 sizes", "layers": n_layers, "layers_of_full_model": full_layers,
+                   "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
+                   "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
+                   "rope_theta": cfg.rope_theta, "rms_eps": cfg.rms_norm_eps, "global_batch": B,
+                   "seq_len": ctx_len, "prompt_len": prompt_len, "context_at_timing": int(avg_ctx),
+                   "cache_tokens": 64 * ctx_len, "parallelism": "single GPU",
+                   "l2": "inputs (14.5 GB of weights) exceed L2; no flush"},
+        "e2e": e2e, "gpu_launches": launches, "clocks": clocks, "prefill": prefill, "roofline": roofline,
+        "points": points, "setup_seconds": time.time() - t0,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+def run_reference(args):
+    print(json.dumps({"impl": "reference", "unavailable":
+                      "mcelrath/braidinfer is Rust + HIP for AMD RDNA3: pip finds neither setup.py nor pyproject.toml, "
+                      "and this image has no cargo, rustc, hipcc or ROCm"}))
+    return 0
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (0: all)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference(args)
+    if args.gpus != 1:
+        print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    return run_ours(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())
