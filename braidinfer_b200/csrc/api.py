@@ -51,6 +51,9 @@ class Kernels:
         self._declare()
         self._error_flag = torch.zeros(4, dtype=torch.int32, device="cuda")
         self._tc_workspace: Optional[torch.Tensor] = None
+        self._attn_libs = {}
+        self._attn_partial: Optional[torch.Tensor] = None
+        self._verbose = verbose
 
     # ------------------------------------------------------------------ plumbing
     def _declare(self) -> None:
@@ -158,6 +161,49 @@ class Kernels:
             positions.data_ptr(), token_seq.data_ptr(), q.stride(0), out.stride(0), rows, nqh, nkh, hd,
             page_size, page_table.shape[1], cache.shape[0], int(window or 0), float(scale), self._stream()),
             "attn_simple")
+
+    @staticmethod
+    def attn_mma_supports(head_dim: int) -> bool:
+        return head_dim % 16 == 0 and 16 <= head_dim <= 256
+
+    def attn_mma_library(self, head_dim: int):
+        """The attention library for one head size, compiled at first use."""
+        lib = self._attn_libs.get(head_dim)
+        if lib is None:
+            if not self.attn_mma_supports(head_dim):
+                raise KernelError(f"the tensor-core attention takes head sizes in steps of 16 up to 256, not {head_dim}")
+            lib = ctypes.CDLL(str(build.attention_library(head_dim, verbose=self._verbose)))
+            lib.braid_last_error.restype = c_char_p
+            lib.braid_attn_mma.restype = c_int
+            lib.braid_attn_mma.argtypes = [c_void_p] * 9 + [c_int] * 12 + [c_float, c_void_p]
+            lib.braid_attn_mma_partial_floats.restype = c_longlong
+            lib.braid_attn_mma_partial_floats.argtypes = [c_int, c_int, c_int]
+            self._attn_libs[head_dim] = lib
+        return lib
+
+    def attn_mma(self, q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, page_table: torch.Tensor,
+                 q_start: torch.Tensor, q_len: torch.Tensor, kv_before: torch.Tensor, token_seq: torch.Tensor,
+                 n_seqs: int, max_q_len: int, nqh: int, nkh: int, hd: int, window: Optional[int], scale: float,
+                 n_splits: int = 1, few_tokens: bool = False) -> None:
+        """bfloat16 attention over the cache on the tensor cores; `n_splits` > 1 slices the
+        context (for steps of few tokens) and merges the slices in a second kernel."""
+        lib = self.attn_mma_library(hd)
+        rows = out.shape[0]
+        partial = None
+        if n_splits > 1:
+            need = lib.braid_attn_mma_partial_floats(rows, nqh, n_splits)
+            if self._attn_partial is None or self._attn_partial.numel() < need:
+                self._attn_partial = torch.empty(need, dtype=torch.float32, device="cuda")
+            partial = self._attn_partial
+            self.launches += 1
+        self.launches += 1
+        rc = lib.braid_attn_mma(q.data_ptr(), out.data_ptr(), _ptr(partial), cache.data_ptr(), page_table.data_ptr(),
+                                q_start.data_ptr(), q_len.data_ptr(), kv_before.data_ptr(), token_seq.data_ptr(),
+                                q.stride(0), out.stride(0), rows, n_seqs, max_q_len, nqh, nkh, hd,
+                                page_table.shape[1], int(window or 0), n_splits, 1 if few_tokens else 0,
+                                float(scale), self._stream())
+        if rc != 0:
+            raise KernelError(f"attn_mma: {lib.braid_last_error().decode(errors='replace')} (code {rc})")
 
     # ------------------------------------------------------------------ matrix products
     def gemm_simt(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, residual: Optional[torch.Tensor] = None) -> None:

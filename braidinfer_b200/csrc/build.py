@@ -137,3 +137,10 @@ def build_library(name: str, sources: Sequence[str], defines: Sequence[str] = ()
 
 def core_library(verbose: bool = True) -> Path:
     return build_library("braidinfer_core", CORE_SOURCES, verbose=verbose)
+
+
+def attention_library(head_dim: int, verbose: bool = True) -> Path:
+    """The tensor-core attention kernels compiled for one head size (what a model needs
+    is compiled when the model is first built)."""
+    return build_library(f"braidinfer_attn_hd{head_dim}", ["errors.cu", "attn_mma.cu"],
+                         defines=[f"-DBRAID_HD={head_dim}"], verbose=verbose)

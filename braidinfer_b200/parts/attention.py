@@ -19,6 +19,10 @@ from .linear import Linear
 from .spec import CacheRequest, PartSpec, TensorSpec
 
 
+# One-warp CTAs of the few-token attention kernel to aim for (148 SMs, several each).
+_DECODE_CTAS = 148 * 6
+
+
 @MIXERS.register("gqa_attention")
 class GQAAttention(Mixer):
     """params: hidden_size, num_heads, num_kv_heads, head_dim, window (int | None),
@@ -72,7 +76,23 @@ class GQAAttention(Mixer):
 
     def _attend(self, qkv, out, ctx, cache) -> None:
         """Pick the attention kernel for this step.  float32 runs, and runs that ask for
-        the plain kernels, use the one-warp-per-query kernel for everything."""
+        the plain kernels, use the one-warp-per-query kernel for everything; bfloat16
+        runs use the tensor-core kernel, slicing the context when the step brings few
+        tokens so that a handful of sequences still fills the machine."""
         K = self.rt.kernels
-        K.attn_simple(qkv, out, cache.storage, cache.page_table, ctx.positions, ctx.token_seq,
-                      self.nqh, self.nkh, self.hd, cache.page_size, self.window, self.scale)
+        plain = (self.rt.is_f32 or self.rt.attention_backend == "plain" or not K.attn_mma_supports(self.hd))
+        if plain:
+            K.attn_simple(qkv, out, cache.storage, cache.page_table, ctx.positions, ctx.token_seq,
+                          self.nqh, self.nkh, self.hd, cache.page_size, self.window, self.scale)
+            return
+        few = ctx.max_q_len <= 8
+        n_splits = 1
+        if few:
+            g = self.nqh // self.nkh
+            ctas = ctx.n_seqs * self.nkh * -(-g // 16)
+            span = min(ctx.max_kv_len, self.window) if self.window else ctx.max_kv_len
+            tiles = max(1, -(-span // 32))
+            n_splits = max(1, min(-(-_DECODE_CTAS // ctas), tiles // 2, 64))
+        K.attn_mma(qkv, out, cache.storage, cache.page_table, ctx.q_start, ctx.q_len, ctx.kv_before, ctx.token_seq,
+                   ctx.n_seqs, ctx.max_q_len, self.nqh, self.nkh, self.hd, self.window, self.scale,
+                   n_splits=n_splits, few_tokens=few)
