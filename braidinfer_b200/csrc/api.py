@@ -52,6 +52,7 @@ class Kernels:
         self._error_flag = torch.zeros(4, dtype=torch.int32, device="cuda")
         self._tc_workspace: Optional[torch.Tensor] = None
         self._attn_libs = {}
+        self.workspace_generation = 0   # grows when a scratch buffer moves (captured graphs are stale then)
         self._attn_partial: Optional[torch.Tensor] = None
         self._verbose = verbose
 
@@ -193,7 +194,8 @@ class Kernels:
         if n_splits > 1:
             need = lib.braid_attn_mma_partial_floats(rows, nqh, n_splits)
             if self._attn_partial is None or self._attn_partial.numel() < need:
-                self._attn_partial = torch.empty(need, dtype=torch.float32, device="cuda")
+                self._attn_partial = torch.empty(max(need, 1 << 22), dtype=torch.float32, device="cuda")
+                self.workspace_generation += 1
             partial = self._attn_partial
             self.launches += 1
         self.launches += 1
@@ -217,7 +219,8 @@ class Kernels:
 
     def tc_workspace(self, nbytes: int) -> torch.Tensor:
         if self._tc_workspace is None or self._tc_workspace.numel() * 4 < nbytes:
-            self._tc_workspace = torch.empty((nbytes + 3) // 4, dtype=torch.float32, device="cuda")
+            self._tc_workspace = torch.empty(max((nbytes + 3) // 4, 1 << 22), dtype=torch.float32, device="cuda")
+            self.workspace_generation += 1
         return self._tc_workspace
 
     def gemm_tc(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, residual: Optional[torch.Tensor] = None,

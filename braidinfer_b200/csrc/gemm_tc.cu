@@ -21,6 +21,11 @@
 //                 3  float32 partial sums of one slice of k (split-k), reduced by
 //                    braid_gemm_splitk_reduce with one of the epilogues above.
 //
+// The kernel is persistent: one CTA per SM walks its share of the work units (output tile
+// x slice of k).  The loader runs ahead across units, and with two accumulator buffers
+// in tensor memory (whenever 2 x BLOCK_N x accumulators fits its 512 columns) the
+// epilogue of one unit overlaps the products of the next.
+//
 // Every wait on an mbarrier is bounded; a wait that runs out sets *error_flag, tells the
 // other warps to stop, and the kernel frees its tensor memory and returns.
 //
@@ -114,7 +119,8 @@ struct GemmTcArgs {
     int n_rows, m_out, k_in;   // mode 2: m_out is the number of gate rows (w has 2 * m_out rows)
     long long ldo;
     int out_dtype;
-    int kb_per_split;          // 64-wide k blocks handled by one blockIdx.z
+    int kb_per_split;          // 64-wide k blocks handled by one slice of k
+    int m_tiles, n_tiles, splits;
     int* error_flag;
 };
 
@@ -126,10 +132,34 @@ struct TcCfg {
     static constexpr int kStageBytes = kABytes + kBBytes;
     static constexpr int kBudget = 200 * 1024;
     static constexpr int kStagesRaw = kBudget / kStageBytes;
-    static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
-    static constexpr int kTmemCols = (BLOCK_N * kAccs) < 32 ? 32 : (BLOCK_N * kAccs);
+    static constexpr int kStages = kStagesRaw > 10 ? 10 : kStagesRaw;
+    static constexpr int kAccCols = BLOCK_N * kAccs;                       // columns of one accumulator buffer
+    static constexpr int kAccBufs = (kAccCols * 2 <= 512) ? 2 : 1;          // two: the epilogue overlaps the next tile
+    static constexpr int kTmemCols = (kAccCols * kAccBufs) < 32 ? 32 : (kAccCols * kAccBufs);
     static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /* alignment */ + 256 /* barriers */;
 };
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// A persistent CTA walks work units u = blockIdx.x, blockIdx.x + gridDim.x, ...; a unit is
+// one [128 x BLOCK_N] output tile for one slice of k.  Token tiles vary fastest so that
+// CTAs running side by side share weight tiles in L2.
+struct TcUnit { int m0, n0, split, kb_begin, num_kb; };
+__device__ __forceinline__ TcUnit tc_unit(const GemmTcArgs& a, int u, int block_n) {
+    TcUnit t;
+    const int nt = u % a.n_tiles;
+    const int rest = u / a.n_tiles;
+    const int mt = rest % a.m_tiles;
+    t.split = rest / a.m_tiles;
+    t.m0 = mt * TC_BLOCK_M;
+    t.n0 = nt * block_n;
+    const int total_kb = (a.k_in + TC_BLOCK_K - 1) / TC_BLOCK_K;
+    t.kb_begin = t.split * a.kb_per_split;
+    t.num_kb = max(0, min(total_kb, t.kb_begin + a.kb_per_split) - t.kb_begin);
+    return t;
+}
 
 template <int BLOCK_N, int MODE>
 __global__ void __launch_bounds__(TC_THREADS, 1)
@@ -140,21 +170,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     uint64_t* bars = (uint64_t*)(smem + Cfg::kStages * Cfg::kStageBytes);
     uint64_t* full = bars;
     uint64_t* empty = bars + Cfg::kStages;
-    uint64_t* acc_full = bars + 2 * Cfg::kStages;
-    uint32_t* tmem_slot = (uint32_t*)(bars + 2 * Cfg::kStages + 1);
+    uint64_t* acc_full = bars + 2 * Cfg::kStages;          // [kAccBufs]
+    uint64_t* acc_empty = acc_full + 2;                    // [kAccBufs]
+    uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = blockIdx.x * TC_BLOCK_M;
-    const int n0 = blockIdx.y * BLOCK_N;
-    const int total_kb = (a.k_in + TC_BLOCK_K - 1) / TC_BLOCK_K;
-    const int kb_begin = blockIdx.z * a.kb_per_split;
-    const int kb_end = min(total_kb, kb_begin + a.kb_per_split);
-    const int num_kb = max(0, kb_end - kb_begin);
+    const int num_units = a.m_tiles * a.n_tiles * a.splits;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < Cfg::kStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-        mbar_init(acc_full, 1);
+        for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 128); }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -167,84 +193,116 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 
     if (warp == 0) {
         if (lane == 0) {
-            for (int i = 0; i < num_kb; ++i) {
-                const int s = i % Cfg::kStages;
-                const uint32_t ph = (uint32_t)(i / Cfg::kStages) & 1u;
-                if (!mbar_wait(&empty[s], ph ^ 1u, abort_flag)) break;
-                uint8_t* sa = smem + s * Cfg::kStageBytes;
-                uint8_t* sb = sa + Cfg::kABytes;
-                mbar_expect_tx(&full[s], Cfg::kStageBytes);
-                const int kx = (kb_begin + i) * TC_BLOCK_K;
-                tma_load_2d(&map_w, &full[s], sa, kx, m0);
-                if (MODE == 2) tma_load_2d(&map_w, &full[s], sa + TC_BLOCK_M * TC_BLOCK_K * 2, kx, a.m_out + m0);
-                tma_load_2d(&map_x, &full[s], sb, kx, n0);
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int u = blockIdx.x; u < num_units && ok; u += gridDim.x) {
+                const TcUnit t = tc_unit(a, u, BLOCK_N);
+                for (int i = 0; i < t.num_kb; ++i) {
+                    ok = mbar_wait(&empty[stage], phase ^ 1u, abort_flag);
+                    if (!ok) break;
+                    uint8_t* sa = smem + stage * Cfg::kStageBytes;
+                    uint8_t* sb = sa + Cfg::kABytes;
+                    mbar_expect_tx(&full[stage], Cfg::kStageBytes);
+                    const int kx = (t.kb_begin + i) * TC_BLOCK_K;
+                    tma_load_2d(&map_w, &full[stage], sa, kx, t.m0);
+                    if (MODE == 2) tma_load_2d(&map_w, &full[stage], sa + TC_BLOCK_M * TC_BLOCK_K * 2, kx, a.m_out + t.m0);
+                    tma_load_2d(&map_x, &full[stage], sb, kx, t.n0);
+                    if (++stage == Cfg::kStages) { stage = 0; phase ^= 1u; }
+                }
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
             constexpr uint32_t idesc = umma_idesc_bf16(TC_BLOCK_M, BLOCK_N);
+            int stage = 0, buf = 0;
+            uint32_t phase = 0, acc_phase = 0;      // bit b: phase of accumulator buffer b
             bool ok = true;
-            for (int i = 0; i < num_kb && ok; ++i) {
-                const int s = i % Cfg::kStages;
-                const uint32_t ph = (uint32_t)(i / Cfg::kStages) & 1u;
-                ok = mbar_wait(&full[s], ph, abort_flag);
+            for (int u = blockIdx.x; u < num_units && ok; u += gridDim.x) {
+                const TcUnit t = tc_unit(a, u, BLOCK_N);
+                ok = mbar_wait(&acc_empty[buf], ((acc_phase >> buf) & 1u) ^ 1u, abort_flag);   // the epilogue has drained this buffer
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t sa = smem_u32(smem + s * Cfg::kStageBytes);
-                const uint32_t sb = sa + Cfg::kABytes;
+                const uint32_t tmem_d = tmem_base + buf * Cfg::kAccCols;
+                for (int i = 0; i < t.num_kb; ++i) {
+                    ok = mbar_wait(&full[stage], phase, abort_flag);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t sa = smem_u32(smem + stage * Cfg::kStageBytes);
+                    const uint32_t sb = sa + Cfg::kABytes;
 #pragma unroll
-                for (int k = 0; k < TC_BLOCK_K / TC_UMMA_K; ++k) {
-                    const uint32_t koff = k * TC_UMMA_K * 2;     // bytes along the 128-byte row
-                    const uint32_t accum = (i > 0 || k > 0) ? 1u : 0u;
-                    umma_bf16(tmem_base, umma_desc_sw128(sa + koff), umma_desc_sw128(sb + koff), idesc, accum);
-                    if (MODE == 2)
-                        umma_bf16(tmem_base + BLOCK_N, umma_desc_sw128(sa + TC_BLOCK_M * TC_BLOCK_K * 2 + koff),
-                                  umma_desc_sw128(sb + koff), idesc, accum);
+                    for (int k = 0; k < TC_BLOCK_K / TC_UMMA_K; ++k) {
+                        const uint32_t koff = k * TC_UMMA_K * 2;     // bytes along the 128-byte row
+                        const uint32_t accum = (i > 0 || k > 0) ? 1u : 0u;
+                        umma_bf16(tmem_d, umma_desc_sw128(sa + koff), umma_desc_sw128(sb + koff), idesc, accum);
+                        if (MODE == 2)
+                            umma_bf16(tmem_d + BLOCK_N, umma_desc_sw128(sa + TC_BLOCK_M * TC_BLOCK_K * 2 + koff),
+                                      umma_desc_sw128(sb + koff), idesc, accum);
+                    }
+                    umma_commit(&empty[stage]);
+                    if (++stage == Cfg::kStages) { stage = 0; phase ^= 1u; }
                 }
-                umma_commit(&empty[s]);
+                if (!ok) break;
+                umma_commit(&acc_full[buf]);
+                acc_phase ^= (1u << buf);
+                if (Cfg::kAccBufs == 2) buf ^= 1;
             }
-            if (ok) umma_commit(acc_full);
         }
     } else {
         // epilogue warps: warp w may read tensor-memory lanes 32 * (w % 4) ...
         const int quarter = warp & 3;
-        const int m = m0 + quarter * 32 + lane;
+        int buf = 0;
+        uint32_t full_phase = 0;                  // bit b: phase of accumulator buffer b
         bool ok = true;
-        if (num_kb > 0) ok = mbar_wait(acc_full, 0, abort_flag);
-        tc_fence_after();
-        if (ok) {
-            const uint32_t trow = tmem_base + ((uint32_t)(quarter * 32) << 16);
+        for (int u = blockIdx.x; u < num_units && ok; u += gridDim.x) {
+            const TcUnit t = tc_unit(a, u, BLOCK_N);
+            const int m = t.m0 + quarter * 32 + lane;
+            ok = mbar_wait(&acc_full[buf], (full_phase >> buf) & 1u, abort_flag);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t trow = tmem_base + buf * Cfg::kAccCols + ((uint32_t)(quarter * 32) << 16);
 #pragma unroll 1
             for (int c0 = 0; c0 < BLOCK_N; c0 += 16) {
-                if (n0 + c0 >= a.n_rows) break;
+                if (t.n0 + c0 >= a.n_rows) break;
                 float v[16];
-                if (num_kb > 0) tmem_ld16(trow + c0, v);
-                else {
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) v[i] = 0.f;
-                }
+                tmem_ld16(trow + c0, v);
                 if (MODE == 2) {
-                    float u[16];
-                    tmem_ld16(trow + BLOCK_N + c0, u);
+                    float up[16];
+                    tmem_ld16(trow + BLOCK_N + c0, up);
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) v[i] = v[i] / (1.f + expf(-v[i])) * u[i];
+                    for (int i = 0; i < 16; ++i) v[i] = v[i] / (1.f + expf(-v[i])) * up[i];
                 }
                 if (m < a.m_out) {
+                    if (MODE == 3) {
+                        float* dst = (float*)a.out + ((size_t)t.split * a.n_rows + t.n0 + c0) * a.m_out + m;
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        const int n = n0 + c0 + i;
-                        if (n >= a.n_rows) break;
-                        if (MODE == 3) {
-                            ((float*)a.out)[((size_t)blockIdx.z * a.n_rows + n) * a.m_out + m] = v[i];
-                        } else {
-                            const size_t o = (size_t)n * a.ldo + m;
-                            if (MODE == 1) ((float*)a.out)[o] = a.res[o] + v[i];
-                            else if (a.out_dtype == BRAID_F32) ((float*)a.out)[o] = v[i];
-                            else ((__nv_bfloat16*)a.out)[o] = __float2bfloat16_rn(v[i]);
+                        for (int i = 0; i < 16; ++i)
+                            if (t.n0 + c0 + i < a.n_rows) dst[(size_t)i * a.m_out] = v[i];
+                    } else if (MODE == 1) {
+                        // all loads of the residual first: out may be res itself, which would
+                        // otherwise chain every load behind the store before it
+                        const size_t o0 = (size_t)(t.n0 + c0) * a.ldo + m;
+                        float r[16];
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) r[i] = (t.n0 + c0 + i < a.n_rows) ? a.res[o0 + (size_t)i * a.ldo] : 0.f;
+#pragma unroll
+                        for (int i = 0; i < 16; ++i)
+                            if (t.n0 + c0 + i < a.n_rows) ((float*)a.out)[o0 + (size_t)i * a.ldo] = r[i] + v[i];
+                    } else {
+                        const size_t o0 = (size_t)(t.n0 + c0) * a.ldo + m;
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            if (t.n0 + c0 + i >= a.n_rows) break;
+                            if (a.out_dtype == BRAID_F32) ((float*)a.out)[o0 + (size_t)i * a.ldo] = v[i];
+                            else ((__nv_bfloat16*)a.out)[o0 + (size_t)i * a.ldo] = __float2bfloat16_rn(v[i]);
                         }
                     }
                 }
             }
+            tc_fence_before();
+            mbar_arrive(&acc_empty[buf]);
+            full_phase ^= (1u << buf);
+            if (Cfg::kAccBufs == 2) buf ^= 1;
         }
     }
     tc_fence_before();
@@ -312,6 +370,16 @@ static int make_map(CUtensorMap* map, const void* base, long long rows, long lon
     return BRAID_OK;
 }
 
+static int sm_count() {
+    static int n = 0;
+    if (!n) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    }
+    return n;
+}
+
 template <int BLOCK_N, int MODE>
 static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const GemmTcArgs& a, dim3 grid, cudaStream_t s) {
     using Cfg = TcCfg<BLOCK_N, MODE>;
@@ -373,17 +441,20 @@ extern "C" int braid_gemm_tc(const void* x, const void* w, void* out, const floa
     rc = make_map(&mx, x, n_rows, k_in, ldx, block_n);
     if (rc) return rc;
     const unsigned n_tiles = (n_rows + block_n - 1) / block_n;
-    if (n_tiles > 65535) BRAID_REFUSE("gemm_tc: %d rows exceed the grid limit", n_rows);
 
     if (splits == 1) {
-        GemmTcArgs a{out, res, n_rows, m_out, k_in, ldo, out_dtype, kb_per_split, error_flag};
-        dim3 grid((m_out + TC_BLOCK_M - 1) / TC_BLOCK_M, n_tiles, 1);
+        const int m_tiles = (m_out + TC_BLOCK_M - 1) / TC_BLOCK_M;
+        GemmTcArgs a{out, res, n_rows, m_out, k_in, ldo, out_dtype, kb_per_split, m_tiles, (int)n_tiles, 1, error_flag};
+        const long long units = (long long)m_tiles * n_tiles;
+        dim3 grid((unsigned)(units < sm_count() ? units : sm_count()), 1, 1);
         if (mode == 0) return dispatch_tc<0>(block_n, mw, mx, a, grid, s);
         if (mode == 1) return dispatch_tc<1>(block_n, mw, mx, a, grid, s);
         return dispatch_tc<2>(block_n, mw, mx, a, grid, s);
     }
-    GemmTcArgs a{workspace, nullptr, n_rows, w_rows, k_in, 0, BRAID_F32, kb_per_split, error_flag};
-    dim3 grid((w_rows + TC_BLOCK_M - 1) / TC_BLOCK_M, n_tiles, splits);
+    const int m_tiles = (w_rows + TC_BLOCK_M - 1) / TC_BLOCK_M;
+    GemmTcArgs a{workspace, nullptr, n_rows, w_rows, k_in, 0, BRAID_F32, kb_per_split, m_tiles, (int)n_tiles, splits, error_flag};
+    const long long units = (long long)m_tiles * n_tiles * splits;
+    dim3 grid((unsigned)(units < sm_count() ? units : sm_count()), 1, 1);
     rc = dispatch_tc<3>(block_n, mw, mx, a, grid, s);
     if (rc) return rc;
     const long long total = (long long)n_rows * m_out;

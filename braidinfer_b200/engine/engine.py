@@ -36,7 +36,8 @@ def parse_dtype(name: Union[str, torch.dtype]) -> torch.dtype:
 class Engine:
     def __init__(self, config_dict: Mapping, tensors_or_folder, *, dtype="bfloat16", max_tokens: int = 8192,
                  max_slots: Optional[int] = None, device: str = "cuda:0", gemm_backend: str = "auto",
-                 attention_backend: str = "auto", row_multiple: int = 1, verbose: bool = True) -> None:
+                 attention_backend: str = "auto", row_multiple: int = 1, use_graphs: bool = True,
+                 verbose: bool = True) -> None:
         from ..csrc.api import get_kernels
         self.dtype = parse_dtype(dtype)
         self.device = torch.device(device)
@@ -63,6 +64,13 @@ class Engine:
         self.packer = StepPacker(self.device, row_multiple=row_multiple)
         self.vocab_size = self.spec.vocab_size
         self.steps_run = 0
+        # Steps in which every sequence brings one token are launch-bound: the second time
+        # a step shape is seen it is captured in a CUDA graph and replayed from then on.
+        self.use_graphs = bool(use_graphs) and all(p.graph_safe for p in self.model.all_parts())
+        self._graphs: Dict[tuple, object] = {}
+        self._graph_seen: Dict[tuple, int] = {}
+        self._graph_generation = (self.packer.generation, self.kernels.workspace_generation)
+        self.graph_replays = 0
 
     # ------------------------------------------------------------------ construction
     @classmethod
@@ -142,11 +150,49 @@ class Engine:
         before = [self.cache.length(s) for s in slots]
         n_new = [len(t) for t in tokens]
         tables = self.cache.begin_step(slots, n_new)
-        ctx = self.packer.pack(slots, tokens, before, want_l, tables)
-        logits = self.model.forward(ctx, self.cache)
+        graphable = self.use_graphs and all(n == 1 for n in n_new)
+        ctx = self.packer.pack(slots, tokens, before, want_l, tables, bucket_tables=graphable)
+        if graphable:
+            logits = self._graph_step(ctx)
+        else:
+            logits = self.model.forward(ctx, self.cache)
         self.cache.end_step(slots, n_new)
         self.steps_run += 1
         return logits
+
+    def _graph_step(self, ctx: StepContext) -> Optional[torch.Tensor]:
+        """Run a one-token-per-sequence step through a CUDA graph.  The graph holds kernel
+        launches only; the step's tables were copied to fixed device addresses before it.
+        Launch shapes may depend on the step's shape alone, so the context length that
+        shapes the attention launch is the bound the page tables' width gives.  The
+        graph writes its logits into its own memory; the caller gets a copy."""
+        generation = (self.packer.generation, self.kernels.workspace_generation)
+        if generation != self._graph_generation:       # a buffer that graphs point into has moved
+            self._graphs.clear()
+            self._graph_seen.clear()
+            self._graph_generation = generation
+        ctx.max_kv_len = max(t.shape[1] for t in ctx.page_tables) * PAGE_SIZE if ctx.page_tables else ctx.max_kv_len
+        key = (ctx.rows, ctx.n_seqs, ctx.n_want, tuple(tuple(t.shape) for t in ctx.page_tables))
+        entry = self._graphs.get(key)
+        if entry is None:
+            seen = self._graph_seen.get(key, 0)
+            self._graph_seen[key] = seen + 1
+            if seen == 0:                    # first sight: run kernel by kernel (also warms every kernel up)
+                return self.model.forward(ctx, self.cache)
+            if len(self._graphs) >= 64:
+                self._graphs.pop(next(iter(self._graphs)))
+            before = self.kernels.launches
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                static_logits = self.model.forward(ctx, self.cache)
+            entry = (graph, static_logits, self.kernels.launches - before)
+            self.kernels.launches = before
+            self._graphs[key] = entry
+        graph, static_logits, n_launches = entry
+        graph.replay()
+        self.kernels.launches += n_launches
+        self.graph_replays += 1
+        return static_logits.clone() if static_logits is not None else None
 
     def check(self) -> None:
         """Raise if a kernel flagged an error since the last check (synchronises)."""

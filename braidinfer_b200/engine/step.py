@@ -56,19 +56,31 @@ class StepPacker:
         self._dev: Optional[torch.Tensor] = None
         self._copied: Optional[torch.cuda.Event] = None
         self.h2d_bytes_last = 0
+        self.generation = 0          # grows when the device buffer moves (captured graphs are stale then)
 
     def _buffers(self, n: int) -> Tuple[torch.Tensor, torch.Tensor]:
         if self._pinned is None or self._pinned.numel() < n:
-            cap = max(4096, 1 << (n - 1).bit_length())
+            cap = max(1 << 18, 1 << (n - 1).bit_length())
             if self._copied is not None:
                 self._copied.synchronize()
+            self.generation += 1
             self._pinned = torch.empty(cap, dtype=torch.int32, pin_memory=True)
             self._dev = torch.empty(cap, dtype=torch.int32, device=self.device)
         return self._pinned, self._dev
 
     def pack(self, slots: Sequence[int], tokens: Sequence[Sequence[int]], kv_before: Sequence[int],
-             want: Sequence[Sequence[int]], tables: Sequence[np.ndarray]) -> StepContext:
+             want: Sequence[Sequence[int]], tables: Sequence[np.ndarray], bucket_tables: bool = False) -> StepContext:
+        """`bucket_tables` widens every page table to a power-of-two number of columns (at
+        least 8), so that steps of the same shape lay their tables out identically."""
         n_seqs = len(slots)
+        if bucket_tables:
+            wide = []
+            for t in tables:
+                cols = max(8, 1 << (t.shape[1] - 1).bit_length())
+                w = np.full((t.shape[0], cols), -1, dtype=np.int32)
+                w[:, :t.shape[1]] = t
+                wide.append(w)
+            tables = wide
         q_len = [len(t) for t in tokens]
         n_tokens = sum(q_len)
         rows = -(-n_tokens // self.row_multiple) * self.row_multiple

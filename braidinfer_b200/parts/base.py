@@ -18,6 +18,11 @@ from .spec import CacheRequest, PartSpec, TensorSpec
 class Part:
     """Common base: tensors in, nothing else assumed."""
 
+    # A part whose forward reads the step's host-side fields, or otherwise does work that
+    # a CUDA graph cannot replay, sets this to False; the engine then launches every
+    # step kernel by kernel.
+    graph_safe = True
+
     def __init__(self, params: dict, prefix: str, runtime) -> None:
         self.params = dict(params)
         self.prefix = prefix
