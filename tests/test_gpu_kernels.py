@@ -1,0 +1,350 @@
+"""Each kernel alone against a plain float64 reference, at sizes other than the
+engine's tiny models: widths and vocabularies that are no power of two, odd head
+counts and groups, head sizes in steps of 16."""
+import math
+
+import pytest
+import torch
+
+import plain_mistral as P
+from braidinfer_b200.csrc.api import KernelError, get_kernels
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+@pytest.fixture(scope="module")
+def K():
+    return get_kernels(verbose=False)
+
+
+def rnd(*shape, dtype=torch.float32, scale=1.0, seed=0):
+    g = torch.Generator(device=DEV).manual_seed(seed + sum(shape))
+    return (torch.randn(*shape, device=DEV, generator=g) * scale).to(dtype)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_embed(K, dtype):
+    table = rnd(301, 72, dtype=dtype)
+    ids = torch.tensor([0, 300, 17, 17, 5], dtype=torch.int32, device=DEV)
+    out = torch.full((5, 72), 9.0, device=DEV)
+    K.embed(table, ids, out)
+    assert torch.equal(out, P.embedding(table.cpu(), ids.tolist()).to(DEV))
+
+
+@pytest.mark.parametrize("width", [72, 1000, 4099])
+@pytest.mark.parametrize("wd, od", [(torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16),
+                                     (torch.float32, torch.bfloat16)])
+def test_rmsnorm(K, width, wd, od):
+    x = rnd(7, width, scale=3.0)
+    w = (1 + rnd(width, scale=0.1, seed=1)).to(wd)
+    out = torch.full((7, width), 9.0, device=DEV, dtype=od)
+    K.rmsnorm(x, w, out, 3e-6)
+    ref = P.rmsnorm(x.double().cpu(), w.double().cpu(), 3e-6)
+    tol = 2e-6 if od == torch.float32 else 1 / 128
+    assert ((out.double().cpu() - ref).abs() <= tol * ref.abs() + 1e-6).all()
+    # gathered rows (the rows whose logits are wanted), with an absent row
+    idx = torch.tensor([6, 0, -1, 3], dtype=torch.int32, device=DEV)
+    out2 = torch.full((4, width), 9.0, device=DEV, dtype=od)
+    K.rmsnorm(x, w, out2, 3e-6, row_index=idx)
+    assert torch.equal(out2[0], out[6]) and torch.equal(out2[1], out[0]) and torch.equal(out2[3], out[3])
+    assert float(out2[2].abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_silu_mul_and_residual_add_and_cast(K, dtype):
+    gu = rnd(5, 2 * 177, dtype=dtype, scale=2.0)
+    out = torch.empty(5, 177, device=DEV, dtype=dtype)
+    K.silu_mul(gu, out)
+    g, u = gu[:, :177].double(), gu[:, 177:].double()
+    ref = g / (1 + torch.exp(-g)) * u
+    tol = 1e-6 if dtype == torch.float32 else 1 / 128
+    assert ((out.double() - ref).abs() <= tol * ref.abs() + 1e-6).all()
+    h = rnd(5, 177)
+    h0 = h.clone()
+    K.residual_add(h, out)
+    assert torch.equal(h, h0 + out.float())
+    a = rnd(1000, dtype=torch.float32)
+    b = torch.empty(1000, device=DEV, dtype=torch.bfloat16)
+    K.cast(a, b)
+    assert torch.equal(b, a.bfloat16())
+
+
+def make_cache(n_seqs, lens, nkh, hd, dtype, shuffle_seed=0, page=64):
+    need = [-(-l // page) for l in lens]
+    total = sum(need) + 2
+    cache = torch.zeros(total, 2, nkh, page, hd, device=DEV, dtype=dtype)
+    perm = torch.randperm(total, generator=torch.Generator().manual_seed(shuffle_seed)).tolist()
+    table = torch.full((n_seqs, max(need)), -1, dtype=torch.int32)
+    k = 0
+    for i, n in enumerate(need):
+        for c in range(n):
+            table[i, c] = perm[k]
+            k += 1
+    return cache, table.to(DEV)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("pairing, rope_dim", [("half", 48), ("adjacent", 48), ("half", 32)])
+def test_rope_and_cache_write(K, dtype, pairing, rope_dim):
+    nqh, nkh, hd, theta = 5, 3, 48, 12345.0
+    seqs = [(60, 10), (0, 3)]                       # (cache length before, new tokens); the first crosses a page
+    cache, table = make_cache(2, [b + n for b, n in seqs], nkh, hd, dtype)
+    rows = sum(n for _, n in seqs) + 2              # two padding rows
+    qkv = rnd(rows, (nqh + 2 * nkh) * hd, dtype=dtype)
+    before = qkv.clone()
+    pos = [p for b, n in seqs for p in range(b, b + n)] + [0, 0]
+    seq = [i for i, (b, n) in enumerate(seqs) for _ in range(n)] + [-1, -1]
+    inv = P.inv_freq(rope_dim, theta).to(DEV)
+    K.rope_kv_write(qkv, inv, torch.tensor(pos, dtype=torch.int32, device=DEV),
+                    torch.tensor(seq, dtype=torch.int32, device=DEV), table, cache, nqh, nkh, hd, rope_dim,
+                    pairing == "adjacent", 64)
+    K.check_device_errors()
+    assert torch.equal(qkv[-2:], before[-2:])       # padding rows untouched
+    tol = 1e-5 if dtype == torch.float32 else 1 / 100
+    x = before[:-2].double().cpu().view(rows - 2, nqh + 2 * nkh, hd)
+    p = torch.tensor(pos[:-2])
+    want_q = x[:, :nqh].clone()
+    want_k = x[:, nqh:nqh + nkh].clone()
+    want_q[..., :rope_dim] = P.rope(x[:, :nqh, :rope_dim].contiguous(), p, theta, pairing)
+    want_k[..., :rope_dim] = P.rope(x[:, nqh:nqh + nkh, :rope_dim].contiguous(), p, theta, pairing)
+    got = qkv[:-2].double().cpu().view(rows - 2, nqh + 2 * nkh, hd)
+    assert (got[:, :nqh] - want_q).abs().max() < tol * 4
+    assert torch.equal(got[:, nqh + nkh:], x[:, nqh + nkh:])               # values are not rotated
+    for r, (s, ps) in enumerate(zip(seq[:-2], pos[:-2])):
+        page = int(table[s, ps // 64])
+        kc = cache[page, 0, :, ps % 64].double().cpu()
+        vc = cache[page, 1, :, ps % 64].double().cpu()
+        assert (kc - want_k[r]).abs().max() < tol * 4
+        assert torch.equal(vc, x[r, nqh + nkh:])
+
+
+def attention_reference(q, k_all, v_all, pos, window):
+    """q [nqh, hd] at position pos over keys/values [len, nkh, hd]: plain softmax."""
+    nqh, hd = q.shape
+    nkh = k_all.shape[1]
+    out = torch.empty(nqh, hd, dtype=torch.float64)
+    lo = max(0, pos - window + 1) if window else 0
+    for h in range(nqh):
+        kv = h // (nqh // nkh)
+        s = (k_all[lo:pos + 1, kv] @ q[h]) / math.sqrt(hd)
+        out[h] = torch.softmax(s, 0) @ v_all[lo:pos + 1, kv]
+    return out
+
+
+def attention_case(K, which, dtype, hd, nqh, nkh, seqs, window, n_splits=1, few=False, plant=None):
+    """seqs: (cache length before, new tokens).  `plant` = (seq, query offset, key position):
+    that key is made to dominate that query's scores, its value made distinctive."""
+    lens = [b + n for b, n in seqs]
+    cache, table = make_cache(len(seqs), lens, nkh, hd, dtype, shuffle_seed=3)
+    kv_ref = []
+    for i, L in enumerate(lens):
+        k = rnd(L, nkh, hd, dtype=dtype, seed=10 + i)
+        v = rnd(L, nkh, hd, dtype=dtype, seed=20 + i)
+        kv_ref.append((k, v))
+    rows = sum(n for _, n in seqs)
+    W = (nqh + 2 * nkh) * hd
+    qkv = rnd(rows + 1, W, dtype=dtype, seed=5)
+    q_start, r = [], 0
+    for b, n in seqs:
+        q_start.append(r)
+        r += n
+    if plant is not None:
+        s, qo, kp = plant
+        row = q_start[s] + qo
+        k, v = kv_ref[s]
+        qv = qkv[row, :nqh * hd].view(nqh, hd)
+        g = nqh // nkh
+        for h in range(nqh):
+            qv[h] = qv[(h // g) * g]                                    # the heads of a group ask alike
+            k[kp, h // g] = (qv[h].float() * 3.0).to(dtype)             # q . k is large and positive
+        v[kp] = 5.0
+    for i, (k, v) in enumerate(kv_ref):
+        for p_ in range(lens[i]):
+            page = int(table[i, p_ // 64])
+            cache[page, 0, :, p_ % 64] = k[p_]
+            cache[page, 1, :, p_ % 64] = v[p_]
+    pos = [p_ for b, n in seqs for p_ in range(b, b + n)] + [0]
+    seq = [i for i, (b, n) in enumerate(seqs) for _ in range(n)] + [-1]
+    t = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
+    out = torch.full((rows + 1, nqh * hd), 9.0, device=DEV, dtype=dtype)
+    if which == "simple":
+        K.attn_simple(qkv, out, cache, table, t(pos), t(seq), nqh, nkh, hd, 64, window, 1 / math.sqrt(hd))
+    else:
+        K.attn_mma(qkv, out, cache, table, t(q_start), t([n for _, n in seqs]), t([b for b, _ in seqs]), t(seq),
+                   len(seqs), max(n for _, n in seqs), nqh, nkh, hd, window, 1 / math.sqrt(hd),
+                   n_splits=n_splits, few_tokens=few)
+    torch.cuda.synchronize()
+    worst = 0.0
+    for r_ in range(rows):
+        s = seq[r_]
+        k, v = kv_ref[s]
+        q = qkv[r_, :nqh * hd].view(nqh, hd).double().cpu()
+        ref = attention_reference(q, k.double().cpu(), v.double().cpu(), pos[r_], window)
+        worst = max(worst, (out[r_].view(nqh, hd).double().cpu() - ref).abs().max().item())
+    return worst, out, q_start
+
+
+ATTN_SHAPES = [
+    # hd, nqh, nkh, seqs, window
+    (16, 4, 2, [(0, 70), (5, 9), (0, 1)], None),
+    (32, 6, 2, [(0, 130), (200, 3)], 8),
+    (48, 5, 5, [(3, 140)], 70),
+    (80, 6, 3, [(0, 65), (64, 64)], 64),
+    (128, 8, 2, [(0, 300), (100, 50)], None),
+    (256, 3, 1, [(0, 90)], 17),
+]
+
+
+@pytest.mark.parametrize("hd, nqh, nkh, seqs, window", ATTN_SHAPES)
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_plain_attention_kernel(K, dtype, hd, nqh, nkh, seqs, window):
+    worst, _, _ = attention_case(K, "simple", dtype, hd, nqh, nkh, seqs, window)
+    assert worst < (2e-5 if dtype == torch.float32 else 2e-2)
+
+
+@pytest.mark.parametrize("hd, nqh, nkh, seqs, window", ATTN_SHAPES)
+def test_tensor_core_attention_kernel(K, hd, nqh, nkh, seqs, window):
+    worst, _, _ = attention_case(K, "mma", torch.bfloat16, hd, nqh, nkh, seqs, window)
+    assert worst < 2e-2
+
+
+@pytest.mark.parametrize("hd, nqh, nkh, seqs, window, splits", [
+    (128, 32, 8, [(2047, 1), (100, 1), (0, 1), (63, 1), (64, 1)], None, 8),
+    (128, 32, 8, [(700, 1), (100, 1)], 128, 4),
+    (32, 6, 2, [(300, 1), (5, 1)], 8, 3),
+    (16, 4, 2, [(30, 3), (64, 2)], None, 2),
+    (64, 40, 2, [(200, 1)], None, 5),
+    (96, 7, 7, [(129, 1)], None, 1),
+])
+def test_tensor_core_attention_sliced_context(K, hd, nqh, nkh, seqs, window, splits):
+    worst, _, _ = attention_case(K, "mma", torch.bfloat16, hd, nqh, nkh, seqs, window, n_splits=splits, few=True)
+    assert worst < 2e-2
+
+
+@pytest.mark.parametrize("which", ["simple", "mma", "mma_sliced"])
+def test_a_far_key_among_hundreds_and_the_windows_edge(K, which):
+    kw = dict(n_splits=7, few=True) if which == "mma_sliced" else {}
+    name = "simple" if which == "simple" else "mma"
+    hd, nqh, nkh = 64, 4, 2
+    # a key at position 3, 700 tokens back, owns the softmax: the output is its value
+    worst, out, qs = attention_case(K, name, torch.bfloat16, hd, nqh, nkh, [(703, 1)], None, plant=(0, 0, 3), **kw)
+    assert worst < 3e-2 and abs(float(out[0].float().mean()) - 5.0) < 0.1
+    # window 100, query at 703: position 604 is the last one inside, 603 the first one outside
+    worst, out, qs = attention_case(K, name, torch.bfloat16, hd, nqh, nkh, [(703, 1)], 100, plant=(0, 0, 604), **kw)
+    assert worst < 3e-2 and abs(float(out[0].float().mean()) - 5.0) < 0.1
+    worst, out, qs = attention_case(K, name, torch.bfloat16, hd, nqh, nkh, [(703, 1)], 100, plant=(0, 0, 603), **kw)
+    assert worst < 3e-2 and abs(float(out[0].float().mean())) < 1.0
+    # the same in a prompt: query 650 of a 704-token prompt looks at key 1
+    if which != "mma_sliced":
+        worst, out, qs = attention_case(K, name, torch.bfloat16, hd, nqh, nkh, [(0, 704)], None, plant=(0, 650, 1))
+        assert worst < 3e-2 and abs(float(out[650].float().mean()) - 5.0) < 0.1
+
+
+@pytest.mark.parametrize("n, m, k", [(5, 70, 33), (64, 64, 64), (130, 200, 96), (1, 331, 120)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_plain_matrix_product(K, dtype, n, m, k):
+    x, w = rnd(n, k, dtype=dtype), rnd(m, k, dtype=dtype, seed=1)
+    ref = x.double() @ w.double().t()
+    out = torch.full((n, m), 9.0, device=DEV)
+    K.gemm_simt(x, w, out)
+    assert (out.double() - ref).abs().max() < 1e-4 * max(1.0, ref.abs().max().item())
+    res = rnd(n, m, seed=2)
+    want = res.double() + ref
+    K.gemm_simt(x, w, res, residual=res)
+    assert (res.double() - want).abs().max() < 1e-4 * max(1.0, ref.abs().max().item())
+
+
+@pytest.mark.parametrize("n, m, k, splits", [
+    (16, 128, 64, 1), (33, 200, 96, 1), (1, 331, 120, 1), (300, 1000, 520, 1), (700, 384, 1024, 1),
+    (2048, 512, 256, 1), (8, 512, 4096, 4), (20, 256, 2048, 3), (64, 1408, 1024, 5), (3, 200, 8200, 7)])
+def test_tensor_core_matrix_product(K, n, m, k, splits):
+    x, w = rnd(n, k, dtype=torch.bfloat16, scale=0.5), rnd(m, k, dtype=torch.bfloat16, scale=0.5, seed=1)
+    ref = x.double() @ w.double().t()
+    scale = max(1.0, ref.abs().max().item())
+    out = torch.full((n, m), 9.0, device=DEV)
+    K.gemm_tc(x, w, out, splits=splits)
+    assert (out.double() - ref).abs().max() < 1e-5 * scale
+    plain = torch.empty(n, m, device=DEV)
+    K.gemm_simt(x, w, plain)
+    assert (out - plain).abs().max() < 1e-5 * scale                  # beside its plain twin
+    outb = torch.full((n, m), 9.0, device=DEV, dtype=torch.bfloat16)
+    K.gemm_tc(x, w, outb, splits=splits)
+    assert (outb.double() - ref).abs().max() < scale / 128
+    res = rnd(n, m, seed=2)
+    want = res.double() + ref
+    K.gemm_tc(x, w, res, residual=res, splits=splits)
+    assert (res.double() - want).abs().max() < 1e-5 * scale
+    K.check_device_errors()
+
+
+@pytest.mark.parametrize("n, inter, k, splits", [(300, 384, 512, 1), (17, 200, 96, 1), (20, 256, 2048, 3), (64, 1000, 520, 2)])
+def test_tensor_core_swiglu_epilogue(K, n, inter, k, splits):
+    x = rnd(n, k, dtype=torch.bfloat16, scale=0.5)
+    w = rnd(2 * inter, k, dtype=torch.bfloat16, scale=0.2, seed=1)
+    ref = x.double() @ w.double().t()
+    g, u = ref[:, :inter], ref[:, inter:]
+    want = g / (1 + torch.exp(-g)) * u
+    out = torch.full((n, inter), 9.0, device=DEV, dtype=torch.bfloat16)
+    K.gemm_tc(x, w, out, swiglu=True, splits=splits)
+    assert ((out.double() - want).abs() <= want.abs() / 100 + 1e-3).all()
+
+
+def test_tensor_core_product_refuses_what_tma_cannot_address(K):
+    x, w = rnd(4, 100, dtype=torch.bfloat16), rnd(128, 100, dtype=torch.bfloat16)     # row stride 100 is no multiple of 8
+    assert not K.gemm_tc_eligible(x, w)
+    with pytest.raises(KernelError, match="multiples of 8"):
+        K.gemm_tc(x, w, torch.empty(4, 128, device=DEV))
+    with pytest.raises(KernelError, match="head_dim"):
+        K.attn_simple(rnd(1, 300 * 3), torch.empty(1, 300, device=DEV), torch.zeros(1, 2, 1, 64, 300, device=DEV),
+                      torch.zeros(1, 1, dtype=torch.int32, device=DEV), torch.zeros(1, dtype=torch.int32, device=DEV),
+                      torch.zeros(1, dtype=torch.int32, device=DEV), 1, 1, 300, 64, None, 1.0)
+
+
+@pytest.mark.parametrize("vocab", [331, 1000, 32768, 50001])
+def test_argmax(K, vocab):
+    lg = rnd(6, vocab, scale=3.0)
+    lg[2, 7] = lg[2, vocab - 1] = 100.0                   # a tie: the lower index wins
+    out = torch.empty(6, dtype=torch.int32, device=DEV)
+    K.argmax(lg, out)
+    assert out.tolist() == [P.argmax_lowest(lg[i].cpu()) for i in range(6)] and out[2] == 7
+
+
+@pytest.mark.parametrize("vocab", [331, 5000])
+def test_sampling_chain(K, vocab):
+    rows = 12
+    lg = rnd(rows, vocab, scale=2.5, seed=4)
+    g = torch.Generator().manual_seed(0)
+    cases = []
+    for i in range(rows):
+        cases.append(dict(temperature=[0.8, 1.0, 0.0, 1.5, 0.3, 2.0][i % 6], top_k=[0, 50, 0, 5, 1, 200][i % 6],
+                          top_p=[1.0, 0.9, 1.0, 0.5, 1.0, 0.95][i % 6], min_p=[0.0, 0.0, 0.0, 0.05, 0.0, 0.01][i % 6],
+                          repetition_penalty=[1.0, 1.3, 1.2, 1.0, 1.0, 1.1][i % 6],
+                          u=float(torch.rand((), generator=g))))
+    hist = [[int(t) for t in torch.randint(0, vocab, (20,), generator=g)] + [3, 3, 3] for _ in range(rows)]
+    bias = [[(5, 2.5), (9, -1.0), (5, 0.5)] if i % 3 == 0 else [] for i in range(rows)]
+    from collections import Counter
+    f = lambda key: torch.tensor([c[key] for c in cases], dtype=torch.float32, device=DEV)
+    ho, ht, hc, bo, bt, bv = [0], [], [], [0], [], []
+    for i in range(rows):
+        for tok, cnt in Counter(hist[i]).items():
+            ht.append(tok); hc.append(cnt)
+        ho.append(len(ht))
+        for tok, d in bias[i]:
+            bt.append(tok); bv.append(d)
+        bo.append(len(bt))
+    ti = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
+    out = torch.empty(rows, dtype=torch.int32, device=DEV)
+    work = torch.empty_like(lg)
+    K.sample(lg, work, out, f("temperature"), f("u"), top_k=ti([c["top_k"] for c in cases]), top_p=f("top_p"),
+             min_p=f("min_p"), rep_penalty=f("repetition_penalty"), hist_off=ti(ho), hist_tok=ti(ht), hist_cnt=ti(hc),
+             bias_off=ti(bo), bias_tok=ti(bt), bias_val=torch.tensor(bv, dtype=torch.float32, device=DEV))
+    got = out.tolist()
+    for i, c in enumerate(cases):
+        kw = {k: v for k, v in c.items()}
+        want = P.sample(lg[i].cpu(), history=hist[i], logit_bias=bias[i], **kw)
+        if got[i] != want:
+            # the draw may land within rounding of a boundary of the cumulative sum
+            lo = P.sample(lg[i].cpu(), history=hist[i], logit_bias=bias[i], **dict(kw, u=max(0.0, c["u"] - 1e-5)))
+            hi = P.sample(lg[i].cpu(), history=hist[i], logit_bias=bias[i], **dict(kw, u=min(1.0, c["u"] + 1e-5)))
+            assert got[i] in (lo, hi), (i, c, got[i], want)
