@@ -224,21 +224,22 @@ class Kernels:
         return self._tc_workspace
 
     def gemm_tc(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, residual: Optional[torch.Tensor] = None,
-                swiglu: bool = False, block_n: int = 0, splits: int = 1) -> None:
+                swiglu: bool = False, block_n: int = 0, stream_k: bool = False) -> None:
         """bfloat16 x [n, k] times w [m, k]^T on the tensor cores.  With `swiglu`, w holds
-        gate rows then up rows and out is [n, m/2]."""
+        gate rows then up rows and out is [n, m/2].  `stream_k` spreads the weight stream
+        evenly over all SMs whatever the shape (for a few tokens) and adds a reduce kernel."""
         n, k = x.shape
         w_rows = w.shape[0]
         m = w_rows // 2 if swiglu else w_rows
         mode = 2 if swiglu else (1 if residual is not None else 0)
         ws = None
-        if splits > 1:
-            ws = self.tc_workspace(self.lib.braid_gemm_tc_workspace_bytes(n, w_rows, splits))
+        if stream_k:
+            ws = self.tc_workspace(self.lib.braid_gemm_tc_workspace_bytes(n, w_rows, k))
             self.launches += 1
         self.launches += 1
         self._check(self.lib.braid_gemm_tc(x.data_ptr(), w.data_ptr(), out.data_ptr(), _ptr(residual), _ptr(ws),
                                            dtype_code(out.dtype), mode, n, m, k, x.stride(0), w.stride(0),
-                                           out.stride(0), block_n, splits,
+                                           out.stride(0), block_n, int(stream_k),
                                            self._error_flag.data_ptr() + 4, self._stream()), "gemm_tc")
 
     @staticmethod

@@ -76,6 +76,8 @@ template <int HD, int NW, int BN, int ST>
 __global__ void __launch_bounds__(NW * 32)
 attn_mma_kernel(AttnMmaArgs a) {
     using C = AttnCfg<HD, NW, BN, ST>;
+    pdl_trigger();
+    pdl_wait();
     extern __shared__ __align__(16) uint8_t smem[];
     uint8_t* sQ = smem;
     uint8_t* sKV = smem + C::Q_BYTES;
@@ -269,6 +271,8 @@ attn_mma_kernel(AttnMmaArgs a) {
 template <int HD>
 __global__ void attn_combine_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ out,
                                     const int* __restrict__ token_seq, int out_row_stride, int nqh, int n_splits) {
+    pdl_trigger();
+    pdl_wait();
     const int row = blockIdx.x, head = blockIdx.y;
     if (token_seq[row] < 0) return;
     const float* p = partial + ((size_t)row * nqh + head) * n_splits * (HD + 2);
@@ -307,7 +311,7 @@ static int launch_attn(const AttnMmaArgs& a, int n_seqs, int max_q_len, cudaStre
     if (gx > 0x7fffffffLL || (long long)a.nkh * hchunks > 65535 || n_seqs > 65535)
         BRAID_REFUSE("attn_mma: the step exceeds the grid limits (%lld tiles, %d heads, %d sequences)", gx, a.nkh * hchunks, n_seqs);
     dim3 grid((unsigned)gx, a.nkh * hchunks, n_seqs);
-    attn_mma_kernel<BRAID_HD, NW, BN, ST><<<grid, NW * 32, C::SMEM, s>>>(a);
+    braid_launch(attn_mma_kernel<BRAID_HD, NW, BN, ST>, dim3(grid), dim3(NW * 32), C::SMEM, s, a);
     BRAID_LAUNCH_CHECK();
 }
 
@@ -341,7 +345,7 @@ extern "C" int braid_attn_mma(const void* q, void* out, void* partial, const voi
     if (rc) return rc;
     if (n_splits > 1) {
         dim3 grid(rows, nqh);
-        attn_combine_kernel<BRAID_HD><<<grid, BRAID_HD >= 128 ? 128 : 32, 0, s>>>((const float*)partial, (__nv_bfloat16*)out, token_seq, out_row_stride, nqh, n_splits);
+        braid_launch(attn_combine_kernel<BRAID_HD>, grid, dim3(BRAID_HD >= 128 ? 128 : 32), 0, s, (const float*)partial, (__nv_bfloat16*)out, token_seq, out_row_stride, nqh, n_splits);
         BRAID_LAUNCH_CHECK();
     }
     return BRAID_OK;

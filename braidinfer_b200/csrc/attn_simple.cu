@@ -30,6 +30,8 @@ struct AttnSimpleArgs {
 template <typename T>
 __global__ void __launch_bounds__(ATTN_SIMPLE_WARPS * 32)
 attn_simple_kernel(AttnSimpleArgs a) {
+    pdl_trigger();
+    pdl_wait();
     extern __shared__ float smem[];                  // [warps][hd] queries, [warps][32] probabilities
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     float* qs = smem + warp * a.hd;
@@ -115,8 +117,8 @@ extern "C" int braid_attn_simple(const void* q, void* out, int dtype, const void
     if (blocks > 0x7fffffffLL) BRAID_REFUSE("attn_simple: %lld (token, head) pairs exceed one launch", items);
     const size_t smem = (size_t)ATTN_SIMPLE_WARPS * (hd + 32) * sizeof(float);
     cudaStream_t s = (cudaStream_t)stream;
-    if (dtype == BRAID_F32) attn_simple_kernel<float><<<(int)blocks, ATTN_SIMPLE_WARPS * 32, smem, s>>>(a);
-    else if (dtype == BRAID_BF16) attn_simple_kernel<__nv_bfloat16><<<(int)blocks, ATTN_SIMPLE_WARPS * 32, smem, s>>>(a);
+    if (dtype == BRAID_F32) braid_launch(attn_simple_kernel<float>, dim3((int)blocks), dim3(ATTN_SIMPLE_WARPS * 32), smem, s, a);
+    else if (dtype == BRAID_BF16) braid_launch(attn_simple_kernel<__nv_bfloat16>, dim3((int)blocks), dim3(ATTN_SIMPLE_WARPS * 32), smem, s, a);
     else BRAID_REFUSE("attn_simple: unknown dtype code %d", dtype);
     BRAID_LAUNCH_CHECK();
 }

@@ -42,6 +42,34 @@ void braid_set_error(const char* fmt, ...);
         return BRAID_OK;                             \
     } while (0)
 
+// Programmatic dependent launch.  Every kernel of the library is launched with the
+// attribute that lets it begin while its predecessor in the stream drains, calls
+// pdl_trigger() at its top (so that its own successor may be scheduled early) and
+// pdl_wait() before its first access to memory that an earlier kernel may have written
+// (or may still read).  What comes before pdl_wait() must touch only weights and the
+// kernel's own shared or tensor memory.  BRAIDINFER_PDL=0 in the environment turns the
+// attribute off; the two instructions are then no-ops.
+int braid_pdl_enabled(void);
+
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t braid_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                       cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = braid_pdl_enabled();
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 __device__ __forceinline__ float to_f32(float v) { return v; }
 __device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
 

@@ -16,6 +16,8 @@
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids,
                              float* __restrict__ out, int n_tokens, int hidden, int vocab) {
+    pdl_trigger();
+    pdl_wait();
     const int t = blockIdx.x;
     if (t >= n_tokens) return;
     int id = ids[t];
@@ -32,9 +34,9 @@ extern "C" int braid_embed(const void* table, int table_dtype, const int* ids, f
     cudaStream_t s = (cudaStream_t)stream;
     const int threads = hidden >= 1024 ? 256 : 128;
     if (table_dtype == BRAID_F32)
-        embed_kernel<float><<<n_tokens, threads, 0, s>>>((const float*)table, ids, out, n_tokens, hidden, vocab);
+        braid_launch(embed_kernel<float>, dim3(n_tokens), dim3(threads), 0, s, (const float*)table, ids, out, n_tokens, hidden, vocab);
     else if (table_dtype == BRAID_BF16)
-        embed_kernel<__nv_bfloat16><<<n_tokens, threads, 0, s>>>((const __nv_bfloat16*)table, ids, out, n_tokens, hidden, vocab);
+        braid_launch(embed_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), 0, s, (const __nv_bfloat16*)table, ids, out, n_tokens, hidden, vocab);
     else
         BRAID_REFUSE("embed: unknown table dtype code %d", table_dtype);
     BRAID_LAUNCH_CHECK();
@@ -46,6 +48,8 @@ extern "C" int braid_embed(const void* table, int table_dtype, const int* ids, f
 template <typename TW, typename TO>
 __global__ void rmsnorm_kernel(const float* __restrict__ x, const TW* __restrict__ w, TO* __restrict__ out,
                                const int* __restrict__ row_index, int rows, int width, float eps) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ float red[32];
     const int r = blockIdx.x;
     if (r >= rows) return;
@@ -72,7 +76,7 @@ extern "C" int braid_rmsnorm(const float* x, const void* w, int w_dtype, void* o
     if (width <= 0) BRAID_REFUSE("rmsnorm: width=%d must be positive", width);
     cudaStream_t s = (cudaStream_t)stream;
     const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
-#define BRAID_RMS(TW, TO) rmsnorm_kernel<TW, TO><<<rows, threads, 0, s>>>(x, (const TW*)w, (TO*)out, row_index, rows, width, eps)
+#define BRAID_RMS(TW, TO) braid_launch(rmsnorm_kernel<TW, TO>, dim3(rows), dim3(threads), 0, s, x, (const TW*)w, (TO*)out, row_index, rows, width, eps)
     if (w_dtype == BRAID_F32 && out_dtype == BRAID_F32) BRAID_RMS(float, float);
     else if (w_dtype == BRAID_F32 && out_dtype == BRAID_BF16) BRAID_RMS(float, __nv_bfloat16);
     else if (w_dtype == BRAID_BF16 && out_dtype == BRAID_F32) BRAID_RMS(__nv_bfloat16, float);
@@ -86,6 +90,8 @@ extern "C" int braid_rmsnorm(const float* x, const void* w, int w_dtype, void* o
 // gu is [rows, 2*inter]: gate in columns [0, inter), up in [inter, 2*inter).
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, long long total, int inter) {
+    pdl_trigger();
+    pdl_wait();
     long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total) return;
     const long long r = i / inter;
@@ -103,8 +109,8 @@ extern "C" int braid_silu_mul(const void* gu, void* out, int dtype, int rows, in
     const long long blocks = (total + threads - 1) / threads;
     if (blocks > 0x7fffffffLL) BRAID_REFUSE("silu_mul: %lld elements exceed one launch", total);
     cudaStream_t s = (cudaStream_t)stream;
-    if (dtype == BRAID_F32) silu_mul_kernel<float><<<(int)blocks, threads, 0, s>>>((const float*)gu, (float*)out, total, inter);
-    else if (dtype == BRAID_BF16) silu_mul_kernel<__nv_bfloat16><<<(int)blocks, threads, 0, s>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, total, inter);
+    if (dtype == BRAID_F32) braid_launch(silu_mul_kernel<float>, dim3((int)blocks), dim3(threads), 0, s, (const float*)gu, (float*)out, total, inter);
+    else if (dtype == BRAID_BF16) braid_launch(silu_mul_kernel<__nv_bfloat16>, dim3((int)blocks), dim3(threads), 0, s, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, total, inter);
     else BRAID_REFUSE("silu_mul: unknown dtype code %d", dtype);
     BRAID_LAUNCH_CHECK();
 }
@@ -112,6 +118,8 @@ extern "C" int braid_silu_mul(const void* gu, void* out, int dtype, int rows, in
 // ------------------------------------------------------------------ residual add
 template <typename T>
 __global__ void residual_add_kernel(float* __restrict__ h, const T* __restrict__ delta, long long total) {
+    pdl_trigger();
+    pdl_wait();
     long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < total) h[i] = h[i] + to_f32(delta[i]);
 }
@@ -122,8 +130,8 @@ extern "C" int braid_residual_add(float* h, const void* delta, int delta_dtype, 
     const long long blocks = (total + threads - 1) / threads;
     if (blocks > 0x7fffffffLL) BRAID_REFUSE("residual_add: %lld elements exceed one launch", total);
     cudaStream_t s = (cudaStream_t)stream;
-    if (delta_dtype == BRAID_F32) residual_add_kernel<float><<<(int)blocks, threads, 0, s>>>(h, (const float*)delta, total);
-    else if (delta_dtype == BRAID_BF16) residual_add_kernel<__nv_bfloat16><<<(int)blocks, threads, 0, s>>>(h, (const __nv_bfloat16*)delta, total);
+    if (delta_dtype == BRAID_F32) braid_launch(residual_add_kernel<float>, dim3((int)blocks), dim3(threads), 0, s, h, (const float*)delta, total);
+    else if (delta_dtype == BRAID_BF16) braid_launch(residual_add_kernel<__nv_bfloat16>, dim3((int)blocks), dim3(threads), 0, s, h, (const __nv_bfloat16*)delta, total);
     else BRAID_REFUSE("residual_add: unknown dtype code %d", delta_dtype);
     BRAID_LAUNCH_CHECK();
 }
@@ -147,6 +155,8 @@ struct RopeKvArgs {
 
 template <typename T>
 __global__ void rope_kv_kernel(RopeKvArgs a) {
+    pdl_trigger();
+    pdl_wait();
     const int row = blockIdx.x;
     const int seq = a.token_seq[row];
     if (seq < 0) return;
@@ -204,8 +214,8 @@ extern "C" int braid_rope_kv_write(void* qkv, int dtype, const float* inv_freq, 
     dim3 grid(rows, nqh + 2 * nkh);
     const int threads = hd >= 128 ? 64 : 32;
     cudaStream_t s = (cudaStream_t)stream;
-    if (dtype == BRAID_F32) rope_kv_kernel<float><<<grid, threads, 0, s>>>(a);
-    else if (dtype == BRAID_BF16) rope_kv_kernel<__nv_bfloat16><<<grid, threads, 0, s>>>(a);
+    if (dtype == BRAID_F32) braid_launch(rope_kv_kernel<float>, dim3(grid), dim3(threads), 0, s, a);
+    else if (dtype == BRAID_BF16) braid_launch(rope_kv_kernel<__nv_bfloat16>, dim3(grid), dim3(threads), 0, s, a);
     else BRAID_REFUSE("rope_kv_write: unknown dtype code %d", dtype);
     BRAID_LAUNCH_CHECK();
 }
@@ -213,6 +223,8 @@ extern "C" int braid_rope_kv_write(void* qkv, int dtype, const float* inv_freq, 
 // ------------------------------------------------------------------ casts
 template <typename TI, typename TO>
 __global__ void cast_kernel(const TI* __restrict__ in, TO* __restrict__ out, long long total) {
+    pdl_trigger();
+    pdl_wait();
     long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < total) out[i] = from_f32<TO>(to_f32(in[i]));
 }
@@ -223,8 +235,8 @@ extern "C" int braid_cast(const void* in, int in_dtype, void* out, int out_dtype
     const long long blocks = (total + threads - 1) / threads;
     if (blocks > 0x7fffffffLL) BRAID_REFUSE("cast: %lld elements exceed one launch", total);
     cudaStream_t s = (cudaStream_t)stream;
-    if (in_dtype == BRAID_F32 && out_dtype == BRAID_BF16) cast_kernel<float, __nv_bfloat16><<<(int)blocks, threads, 0, s>>>((const float*)in, (__nv_bfloat16*)out, total);
-    else if (in_dtype == BRAID_BF16 && out_dtype == BRAID_F32) cast_kernel<__nv_bfloat16, float><<<(int)blocks, threads, 0, s>>>((const __nv_bfloat16*)in, (float*)out, total);
+    if (in_dtype == BRAID_F32 && out_dtype == BRAID_BF16) braid_launch(cast_kernel<float, __nv_bfloat16>, dim3((int)blocks), dim3(threads), 0, s, (const float*)in, (__nv_bfloat16*)out, total);
+    else if (in_dtype == BRAID_BF16 && out_dtype == BRAID_F32) braid_launch(cast_kernel<__nv_bfloat16, float>, dim3((int)blocks), dim3(threads), 0, s, (const __nv_bfloat16*)in, (float*)out, total);
     else BRAID_REFUSE("cast: unsupported dtype codes %d -> %d", in_dtype, out_dtype);
     BRAID_LAUNCH_CHECK();
 }

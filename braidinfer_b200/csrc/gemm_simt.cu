@@ -20,6 +20,8 @@ __global__ void __launch_bounds__(256)
 gemm_simt_kernel(const T* __restrict__ x, const T* __restrict__ w, TO* __restrict__ out,
                  const float* __restrict__ res, int n_rows, int m_out, int k_in,
                  long long ldx, long long ldw, long long ldo) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ float xs[SG_BK][SG_BN + 4];
     __shared__ float ws[SG_BK][SG_BM + 4];
     const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;     // tx: outputs, ty: tokens
@@ -81,7 +83,7 @@ extern "C" int braid_gemm_simt(const void* x, const void* w, void* out, const fl
     dim3 grid((m_out + SG_BM - 1) / SG_BM, (n_rows + SG_BN - 1) / SG_BN);
     if (grid.y > 65535) BRAID_REFUSE("gemm_simt: %d rows exceed the grid limit", n_rows);
     cudaStream_t s = (cudaStream_t)stream;
-#define SG_LAUNCH(T, TO, MODE) gemm_simt_kernel<T, TO, MODE><<<grid, 256, 0, s>>>((const T*)x, (const T*)w, (TO*)out, res, n_rows, m_out, k_in, ldx, ldw, ldo)
+#define SG_LAUNCH(T, TO, MODE) braid_launch(gemm_simt_kernel<T, TO, MODE>, dim3(grid), dim3(256), 0, s, (const T*)x, (const T*)w, (TO*)out, res, n_rows, m_out, k_in, ldx, ldw, ldo)
     if (in_dtype == BRAID_F32 && out_dtype == BRAID_F32) { if (mode) SG_LAUNCH(float, float, 1); else SG_LAUNCH(float, float, 0); }
     else if (in_dtype == BRAID_BF16 && out_dtype == BRAID_F32) { if (mode) SG_LAUNCH(__nv_bfloat16, float, 1); else SG_LAUNCH(__nv_bfloat16, float, 0); }
     else if (in_dtype == BRAID_BF16 && out_dtype == BRAID_BF16) SG_LAUNCH(__nv_bfloat16, __nv_bfloat16, 0);

@@ -18,8 +18,8 @@
 //                 1  float32 residual sum: out = res + product,
 //                 2  SwiGLU: w holds gate rows [0, I) and up rows [I, 2I); two
 //                    accumulators share the token tile; out = silu(gate) * up,
-//                 3  float32 partial sums of one slice of k (split-k), reduced by
-//                    braid_gemm_splitk_reduce with one of the epilogues above.
+//                 3  float32 partial sums of a run of k blocks ("stream-k"), added up
+//                    by a reduce kernel with one of the epilogues above.
 //
 // The kernel is persistent: one CTA per SM walks its share of the work units (output tile
 // x slice of k).  The loader runs ahead across units, and with two accumulator buffers
@@ -114,13 +114,13 @@ __host__ __device__ constexpr uint32_t umma_idesc_bf16(int m, int n) {
 }
 
 struct GemmTcArgs {
-    void* out;                 // mode 0: [n, ldo] bf16/f32; 1: f32; 2: bf16/f32 [n, ldo]; 3: f32 [splits][n_rows][m_out]
+    void* out;                 // mode 0: [n, ldo] bf16/f32; 1: f32; 2: bf16/f32 [n, ldo]; 3: f32 [slot][n_rows][128]
     const float* res;          // mode 1
     int n_rows, m_out, k_in;   // mode 2: m_out is the number of gate rows (w has 2 * m_out rows)
     long long ldo;
     int out_dtype;
-    int kb_per_split;          // 64-wide k blocks handled by one slice of k
-    int m_tiles, n_tiles, splits;
+    int m_tiles, n_tiles;
+    int max_segs;              // mode 3: partial slots per CTA
     int* error_flag;
 };
 
@@ -143,23 +143,62 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
-// A persistent CTA walks work units u = blockIdx.x, blockIdx.x + gridDim.x, ...; a unit is
-// one [128 x BLOCK_N] output tile for one slice of k.  Token tiles vary fastest so that
-// CTAs running side by side share weight tiles in L2.
-struct TcUnit { int m0, n0, split, kb_begin, num_kb; };
-__device__ __forceinline__ TcUnit tc_unit(const GemmTcArgs& a, int u, int block_n) {
-    TcUnit t;
-    const int nt = u % a.n_tiles;
-    const int rest = u / a.n_tiles;
-    const int mt = rest % a.m_tiles;
-    t.split = rest / a.m_tiles;
-    t.m0 = mt * TC_BLOCK_M;
-    t.n0 = nt * block_n;
-    const int total_kb = (a.k_in + TC_BLOCK_K - 1) / TC_BLOCK_K;
-    t.kb_begin = t.split * a.kb_per_split;
-    t.num_kb = max(0, min(total_kb, t.kb_begin + a.kb_per_split) - t.kb_begin);
-    return t;
-}
+// Work of a persistent CTA.
+//
+// Modes 0-2: units u = blockIdx.x, blockIdx.x + gridDim.x, ...; a unit is one whole
+// [128 x BLOCK_N] output tile.  Token tiles vary fastest so that CTAs running side by
+// side share weight tiles in L2.
+//
+// Mode 3 ("stream-k", for a few tokens, where the product only streams weights): the
+// k blocks of all tiles form one line of m_tiles * n_tiles * total_kb blocks, cut into
+// gridDim.x equal ranges.  A CTA's range is a run of segments (tile, first k block,
+// count); it writes the float32 partial product of its j-th segment to slot
+// blockIdx.x * max_segs + j, and braid_gemm_tc's reduce kernel adds the slots of a tile
+// in ascending CTA order.  Every CTA streams the same number of bytes whatever the shape.
+struct TcUnit { int m0, n0, slot, kb_begin, num_kb; };
+
+template <int BLOCK_N, int MODE>
+struct TcWalk {
+    const GemmTcArgs& a;
+    int total_kb;
+    long long idx, hi;       // mode 3: position in the line of k blocks
+    int u, seg;
+    __device__ TcWalk(const GemmTcArgs& a_) : a(a_) {
+        total_kb = (a.k_in + TC_BLOCK_K - 1) / TC_BLOCK_K;
+        if (MODE == 3) {
+            const long long w = (long long)a.m_tiles * a.n_tiles * total_kb;
+            idx = (long long)blockIdx.x * w / gridDim.x;
+            hi = (long long)(blockIdx.x + 1) * w / gridDim.x;
+        } else {
+            idx = hi = 0;
+        }
+        u = blockIdx.x;
+        seg = 0;
+    }
+    __device__ bool next(TcUnit& t) {
+        int tile;
+        if (MODE == 3) {
+            if (idx >= hi) return false;
+            tile = (int)(idx / total_kb);
+            t.kb_begin = (int)(idx - (long long)tile * total_kb);
+            t.num_kb = (int)min((long long)(total_kb - t.kb_begin), hi - idx);
+            t.slot = blockIdx.x * a.max_segs + seg;
+            idx += t.num_kb;
+            ++seg;
+        } else {
+            if (u >= a.m_tiles * a.n_tiles) return false;
+            tile = u;
+            t.kb_begin = 0;
+            t.num_kb = total_kb;
+            t.slot = 0;
+            u += gridDim.x;
+        }
+        const int nt = tile % a.n_tiles;
+        t.m0 = (tile / a.n_tiles) * TC_BLOCK_M;
+        t.n0 = nt * BLOCK_N;
+        return true;
+    }
+};
 
 template <int BLOCK_N, int MODE>
 __global__ void __launch_bounds__(TC_THREADS, 1)
@@ -176,7 +215,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int num_units = a.m_tiles * a.n_tiles * a.splits;
+    pdl_trigger();
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < Cfg::kStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
@@ -196,17 +235,38 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
-            for (int u = blockIdx.x; u < num_units && ok; u += gridDim.x) {
-                const TcUnit t = tc_unit(a, u, BLOCK_N);
-                for (int i = 0; i < t.num_kb; ++i) {
-                    ok = mbar_wait(&empty[stage], phase ^ 1u, abort_flag);
-                    if (!ok) break;
+            // Weights are written by no kernel, so the first ring of weight tiles is on its
+            // way before the predecessor in the stream has finished; the token tiles of the
+            // same stages follow once it has.
+            {
+                TcWalk<BLOCK_N, MODE> pre(a);
+                TcUnit t;
+                int n = 0;
+                while (n < Cfg::kStages && pre.next(t))
+                    for (int i = 0; i < t.num_kb && n < Cfg::kStages; ++i, ++n) {
+                        uint8_t* sa = smem + n * Cfg::kStageBytes;
+                        mbar_expect_tx(&full[n], Cfg::kStageBytes);
+                        const int kx = (t.kb_begin + i) * TC_BLOCK_K;
+                        tma_load_2d(&map_w, &full[n], sa, kx, t.m0);
+                        if (MODE == 2) tma_load_2d(&map_w, &full[n], sa + TC_BLOCK_M * TC_BLOCK_K * 2, kx, a.m_out + t.m0);
+                    }
+            }
+            pdl_wait();
+            TcWalk<BLOCK_N, MODE> walk(a);
+            TcUnit t;
+            int issued = 0;                       // k blocks whose weight tile is already in flight
+            while (ok && walk.next(t)) {
+                for (int i = 0; i < t.num_kb; ++i, ++issued) {
                     uint8_t* sa = smem + stage * Cfg::kStageBytes;
                     uint8_t* sb = sa + Cfg::kABytes;
-                    mbar_expect_tx(&full[stage], Cfg::kStageBytes);
                     const int kx = (t.kb_begin + i) * TC_BLOCK_K;
-                    tma_load_2d(&map_w, &full[stage], sa, kx, t.m0);
-                    if (MODE == 2) tma_load_2d(&map_w, &full[stage], sa + TC_BLOCK_M * TC_BLOCK_K * 2, kx, a.m_out + t.m0);
+                    if (issued >= Cfg::kStages) {
+                        ok = mbar_wait(&empty[stage], phase ^ 1u, abort_flag);
+                        if (!ok) break;
+                        mbar_expect_tx(&full[stage], Cfg::kStageBytes);
+                        tma_load_2d(&map_w, &full[stage], sa, kx, t.m0);
+                        if (MODE == 2) tma_load_2d(&map_w, &full[stage], sa + TC_BLOCK_M * TC_BLOCK_K * 2, kx, a.m_out + t.m0);
+                    }
                     tma_load_2d(&map_x, &full[stage], sb, kx, t.n0);
                     if (++stage == Cfg::kStages) { stage = 0; phase ^= 1u; }
                 }
@@ -218,8 +278,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             int stage = 0, buf = 0;
             uint32_t phase = 0, acc_phase = 0;      // bit b: phase of accumulator buffer b
             bool ok = true;
-            for (int u = blockIdx.x; u < num_units && ok; u += gridDim.x) {
-                const TcUnit t = tc_unit(a, u, BLOCK_N);
+            TcWalk<BLOCK_N, MODE> walk(a);
+            TcUnit t;
+            while (ok && walk.next(t)) {
                 ok = mbar_wait(&acc_empty[buf], ((acc_phase >> buf) & 1u) ^ 1u, abort_flag);   // the epilogue has drained this buffer
                 if (!ok) break;
                 tc_fence_after();
@@ -251,11 +312,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     } else {
         // epilogue warps: warp w may read tensor-memory lanes 32 * (w % 4) ...
         const int quarter = warp & 3;
+        pdl_wait();
         int buf = 0;
         uint32_t full_phase = 0;                  // bit b: phase of accumulator buffer b
         bool ok = true;
-        for (int u = blockIdx.x; u < num_units && ok; u += gridDim.x) {
-            const TcUnit t = tc_unit(a, u, BLOCK_N);
+        TcWalk<BLOCK_N, MODE> walk(a);
+        TcUnit t;
+        while (ok && walk.next(t)) {
             const int m = t.m0 + quarter * 32 + lane;
             ok = mbar_wait(&acc_full[buf], (full_phase >> buf) & 1u, abort_flag);
             if (!ok) break;
@@ -274,10 +337,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 }
                 if (m < a.m_out) {
                     if (MODE == 3) {
-                        float* dst = (float*)a.out + ((size_t)t.split * a.n_rows + t.n0 + c0) * a.m_out + m;
+                        // slot layout [n_rows][128]: this thread's output feature is column quarter * 32 + lane
+                        float* dst = (float*)a.out + ((size_t)t.slot * a.n_rows + t.n0 + c0) * TC_BLOCK_M + quarter * 32 + lane;
 #pragma unroll
                         for (int i = 0; i < 16; ++i)
-                            if (t.n0 + c0 + i < a.n_rows) dst[(size_t)i * a.m_out] = v[i];
+                            if (t.n0 + c0 + i < a.n_rows) dst[(size_t)i * TC_BLOCK_M] = v[i];
                     } else if (MODE == 1) {
                         // all loads of the residual first: out may be res itself, which would
                         // otherwise chain every load behind the store before it
@@ -314,22 +378,44 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     }
 }
 
-// ------------------------------------------------------------------ split-k reduce
-// partial: [splits][n_rows][m_cols] float32.  mode 0: store; 1: res + sum (float32);
-// 2: columns [0, I) are gate and [I, 2I) are up, out[n, I] = silu(gate) * up.
-template <int MODE>
-__global__ void splitk_reduce_kernel(const float* __restrict__ partial, void* __restrict__ out,
-                                     const float* __restrict__ res, int splits, int n_rows, int m_cols,
-                                     int m_out, long long ldo, int out_dtype) {
-    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= (long long)n_rows * m_out) return;
-    const int n = (int)(i / m_out), m = (int)(i - (long long)n * m_out);
-    const size_t plane = (size_t)n_rows * m_cols;
+// ------------------------------------------------------------------ stream-k reduce
+// Sum of the partial slots that cover output (n, column) of the [n_rows, w_rows] product.
+struct StreamK {
+    const float* partial;
+    int grid, max_segs, total_kb, n_tiles, n_rows, block_n;
+    long long w;               // m_tiles * n_tiles * total_kb
+};
+
+__device__ __forceinline__ float streamk_sum(const StreamK& k, int n, int col) {
+    const int tile = (col / TC_BLOCK_M) * k.n_tiles + n / k.block_n;
+    const long long x0 = (long long)tile * k.total_kb, x1 = x0 + k.total_kb;
+    int c = (int)(x0 * k.grid / k.w);
+    while (c + 1 < k.grid && (long long)(c + 1) * k.w / k.grid <= x0) ++c;
+    while (c > 0 && (long long)c * k.w / k.grid > x0) --c;
     float s = 0.f;
-    for (int k = 0; k < splits; ++k) s += partial[k * plane + (size_t)n * m_cols + m];
+    for (; c < k.grid; ++c) {
+        const long long lo = (long long)c * k.w / k.grid;
+        if (lo >= x1) break;
+        const int j = tile - (int)(lo / k.total_kb);
+        const size_t slot = (size_t)c * k.max_segs + j;
+        s += k.partial[(slot * k.n_rows + n) * TC_BLOCK_M + (col % TC_BLOCK_M)];
+    }
+    return s;
+}
+
+// mode 0: store; 1: res + sum (float32); 2: columns [0, I) are gate and [I, 2I) are up,
+// out[n, I] = silu(gate) * up.
+template <int MODE>
+__global__ void streamk_reduce_kernel(StreamK k, void* __restrict__ out, const float* __restrict__ res,
+                                      int m_out, long long ldo, int out_dtype) {
+    pdl_trigger();
+    pdl_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long long)k.n_rows * m_out) return;
+    const int n = (int)(i / m_out), m = (int)(i - (long long)n * m_out);
+    float s = streamk_sum(k, n, m);
     if (MODE == 2) {
-        float u = 0.f;
-        for (int k = 0; k < splits; ++k) u += partial[k * plane + (size_t)n * m_cols + m_out + m];
+        const float u = streamk_sum(k, n, m_out + m);
         s = s / (1.f + expf(-s)) * u;
     }
     const size_t o = (size_t)n * ldo + m;
@@ -389,7 +475,7 @@ static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const GemmTcA
         if (e != cudaSuccess) { braid_set_error("gemm_tc: cannot reserve %d bytes of shared memory: %s", Cfg::kSmemBytes, cudaGetErrorString(e)); return (int)e; }
         configured = true;
     }
-    gemm_tc_kernel<BLOCK_N, MODE><<<grid, TC_THREADS, Cfg::kSmemBytes, s>>>(mw, mx, a);
+    braid_launch(gemm_tc_kernel<BLOCK_N, MODE>, dim3(grid), dim3(TC_THREADS), Cfg::kSmemBytes, s, mw, mx, a);
     BRAID_LAUNCH_CHECK();
 }
 
@@ -405,17 +491,37 @@ static int dispatch_tc(int block_n, const CUtensorMap& mw, const CUtensorMap& mx
     BRAID_REFUSE("gemm_tc: token tile %d is not one of 16, 32, 64, 128, 256", block_n);
 }
 
-// Bytes of float32 scratch that `splits` > 1 needs.
-extern "C" long long braid_gemm_tc_workspace_bytes(int n_rows, int w_rows, int splits) {
-    return splits > 1 ? (long long)splits * n_rows * w_rows * 4 : 0;
+struct StreamKPlan { int grid, max_segs, total_kb, m_tiles, n_tiles; long long w, bytes; };
+
+static StreamKPlan plan_stream_k(int n_rows, int w_rows, int k_in, int block_n) {
+    StreamKPlan p;
+    p.total_kb = (k_in + TC_BLOCK_K - 1) / TC_BLOCK_K;
+    p.m_tiles = (w_rows + TC_BLOCK_M - 1) / TC_BLOCK_M;
+    p.n_tiles = (n_rows + block_n - 1) / block_n;
+    p.w = (long long)p.m_tiles * p.n_tiles * p.total_kb;
+    p.grid = (int)(p.w < sm_count() ? p.w : sm_count());
+    const long long per = (p.w + p.grid - 1) / p.grid;
+    p.max_segs = (int)((per + p.total_kb - 1) / p.total_kb) + 1;
+    p.bytes = (long long)p.grid * p.max_segs * n_rows * TC_BLOCK_M * 4;
+    return p;
+}
+
+static int pick_block_n(int n_rows) {
+    return n_rows <= 16 ? 16 : n_rows <= 32 ? 32 : n_rows <= 64 ? 64 : n_rows <= 128 ? 128 : 256;
+}
+
+// Bytes of float32 scratch that the stream-k form needs for this shape.
+extern "C" long long braid_gemm_tc_workspace_bytes(int n_rows, int w_rows, int k_in) {
+    return plan_stream_k(n_rows, w_rows, k_in, pick_block_n(n_rows)).bytes;
 }
 
 // x: [n_rows, k_in] bf16 (row stride ldx); w: [w_rows, k_in] bf16 (row stride ldw), where
-// w_rows = m_out, or 2 * m_out for the SwiGLU epilogue.  splits > 1 slices k and needs
+// w_rows = m_out, or 2 * m_out for the SwiGLU epilogue.  stream_k != 0 balances the
+// weight stream over all SMs for any shape (meant for a few tokens) and needs
 // `workspace`.  block_n = 0 picks the token tile.
 extern "C" int braid_gemm_tc(const void* x, const void* w, void* out, const float* res, void* workspace,
                              int out_dtype, int mode, int n_rows, int m_out, int k_in,
-                             long long ldx, long long ldw, long long ldo, int block_n, int splits,
+                             long long ldx, long long ldw, long long ldo, int block_n, int stream_k,
                              int* error_flag, void* stream) {
     if (n_rows <= 0 || m_out <= 0) return BRAID_OK;
     if (mode < 0 || mode > 2) BRAID_REFUSE("gemm_tc: unknown epilogue %d", mode);
@@ -426,13 +532,8 @@ extern "C" int braid_gemm_tc(const void* x, const void* w, void* out, const floa
     if (out_dtype != BRAID_F32 && out_dtype != BRAID_BF16) BRAID_REFUSE("gemm_tc: unknown out dtype code %d", out_dtype);
     if (!error_flag) BRAID_REFUSE("gemm_tc: error_flag is required");
     const int w_rows = (mode == 2) ? 2 * m_out : m_out;
-    if (block_n == 0) block_n = n_rows <= 16 ? 16 : n_rows <= 32 ? 32 : n_rows <= 64 ? 64 : n_rows <= 128 ? 128 : 256;
-    const int total_kb = (k_in + TC_BLOCK_K - 1) / TC_BLOCK_K;
-    if (splits < 1) splits = 1;
-    if (splits > total_kb) splits = total_kb;
-    if (splits > 1 && !workspace) BRAID_REFUSE("gemm_tc: split-k needs a workspace");
-    const int kb_per_split = (total_kb + splits - 1) / splits;
-    splits = (total_kb + kb_per_split - 1) / kb_per_split;
+    if (block_n == 0) block_n = stream_k ? pick_block_n(n_rows) : pick_block_n(n_rows);
+    if (stream_k && !workspace) BRAID_REFUSE("gemm_tc: the stream-k form needs a workspace");
     cudaStream_t s = (cudaStream_t)stream;
 
     CUtensorMap mw, mx;
@@ -440,30 +541,28 @@ extern "C" int braid_gemm_tc(const void* x, const void* w, void* out, const floa
     if (rc) return rc;
     rc = make_map(&mx, x, n_rows, k_in, ldx, block_n);
     if (rc) return rc;
-    const unsigned n_tiles = (n_rows + block_n - 1) / block_n;
 
-    if (splits == 1) {
+    if (!stream_k) {
         const int m_tiles = (m_out + TC_BLOCK_M - 1) / TC_BLOCK_M;
-        GemmTcArgs a{out, res, n_rows, m_out, k_in, ldo, out_dtype, kb_per_split, m_tiles, (int)n_tiles, 1, error_flag};
+        const int n_tiles = (n_rows + block_n - 1) / block_n;
+        GemmTcArgs a{out, res, n_rows, m_out, k_in, ldo, out_dtype, m_tiles, n_tiles, 0, error_flag};
         const long long units = (long long)m_tiles * n_tiles;
         dim3 grid((unsigned)(units < sm_count() ? units : sm_count()), 1, 1);
         if (mode == 0) return dispatch_tc<0>(block_n, mw, mx, a, grid, s);
         if (mode == 1) return dispatch_tc<1>(block_n, mw, mx, a, grid, s);
         return dispatch_tc<2>(block_n, mw, mx, a, grid, s);
     }
-    const int m_tiles = (w_rows + TC_BLOCK_M - 1) / TC_BLOCK_M;
-    GemmTcArgs a{workspace, nullptr, n_rows, w_rows, k_in, 0, BRAID_F32, kb_per_split, m_tiles, (int)n_tiles, splits, error_flag};
-    const long long units = (long long)m_tiles * n_tiles * splits;
-    dim3 grid((unsigned)(units < sm_count() ? units : sm_count()), 1, 1);
-    rc = dispatch_tc<3>(block_n, mw, mx, a, grid, s);
+    const StreamKPlan p = plan_stream_k(n_rows, w_rows, k_in, block_n);
+    GemmTcArgs a{workspace, nullptr, n_rows, w_rows, k_in, 0, BRAID_F32, p.m_tiles, p.n_tiles, p.max_segs, error_flag};
+    rc = dispatch_tc<3>(block_n, mw, mx, a, dim3(p.grid, 1, 1), s);
     if (rc) return rc;
     const long long total = (long long)n_rows * m_out;
     const int threads = 256;
     const long long blocks = (total + threads - 1) / threads;
     if (blocks > 0x7fffffffLL) BRAID_REFUSE("gemm_tc: %lld outputs exceed one reduce launch", total);
-    const float* p = (const float*)workspace;
-    if (mode == 0) splitk_reduce_kernel<0><<<(int)blocks, threads, 0, s>>>(p, out, res, splits, n_rows, w_rows, m_out, ldo, out_dtype);
-    else if (mode == 1) splitk_reduce_kernel<1><<<(int)blocks, threads, 0, s>>>(p, out, res, splits, n_rows, w_rows, m_out, ldo, out_dtype);
-    else splitk_reduce_kernel<2><<<(int)blocks, threads, 0, s>>>(p, out, res, splits, n_rows, w_rows, m_out, ldo, out_dtype);
+    StreamK k{(const float*)workspace, p.grid, p.max_segs, p.total_kb, p.n_tiles, n_rows, block_n, p.w};
+    if (mode == 0) braid_launch(streamk_reduce_kernel<0>, dim3((int)blocks), dim3(threads), 0, s, k, out, res, m_out, ldo, out_dtype);
+    else if (mode == 1) braid_launch(streamk_reduce_kernel<1>, dim3((int)blocks), dim3(threads), 0, s, k, out, res, m_out, ldo, out_dtype);
+    else braid_launch(streamk_reduce_kernel<2>, dim3((int)blocks), dim3(threads), 0, s, k, out, res, m_out, ldo, out_dtype);
     BRAID_LAUNCH_CHECK();
 }

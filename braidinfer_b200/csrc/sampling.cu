@@ -108,6 +108,8 @@ __device__ int block_argmax(const float* x, int n, float* shf, int* shi, int* na
 
 __global__ void __launch_bounds__(SAMP_THREADS)
 argmax_kernel(const float* __restrict__ logits, long long ld, int* __restrict__ out, int vocab, int* nan_flag) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ float shf[32];
     __shared__ int shi[32];
     const int r = block_argmax(logits + (size_t)blockIdx.x * ld, vocab, shf, shi, nan_flag);
@@ -118,7 +120,7 @@ extern "C" int braid_argmax(const float* logits, long long ld, int* out, int row
                             int* nan_flag, void* stream) {
     if (rows <= 0) return BRAID_OK;
     if (vocab <= 0) BRAID_REFUSE("argmax: vocab=%d must be positive", vocab);
-    argmax_kernel<<<rows, SAMP_THREADS, 0, (cudaStream_t)stream>>>(logits, ld, out, vocab, nan_flag);
+    braid_launch(argmax_kernel, dim3(rows), dim3(SAMP_THREADS), 0, (cudaStream_t)stream, logits, ld, out, vocab, nan_flag);
     BRAID_LAUNCH_CHECK();
 }
 
@@ -167,6 +169,8 @@ __device__ void apply_cut(float* x, int n, unsigned int cut, int keep_equal, int
 
 __global__ void __launch_bounds__(SAMP_THREADS)
 sample_kernel(SampleArgs a) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ float shf[32];
     __shared__ int shi[32];
     __shared__ int found;
@@ -311,6 +315,6 @@ extern "C" int braid_sample(const float* logits, float* work, long long ld, int*
     if (!temperature || !uniform) BRAID_REFUSE("sample: temperature and uniform arrays are required");
     SampleArgs a{logits, work, ld, out, vocab, temperature, top_k, top_p, min_p, rep_penalty, uniform,
                  hist_off, hist_tok, hist_cnt, bias_off, bias_tok, bias_val, nan_flag};
-    sample_kernel<<<rows, SAMP_THREADS, 0, (cudaStream_t)stream>>>(a);
+    braid_launch(sample_kernel, dim3(rows), dim3(SAMP_THREADS), 0, (cudaStream_t)stream, a);
     BRAID_LAUNCH_CHECK();
 }

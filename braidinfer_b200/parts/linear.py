@@ -13,10 +13,9 @@ import torch
 
 from .spec import TensorSpec
 
-# Launch shaping for few tokens: aim for about this many CTAs so that weight
-# streaming fills the machine, but keep at least this many 64-wide k blocks a slice.
-_TARGET_CTAS = 148 * 2
-_MIN_KB_PER_SPLIT = 4
+# Up to this many tokens a product only streams its weights: it is spread evenly over
+# all SMs along k as well as along the output ("stream-k").
+_STREAM_K_MAX_ROWS = 64
 
 
 class Linear:
@@ -44,14 +43,6 @@ class Linear:
     def total_out(self) -> int:
         return sum(self.out_features)
 
-    def _splits(self, rows: int, w_rows: int, k: int, swiglu: bool) -> int:
-        if rows > 64:
-            return 1
-        tiles = (w_rows // (2 if swiglu else 1) + 127) // 128
-        total_kb = (k + 63) // 64
-        want = max(1, _TARGET_CTAS // max(1, tiles))
-        return max(1, min(want, total_kb // _MIN_KB_PER_SPLIT))
-
     def forward(self, x: torch.Tensor, *, out_dtype: Optional[torch.dtype] = None,
                 residual: Optional[torch.Tensor] = None, swiglu: bool = False) -> torch.Tensor:
         """x [rows, in].  Plain: returns [rows, out] in `out_dtype` (default x's type).
@@ -78,7 +69,7 @@ class Linear:
         use_tc = (self.rt.gemm_backend == "auto" and x.dtype == torch.bfloat16 and K.gemm_tc_eligible(x, w))
         if residual is not None:
             if use_tc:
-                K.gemm_tc(x, w, residual, residual=residual, splits=self._splits(rows, w_rows, x.shape[1], False))
+                K.gemm_tc(x, w, residual, residual=residual, stream_k=rows <= _STREAM_K_MAX_ROWS)
             else:
                 K.gemm_simt(x, w, residual, residual=residual)
             return residual
@@ -86,7 +77,7 @@ class Linear:
             inter = w_rows // 2
             out = torch.empty((rows, inter), dtype=out_dtype or x.dtype, device=x.device)
             if use_tc:
-                K.gemm_tc(x, w, out, swiglu=True, splits=self._splits(rows, w_rows, x.shape[1], True))
+                K.gemm_tc(x, w, out, swiglu=True, stream_k=rows <= _STREAM_K_MAX_ROWS)
             else:
                 gu = torch.empty((rows, w_rows), dtype=x.dtype, device=x.device)
                 K.gemm_simt(x, w, gu)
@@ -94,7 +85,7 @@ class Linear:
             return out
         out = torch.empty((rows, w_rows), dtype=out_dtype or x.dtype, device=x.device)
         if use_tc:
-            K.gemm_tc(x, w, out, splits=self._splits(rows, w_rows, x.shape[1], False))
+            K.gemm_tc(x, w, out, stream_k=rows <= _STREAM_K_MAX_ROWS)
         else:
             K.gemm_simt(x, w, out)
         return out

@@ -255,38 +255,40 @@ def test_plain_matrix_product(K, dtype, n, m, k):
     assert (res.double() - want).abs().max() < 1e-4 * max(1.0, ref.abs().max().item())
 
 
-@pytest.mark.parametrize("n, m, k, splits", [
-    (16, 128, 64, 1), (33, 200, 96, 1), (1, 331, 120, 1), (300, 1000, 520, 1), (700, 384, 1024, 1),
-    (2048, 512, 256, 1), (8, 512, 4096, 4), (20, 256, 2048, 3), (64, 1408, 1024, 5), (3, 200, 8200, 7)])
-def test_tensor_core_matrix_product(K, n, m, k, splits):
+@pytest.mark.parametrize("n, m, k, sk", [
+    (16, 128, 64, False), (33, 200, 96, False), (1, 331, 120, False), (300, 1000, 520, False),
+    (700, 384, 1024, False), (2048, 512, 256, False), (8, 512, 4096, True), (20, 256, 2048, True),
+    (64, 1408, 1024, True), (3, 200, 8200, True), (1, 128, 64, True), (40, 20000, 320, True), (300, 640, 2048, True)])
+def test_tensor_core_matrix_product(K, n, m, k, sk):
     x, w = rnd(n, k, dtype=torch.bfloat16, scale=0.5), rnd(m, k, dtype=torch.bfloat16, scale=0.5, seed=1)
     ref = x.double() @ w.double().t()
     scale = max(1.0, ref.abs().max().item())
     out = torch.full((n, m), 9.0, device=DEV)
-    K.gemm_tc(x, w, out, splits=splits)
+    K.gemm_tc(x, w, out, stream_k=sk)
     assert (out.double() - ref).abs().max() < 1e-5 * scale
     plain = torch.empty(n, m, device=DEV)
     K.gemm_simt(x, w, plain)
     assert (out - plain).abs().max() < 1e-5 * scale                  # beside its plain twin
     outb = torch.full((n, m), 9.0, device=DEV, dtype=torch.bfloat16)
-    K.gemm_tc(x, w, outb, splits=splits)
+    K.gemm_tc(x, w, outb, stream_k=sk)
     assert (outb.double() - ref).abs().max() < scale / 128
     res = rnd(n, m, seed=2)
     want = res.double() + ref
-    K.gemm_tc(x, w, res, residual=res, splits=splits)
+    K.gemm_tc(x, w, res, residual=res, stream_k=sk)
     assert (res.double() - want).abs().max() < 1e-5 * scale
     K.check_device_errors()
 
 
-@pytest.mark.parametrize("n, inter, k, splits", [(300, 384, 512, 1), (17, 200, 96, 1), (20, 256, 2048, 3), (64, 1000, 520, 2)])
-def test_tensor_core_swiglu_epilogue(K, n, inter, k, splits):
+@pytest.mark.parametrize("n, inter, k, sk", [(300, 384, 512, False), (17, 200, 96, False), (20, 256, 2048, True),
+                                             (64, 1000, 520, True), (8, 14336, 512, True)])
+def test_tensor_core_swiglu_epilogue(K, n, inter, k, sk):
     x = rnd(n, k, dtype=torch.bfloat16, scale=0.5)
     w = rnd(2 * inter, k, dtype=torch.bfloat16, scale=0.2, seed=1)
     ref = x.double() @ w.double().t()
     g, u = ref[:, :inter], ref[:, inter:]
     want = g / (1 + torch.exp(-g)) * u
     out = torch.full((n, inter), 9.0, device=DEV, dtype=torch.bfloat16)
-    K.gemm_tc(x, w, out, swiglu=True, splits=splits)
+    K.gemm_tc(x, w, out, swiglu=True, stream_k=sk)
     assert ((out.double() - want).abs() <= want.abs() / 100 + 1e-3).all()
 
 
