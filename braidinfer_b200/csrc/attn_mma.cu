@@ -350,3 +350,47 @@ extern "C" int braid_attn_mma(const void* q, void* out, void* partial, const voi
     }
     return BRAID_OK;
 }
+
+// ------------------------------------------------------------------ no-allocation entry point
+// See attn_noalloc.h for who needs this and what it costs.
+#include "attn_noalloc.h"
+
+// The scratch itself.  In host code this name is only a handle for the runtime: its
+// device address has to be asked for (below) before a kernel can be given it.
+static __device__ __align__(256) float g_noalloc_scratch[BRAID_ATTN_NOALLOC_MAX_FLOATS];
+
+#define BRAID_NOALLOC_MAX_DEVICES 64
+static float* g_noalloc_ptr[BRAID_NOALLOC_MAX_DEVICES];      // device address of the array, per device
+
+extern "C" long long braid_attn_noalloc_capacity_floats(void) { return BRAID_ATTN_NOALLOC_MAX_FLOATS; }
+
+extern "C" int braid_attn_mma_noalloc(const void* q, void* out, const void* cache, const int* page_table,
+                                      const int* q_start, const int* q_len, const int* kv_before, const int* token_seq,
+                                      int q_row_stride, int out_row_stride, int rows, int n_seqs, int max_q_len,
+                                      int nqh, int nkh, int hd, int table_cols, int window, int n_splits, int kind,
+                                      float scale, void* stream) {
+    if (rows <= 0 || n_seqs <= 0) return BRAID_OK;
+    if (n_splits < 1) n_splits = 1;
+    const long long need = braid_attn_mma_partial_floats(rows, nqh, n_splits);
+    if (need > BRAID_ATTN_NOALLOC_MAX_FLOATS)
+        BRAID_REFUSE("attn_mma_noalloc: the step needs %lld floats of scratch (rows=%d heads=%d slices=%d head_dim=%d), "
+                     "the built-in array holds %d; use fewer slices or braid_attn_mma with a buffer of your own",
+                     need, rows, nqh, n_splits, BRAID_HD, BRAID_ATTN_NOALLOC_MAX_FLOATS);
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) { braid_set_error("attn_mma_noalloc: cudaGetDevice: %s", cudaGetErrorString(e)); return (int)e; }
+    if (dev < 0 || dev >= BRAID_NOALLOC_MAX_DEVICES) BRAID_REFUSE("attn_mma_noalloc: device index %d is beyond %d", dev, BRAID_NOALLOC_MAX_DEVICES);
+    if (!g_noalloc_ptr[dev]) {
+        // set-up, once per device, with that device current: the array's address on it
+        float* p = nullptr;
+        e = cudaGetSymbolAddress((void**)&p, g_noalloc_scratch);
+        if (e != cudaSuccess || !p) {
+            braid_set_error("attn_mma_noalloc: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+            return e != cudaSuccess ? (int)e : BRAID_REFUSED;
+        }
+        g_noalloc_ptr[dev] = p;
+    }
+    return braid_attn_mma(q, out, n_splits > 1 ? g_noalloc_ptr[dev] : nullptr, cache, page_table, q_start, q_len,
+                          kv_before, token_seq, q_row_stride, out_row_stride, rows, n_seqs, max_q_len, nqh, nkh, hd,
+                          table_cols, window, n_splits, kind, scale, stream);
+}
