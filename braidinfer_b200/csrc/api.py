@@ -34,6 +34,13 @@ def _ptr(t: Optional[torch.Tensor]):
     return None if t is None else t.data_ptr()
 
 
+class PartialProduct:
+    """Partial products of a stream-k GEMM waiting in the workspace to be added up."""
+
+    def __init__(self, workspace: torch.Tensor, plan, n_rows: int, w_rows: int) -> None:
+        self.workspace, self.plan, self.n_rows, self.w_rows = workspace, plan, n_rows, w_rows
+
+
 class Kernels:
     """The loaded kernel library.  One instance per process (`get_kernels`)."""
 
@@ -52,6 +59,7 @@ class Kernels:
         self._error_flag = torch.zeros(4, dtype=torch.int32, device="cuda")
         self._tc_workspace: Optional[torch.Tensor] = None
         self._attn_libs = {}
+        self.pending_partial = None     # the open PartialProduct, if any (it owns the GEMM workspace)
         self.workspace_generation = 0   # grows when a scratch buffer moves (captured graphs are stale then)
         self._attn_partial: Optional[torch.Tensor] = None
         self._verbose = verbose
@@ -75,7 +83,12 @@ class Kernels:
                                       c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_void_p]
         L.braid_gemm_tc.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                     c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_int, c_int,
-                                    c_void_p, c_void_p]
+                                    c_void_p, c_void_p, c_void_p]
+        L.braid_streamk_reduce.argtypes = [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_longlong,
+                                           c_int, c_int, c_void_p]
+        L.braid_streamk_reduce_norm.argtypes = [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int,
+                                                c_void_p, c_int, c_int, c_float, c_void_p]
+        L.braid_streamk_reduce_rope_kv.argtypes = [c_void_p] * 8 + [c_int] * 9 + [c_void_p, c_void_p]
         L.braid_gemm_tc_workspace_bytes.argtypes = [c_int, c_int, c_int]
         L.braid_gemm_tc_workspace_bytes.restype = c_longlong
         L.braid_argmax.argtypes = [c_void_p, c_longlong, c_void_p, c_int, c_int, c_void_p, c_void_p]
@@ -83,7 +96,8 @@ class Kernels:
                                   [c_void_p, c_void_p]
         for name in ("braid_embed", "braid_rmsnorm", "braid_silu_mul", "braid_residual_add",
                      "braid_rope_kv_write", "braid_cast", "braid_attn_simple", "braid_gemm_simt",
-                     "braid_gemm_tc", "braid_argmax", "braid_sample"):
+                     "braid_gemm_tc", "braid_argmax", "braid_sample", "braid_streamk_reduce",
+                     "braid_streamk_reduce_norm", "braid_streamk_reduce_rope_kv"):
             getattr(L, name).restype = c_int
 
     def _check(self, rc: int, what: str) -> None:
@@ -234,13 +248,75 @@ class Kernels:
         mode = 2 if swiglu else (1 if residual is not None else 0)
         ws = None
         if stream_k:
+            if self.pending_partial is not None:
+                raise KernelError("a deferred sum still lives in the GEMM workspace; resolve it before the next "
+                                  "stream-k product")
             ws = self.tc_workspace(self.lib.braid_gemm_tc_workspace_bytes(n, w_rows, k))
             self.launches += 1
         self.launches += 1
         self._check(self.lib.braid_gemm_tc(x.data_ptr(), w.data_ptr(), out.data_ptr(), _ptr(residual), _ptr(ws),
                                            dtype_code(out.dtype), mode, n, m, k, x.stride(0), w.stride(0),
-                                           out.stride(0), block_n, int(stream_k),
+                                           out.stride(0), block_n, int(stream_k), None,
                                            self._error_flag.data_ptr() + 4, self._stream()), "gemm_tc")
+
+    def gemm_tc_partial(self, x: torch.Tensor, w: torch.Tensor) -> "PartialProduct":
+        """The stream-k product without its reduce: the partial products stay in the
+        workspace, and the returned handle lets one of the `streamk_reduce*` calls add
+        them up together with what follows.  Only one such handle may be open at a time."""
+        if self.pending_partial is not None:
+            raise KernelError("a deferred sum still lives in the GEMM workspace; resolve it first")
+        n, k = x.shape
+        w_rows = w.shape[0]
+        ws = self.tc_workspace(self.lib.braid_gemm_tc_workspace_bytes(n, w_rows, k))
+        plan = (c_int * 6)()
+        self.launches += 1
+        self._check(self.lib.braid_gemm_tc(x.data_ptr(), w.data_ptr(), None, None, ws.data_ptr(), F32, 0, n, w_rows, k,
+                                           x.stride(0), w.stride(0), 0, 0, 1, plan,
+                                           self._error_flag.data_ptr() + 4, self._stream()), "gemm_tc_partial")
+        p = PartialProduct(ws, plan, n, w_rows)
+        self.pending_partial = p
+        return p
+
+    def _close_partial(self, p: "PartialProduct") -> None:
+        if self.pending_partial is not p:
+            raise KernelError("this partial product is not the one that lives in the workspace")
+        self.pending_partial = None
+
+    def streamk_reduce(self, p: "PartialProduct", out: torch.Tensor, residual: Optional[torch.Tensor] = None,
+                       swiglu: bool = False) -> None:
+        m = p.w_rows // 2 if swiglu else p.w_rows
+        mode = 2 if swiglu else (1 if residual is not None else 0)
+        self._close_partial(p)
+        self.launches += 1
+        self._check(self.lib.braid_streamk_reduce(p.workspace.data_ptr(), p.plan, p.n_rows, out.data_ptr(), _ptr(residual),
+                                                  m, out.stride(0), dtype_code(out.dtype), mode, self._stream()),
+                    "streamk_reduce")
+
+    def streamk_reduce_norm(self, p: "PartialProduct", h: torch.Tensor, w: torch.Tensor, out: torch.Tensor, eps: float,
+                            row_index: Optional[torch.Tensor] = None) -> None:
+        """h += sum of the partial products (written back unless rows are gathered), then
+        out = RMSNorm(h) * w, in one kernel."""
+        rows_out, width = out.shape
+        self._close_partial(p)
+        self.launches += 1
+        self._check(self.lib.braid_streamk_reduce_norm(p.workspace.data_ptr(), p.plan, p.n_rows, h.data_ptr(), w.data_ptr(),
+                                                       dtype_code(w.dtype), out.data_ptr(), dtype_code(out.dtype),
+                                                       _ptr(row_index), rows_out, width, float(eps), self._stream()),
+                    "streamk_reduce_norm")
+
+    def streamk_reduce_rope_kv(self, p: "PartialProduct", qkv: torch.Tensor, inv_freq: torch.Tensor,
+                               positions: torch.Tensor, token_seq: torch.Tensor, page_table: Optional[torch.Tensor],
+                               cache: Optional[torch.Tensor], nqh: int, nkh: int, hd: int, rope_dim: int,
+                               adjacent: bool, page_size: int) -> None:
+        """qkv = sum of the partial products, rotated, keys and values into the cache."""
+        cols = page_table.shape[1] if page_table is not None else 0
+        num_pages = cache.shape[0] if cache is not None else 0
+        self._close_partial(p)
+        self.launches += 1
+        self._check(self.lib.braid_streamk_reduce_rope_kv(
+            p.workspace.data_ptr(), p.plan, qkv.data_ptr(), inv_freq.data_ptr(), positions.data_ptr(),
+            token_seq.data_ptr(), _ptr(page_table), _ptr(cache), qkv.shape[0], nqh, nkh, hd, rope_dim, int(adjacent),
+            page_size, cols, num_pages, self._error_flag.data_ptr(), self._stream()), "streamk_reduce_rope_kv")
 
     @staticmethod
     def gemm_tc_eligible(x: torch.Tensor, w: torch.Tensor) -> bool:

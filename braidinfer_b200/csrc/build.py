@@ -28,8 +28,8 @@ COMMON_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "--expt
 
 # Sources that do not depend on a model size.
 CORE_SOURCES = ["errors.cu", "elementwise.cu", "attn_simple.cu", "gemm_simt.cu", "gemm_tc.cu",
-                "sampling.cu"]
-HEADERS = ["common.cuh", "attn_noalloc.h"]
+                "fused_reduce.cu", "sampling.cu"]
+HEADERS = ["common.cuh", "streamk.cuh", "attn_noalloc.h"]
 
 
 class BuildError(RuntimeError):

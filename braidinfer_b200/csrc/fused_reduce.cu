@@ -1,0 +1,194 @@
+// Kernels that add up the partial products of a stream-k GEMM and go straight on with
+// what follows the product, for steps of a few tokens where every launch counts:
+//
+//   braid_streamk_reduce_norm     h = h + sum (the residual sum, float32, written back),
+//                                 then RMSNorm of the new h: out = h * rsqrt(mean(h^2) + eps) * w.
+//                                 A row is shared by a cluster of up to 8 CTAs that exchange
+//                                 their sums of squares through distributed shared memory.
+//   braid_streamk_reduce_rope_kv  qkv = sum, rotary encoding of the query and key heads,
+//                                 keys and values into the paged cache (what elementwise.cu's
+//                                 rope_kv_kernel does after a plain product).
+//
+// Formulas are those of the unfused kernels (elementwise.cu cites the reference lines).
+#include "common.cuh"
+#include "streamk.cuh"
+#include <cooperative_groups.h>
+namespace cg = cooperative_groups;
+
+#define RN_THREADS 128
+
+// grid (cluster_size, rows); cluster dims (cluster_size, 1, 1): the CTAs of a cluster share row blockIdx.y.
+template <typename TW, typename TO>
+__global__ void __launch_bounds__(RN_THREADS)
+streamk_reduce_norm_kernel(StreamK k, float* h, const TW* __restrict__ w, TO* __restrict__ out,
+                           const int* __restrict__ row_index, int width, float eps) {
+    pdl_trigger();
+    pdl_wait();
+    __shared__ float red[32];
+    __shared__ float my_ss;
+    cg::cluster_group cluster = cg::this_cluster();
+    const int rank = (int)cluster.block_rank(), csize = (int)cluster.num_blocks();
+    const int r = blockIdx.y;
+    const int src = row_index ? row_index[r] : r;
+    const bool write_back = (row_index == nullptr);      // gathered rows may repeat: leave h alone
+    const int groups = (width + 3) / 4;                  // groups of four columns
+    const int per = (groups + csize - 1) / csize;
+    const int g0 = rank * per, g1 = min(groups, g0 + per);
+    TO* o = out + (size_t)r * width;
+    float ss = 0.f;
+    if (src >= 0) {
+        float* hr = h + (size_t)src * width;
+        for (int g = g0 + threadIdx.x; g < g1; g += RN_THREADS) {
+            const int c = g * 4;
+            const float4 s4 = streamk_sum4(k, streamk_span(k, src, c), src, c);
+            const float s[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                if (c + e >= width) break;
+                const float v = hr[c + e] + s[e];
+                if (write_back) hr[c + e] = v;
+                ss = fmaf(v, v, ss);
+            }
+        }
+    }
+    ss = block_sum(ss, red);
+    if (threadIdx.x == 0) my_ss = ss;
+    cluster.sync();
+    float total = 0.f;
+    for (int b = 0; b < csize; ++b) total += *cluster.map_shared_rank(&my_ss, b);
+    cluster.sync();                                       // nobody leaves while its sum may still be read
+    if (src < 0) {
+        for (int g = g0 + threadIdx.x; g < g1; g += RN_THREADS)
+            for (int e = 0; e < 4 && g * 4 + e < width; ++e) o[g * 4 + e] = from_f32<TO>(0.f);
+        return;
+    }
+    const float scale = rsqrtf(total / (float)width + eps);
+    const float* hr = h + (size_t)src * width;
+    for (int g = g0 + threadIdx.x; g < g1; g += RN_THREADS) {
+        const int c = g * 4;
+        float s[4] = {0.f, 0.f, 0.f, 0.f};
+        if (!write_back) {
+            const float4 s4 = streamk_sum4(k, streamk_span(k, src, c), src, c);
+            s[0] = s4.x; s[1] = s4.y; s[2] = s4.z; s[3] = s4.w;
+        }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            if (c + e >= width) break;
+            const float v = hr[c + e] + s[e];             // written back above by this very thread, or recomputed
+            o[c + e] = from_f32<TO>(v * scale * to_f32(w[c + e]));
+        }
+    }
+}
+
+extern "C" int braid_streamk_reduce_norm(const float* partial, const int* plan, int n_rows, float* h, const void* w,
+                                         int w_dtype, void* out, int out_dtype, const int* row_index, int rows_out,
+                                         int width, float eps, void* stream) {
+    if (rows_out <= 0) return BRAID_OK;
+    if (width <= 0) BRAID_REFUSE("reduce_norm: width=%d must be positive", width);
+    StreamK k{partial, plan[0], plan[1], plan[2], plan[3], n_rows, plan[4], (long long)plan[5]};
+    int csize = 1;
+    while (csize < 8 && width / (csize * 2) >= 256) csize *= 2;      // at least 256 columns a CTA
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(csize, rows_out);
+    cfg.blockDim = dim3(RN_THREADS);
+    cfg.stream = (cudaStream_t)stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = csize; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = braid_pdl_enabled();
+    cfg.attrs = attr;
+    cfg.numAttrs = 2;
+#define RN_LAUNCH(TW, TO) cudaLaunchKernelEx(&cfg, streamk_reduce_norm_kernel<TW, TO>, k, h, (const TW*)w, (TO*)out, row_index, width, eps)
+    if (w_dtype == BRAID_F32 && out_dtype == BRAID_F32) RN_LAUNCH(float, float);
+    else if (w_dtype == BRAID_F32 && out_dtype == BRAID_BF16) RN_LAUNCH(float, __nv_bfloat16);
+    else if (w_dtype == BRAID_BF16 && out_dtype == BRAID_F32) RN_LAUNCH(__nv_bfloat16, float);
+    else if (w_dtype == BRAID_BF16 && out_dtype == BRAID_BF16) RN_LAUNCH(__nv_bfloat16, __nv_bfloat16);
+    else BRAID_REFUSE("reduce_norm: unknown dtype codes w=%d out=%d", w_dtype, out_dtype);
+#undef RN_LAUNCH
+    BRAID_LAUNCH_CHECK();
+}
+
+// ------------------------------------------------------------------ reduce + rotary + cache write
+struct ReduceRopeArgs {
+    StreamK k;
+    __nv_bfloat16* qkv;          // [rows, (nqh + 2 nkh) * hd], written here
+    const float* inv_freq;
+    const int* positions;
+    const int* token_seq;
+    const int* page_table;
+    __nv_bfloat16* cache;        // one layer, or null (no write)
+    int rows, nqh, nkh, hd, rope_dim, adjacent;
+    int page_size, table_cols, num_pages;
+    int* error_flag;
+};
+
+__global__ void streamk_reduce_rope_kv_kernel(ReduceRopeArgs a) {
+    pdl_trigger();
+    pdl_wait();
+    const int row = blockIdx.x;
+    const int seq = a.token_seq[row];
+    if (seq < 0) return;
+    const int head = blockIdx.y;
+    const int pos = a.positions[row];
+    const int width = (a.nqh + 2 * a.nkh) * a.hd;
+    const int col0 = head * a.hd;
+    __nv_bfloat16* dst_row = a.qkv + (size_t)row * width + col0;
+    const bool is_q = head < a.nqh;
+    const bool is_k = !is_q && head < a.nqh + a.nkh;
+    __nv_bfloat16* dst = nullptr;
+    if (!is_q && a.cache) {
+        const int kvh = is_k ? head - a.nqh : head - a.nqh - a.nkh;
+        const int block = pos / a.page_size, off = pos - block * a.page_size;
+        int page = (block < a.table_cols) ? a.page_table[(size_t)seq * a.table_cols + block] : -1;
+        if (page < 0 || page >= a.num_pages) {
+            if (threadIdx.x == 0) atomicExch(a.error_flag, 1);
+            page = -1;
+        }
+        if (page >= 0)
+            dst = a.cache + ((((size_t)page * 2 + (is_k ? 0 : 1)) * a.nkh + kvh) * a.page_size + off) * a.hd;
+    }
+    const int half = a.rope_dim / 2;
+    if (is_q || is_k) {
+        for (int p = threadIdx.x; p < half; p += blockDim.x) {
+            const int i0 = a.adjacent ? 2 * p : p;
+            const int i1 = a.adjacent ? 2 * p + 1 : p + half;
+            // the product is rounded to bfloat16 before it is rotated, as after a plain product
+            const float x0 = __bfloat162float(__float2bfloat16_rn(streamk_sum(a.k, streamk_span(a.k, row, col0 + i0), row, col0 + i0)));
+            const float x1 = __bfloat162float(__float2bfloat16_rn(streamk_sum(a.k, streamk_span(a.k, row, col0 + i1), row, col0 + i1)));
+            float sn, cs;
+            sincosf((float)pos * a.inv_freq[p], &sn, &cs);
+            const __nv_bfloat16 y0 = __float2bfloat16_rn(x0 * cs - x1 * sn);
+            const __nv_bfloat16 y1 = __float2bfloat16_rn(x0 * sn + x1 * cs);
+            dst_row[i0] = y0;
+            dst_row[i1] = y1;
+            if (dst) { dst[i0] = y0; dst[i1] = y1; }
+        }
+        for (int i = a.rope_dim + threadIdx.x; i < a.hd; i += blockDim.x) {
+            const __nv_bfloat16 y = __float2bfloat16_rn(streamk_sum(a.k, streamk_span(a.k, row, col0 + i), row, col0 + i));
+            dst_row[i] = y;
+            if (dst) dst[i] = y;
+        }
+    } else {
+        for (int i = threadIdx.x; i < a.hd; i += blockDim.x) {
+            const __nv_bfloat16 y = __float2bfloat16_rn(streamk_sum(a.k, streamk_span(a.k, row, col0 + i), row, col0 + i));
+            dst_row[i] = y;
+            if (dst) dst[i] = y;
+        }
+    }
+}
+
+extern "C" int braid_streamk_reduce_rope_kv(const float* partial, const int* plan, void* qkv, const float* inv_freq,
+                                            const int* positions, const int* token_seq, const int* page_table,
+                                            void* cache, int rows, int nqh, int nkh, int hd, int rope_dim, int adjacent,
+                                            int page_size, int table_cols, int num_pages, int* error_flag, void* stream) {
+    if (rows <= 0) return BRAID_OK;
+    if (nqh <= 0 || nkh <= 0 || hd <= 0) BRAID_REFUSE("reduce_rope_kv: heads/head_dim must be positive");
+    if (rope_dim < 0 || rope_dim > hd || (rope_dim & 1)) BRAID_REFUSE("reduce_rope_kv: rope_dim=%d must be even and <= head_dim=%d", rope_dim, hd);
+    if (nqh + 2 * nkh > 65535) BRAID_REFUSE("reduce_rope_kv: %d heads exceed the grid limit", nqh + 2 * nkh);
+    ReduceRopeArgs a{{partial, plan[0], plan[1], plan[2], plan[3], rows, plan[4], (long long)plan[5]},
+                     (__nv_bfloat16*)qkv, inv_freq, positions, token_seq, page_table, (__nv_bfloat16*)cache,
+                     rows, nqh, nkh, hd, rope_dim, adjacent, page_size, table_cols, num_pages, error_flag};
+    braid_launch(streamk_reduce_rope_kv_kernel, dim3(rows, nqh + 2 * nkh), dim3(hd >= 128 ? 64 : 32), 0, (cudaStream_t)stream, a);
+    BRAID_LAUNCH_CHECK();
+}

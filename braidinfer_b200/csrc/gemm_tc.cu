@@ -32,6 +32,7 @@
 // Replaces the reference's per-row GEMV ops (kernels/megakernel_ops.hip:168-276 linear,
 // :1474-1602 feed-forward, :1783-1842 output head), which run on scalar FMA.
 #include "common.cuh"
+#include "streamk.cuh"
 #include <cuda.h>
 
 #define TC_BLOCK_M 128
@@ -379,49 +380,46 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 }
 
 // ------------------------------------------------------------------ stream-k reduce
-// Sum of the partial slots that cover output (n, column) of the [n_rows, w_rows] product.
-struct StreamK {
-    const float* partial;
-    int grid, max_segs, total_kb, n_tiles, n_rows, block_n;
-    long long w;               // m_tiles * n_tiles * total_kb
-};
-
-__device__ __forceinline__ float streamk_sum(const StreamK& k, int n, int col) {
-    const int tile = (col / TC_BLOCK_M) * k.n_tiles + n / k.block_n;
-    const long long x0 = (long long)tile * k.total_kb, x1 = x0 + k.total_kb;
-    int c = (int)(x0 * k.grid / k.w);
-    while (c + 1 < k.grid && (long long)(c + 1) * k.w / k.grid <= x0) ++c;
-    while (c > 0 && (long long)c * k.w / k.grid > x0) --c;
-    float s = 0.f;
-    for (; c < k.grid; ++c) {
-        const long long lo = (long long)c * k.w / k.grid;
-        if (lo >= x1) break;
-        const int j = tile - (int)(lo / k.total_kb);
-        const size_t slot = (size_t)c * k.max_segs + j;
-        s += k.partial[(slot * k.n_rows + n) * TC_BLOCK_M + (col % TC_BLOCK_M)];
-    }
-    return s;
-}
-
 // mode 0: store; 1: res + sum (float32); 2: columns [0, I) are gate and [I, 2I) are up,
-// out[n, I] = silu(gate) * up.
+// out[n, I] = silu(gate) * up.  One thread per four consecutive outputs of a row.
 template <int MODE>
 __global__ void streamk_reduce_kernel(StreamK k, void* __restrict__ out, const float* __restrict__ res,
                                       int m_out, long long ldo, int out_dtype) {
     pdl_trigger();
     pdl_wait();
+    const int groups = (m_out + 3) / 4;
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= (long long)k.n_rows * m_out) return;
-    const int n = (int)(i / m_out), m = (int)(i - (long long)n * m_out);
-    float s = streamk_sum(k, n, m);
-    if (MODE == 2) {
-        const float u = streamk_sum(k, n, m_out + m);
-        s = s / (1.f + expf(-s)) * u;
+    if (i >= (long long)k.n_rows * groups) return;
+    const int n = (int)(i / groups), m = (int)(i - (long long)n * groups) * 4;
+    float v[4];
+    if (MODE == 2 && (m_out & 3) == 0) {
+        const float4 g4 = streamk_sum4(k, streamk_span(k, n, m), n, m);
+        const float4 u4 = streamk_sum4(k, streamk_span(k, n, m_out + m), n, m_out + m);
+        v[0] = g4.x / (1.f + expf(-g4.x)) * u4.x;
+        v[1] = g4.y / (1.f + expf(-g4.y)) * u4.y;
+        v[2] = g4.z / (1.f + expf(-g4.z)) * u4.z;
+        v[3] = g4.w / (1.f + expf(-g4.w)) * u4.w;
+    } else if (MODE == 2) {
+        // gate column m and up column m_out + m are not aligned alike: element by element
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            if (m + e >= m_out) { v[e] = 0.f; continue; }
+            const float g = streamk_sum(k, streamk_span(k, n, m + e), n, m + e);
+            const float u = streamk_sum(k, streamk_span(k, n, m_out + m + e), n, m_out + m + e);
+            v[e] = g / (1.f + expf(-g)) * u;
+        }
+    } else {
+        const float4 s4 = streamk_sum4(k, streamk_span(k, n, m), n, m);
+        v[0] = s4.x; v[1] = s4.y; v[2] = s4.z; v[3] = s4.w;
     }
-    const size_t o = (size_t)n * ldo + m;
-    if (MODE == 1) ((float*)out)[o] = res[o] + s;
-    else if (out_dtype == BRAID_F32) ((float*)out)[o] = s;
-    else ((__nv_bfloat16*)out)[o] = __float2bfloat16_rn(s);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        if (m + e >= m_out) break;
+        const size_t o = (size_t)n * ldo + m + e;
+        if (MODE == 1) ((float*)out)[o] = res[o] + v[e];
+        else if (out_dtype == BRAID_F32) ((float*)out)[o] = v[e];
+        else ((__nv_bfloat16*)out)[o] = __float2bfloat16_rn(v[e]);
+    }
 }
 
 // ------------------------------------------------------------------ host side
@@ -518,11 +516,13 @@ extern "C" long long braid_gemm_tc_workspace_bytes(int n_rows, int w_rows, int k
 // x: [n_rows, k_in] bf16 (row stride ldx); w: [w_rows, k_in] bf16 (row stride ldw), where
 // w_rows = m_out, or 2 * m_out for the SwiGLU epilogue.  stream_k != 0 balances the
 // weight stream over all SMs for any shape (meant for a few tokens) and needs
-// `workspace`.  block_n = 0 picks the token tile.
+// `workspace`.  block_n = 0 picks the token tile.  With stream_k and plan_out != null only
+// the partial products are computed; plan_out receives {grid, max_segs, total_kb,
+// n_tiles, block_n, w} for the kernel that adds them up (fused_reduce.cu).
 extern "C" int braid_gemm_tc(const void* x, const void* w, void* out, const float* res, void* workspace,
                              int out_dtype, int mode, int n_rows, int m_out, int k_in,
                              long long ldx, long long ldw, long long ldo, int block_n, int stream_k,
-                             int* error_flag, void* stream) {
+                             int* plan_out, int* error_flag, void* stream) {
     if (n_rows <= 0 || m_out <= 0) return BRAID_OK;
     if (mode < 0 || mode > 2) BRAID_REFUSE("gemm_tc: unknown epilogue %d", mode);
     if (k_in <= 0) BRAID_REFUSE("gemm_tc: k=%d must be positive", k_in);
@@ -556,11 +556,36 @@ extern "C" int braid_gemm_tc(const void* x, const void* w, void* out, const floa
     GemmTcArgs a{workspace, nullptr, n_rows, w_rows, k_in, 0, BRAID_F32, p.m_tiles, p.n_tiles, p.max_segs, error_flag};
     rc = dispatch_tc<3>(block_n, mw, mx, a, dim3(p.grid, 1, 1), s);
     if (rc) return rc;
-    const long long total = (long long)n_rows * m_out;
-    const int threads = 256;
+    if (plan_out) {
+        // the caller adds the partial products up itself (fused with what follows the product)
+        plan_out[0] = p.grid; plan_out[1] = p.max_segs; plan_out[2] = p.total_kb; plan_out[3] = p.n_tiles;
+        plan_out[4] = block_n; plan_out[5] = (int)p.w;
+        return BRAID_OK;
+    }
+    const long long total = (long long)n_rows * ((m_out + 3) / 4);
+    const int threads = 128;
     const long long blocks = (total + threads - 1) / threads;
     if (blocks > 0x7fffffffLL) BRAID_REFUSE("gemm_tc: %lld outputs exceed one reduce launch", total);
     StreamK k{(const float*)workspace, p.grid, p.max_segs, p.total_kb, p.n_tiles, n_rows, block_n, p.w};
+    if (mode == 0) braid_launch(streamk_reduce_kernel<0>, dim3((int)blocks), dim3(threads), 0, s, k, out, res, m_out, ldo, out_dtype);
+    else if (mode == 1) braid_launch(streamk_reduce_kernel<1>, dim3((int)blocks), dim3(threads), 0, s, k, out, res, m_out, ldo, out_dtype);
+    else braid_launch(streamk_reduce_kernel<2>, dim3((int)blocks), dim3(threads), 0, s, k, out, res, m_out, ldo, out_dtype);
+    BRAID_LAUNCH_CHECK();
+}
+
+// Add up the partial products of an earlier stream-k call made with plan_out (the same
+// reduce the fused call runs): mode 0 store, 1 res + sum, 2 silu(gate) * up.
+extern "C" int braid_streamk_reduce(const float* partial, const int* plan, int n_rows, void* out, const float* res,
+                                    int m_out, long long ldo, int out_dtype, int mode, void* stream) {
+    if (n_rows <= 0 || m_out <= 0) return BRAID_OK;
+    if (mode < 0 || mode > 2) BRAID_REFUSE("streamk_reduce: unknown epilogue %d", mode);
+    if (mode == 1 && (!res || out_dtype != BRAID_F32)) BRAID_REFUSE("streamk_reduce: the residual epilogue writes float32 and needs res");
+    StreamK k{partial, plan[0], plan[1], plan[2], plan[3], n_rows, plan[4], (long long)plan[5]};
+    const long long total = (long long)n_rows * ((m_out + 3) / 4);
+    const int threads = 128;
+    const long long blocks = (total + threads - 1) / threads;
+    if (blocks > 0x7fffffffLL) BRAID_REFUSE("streamk_reduce: %lld outputs exceed one launch", total);
+    cudaStream_t s = (cudaStream_t)stream;
     if (mode == 0) braid_launch(streamk_reduce_kernel<0>, dim3((int)blocks), dim3(threads), 0, s, k, out, res, m_out, ldo, out_dtype);
     else if (mode == 1) braid_launch(streamk_reduce_kernel<1>, dim3((int)blocks), dim3(threads), 0, s, k, out, res, m_out, ldo, out_dtype);
     else braid_launch(streamk_reduce_kernel<2>, dim3((int)blocks), dim3(threads), 0, s, k, out, res, m_out, ldo, out_dtype);

@@ -37,7 +37,7 @@ class Engine:
     def __init__(self, config_dict: Mapping, tensors_or_folder, *, dtype="bfloat16", max_tokens: int = 8192,
                  max_slots: Optional[int] = None, device: str = "cuda:0", gemm_backend: str = "auto",
                  attention_backend: str = "auto", row_multiple: int = 1, use_graphs: bool = True,
-                 verbose: bool = True) -> None:
+                 fuse_reduce: bool = True, verbose: bool = True) -> None:
         from ..csrc.api import get_kernels
         self.dtype = parse_dtype(dtype)
         self.device = torch.device(device)
@@ -47,7 +47,7 @@ class Engine:
         self.config = self.arch.config_from_dict(config_dict)
         self.spec = self.arch.build_spec(self.config)
         self.rt = Runtime(act_dtype=self.dtype, device=self.device, kernels=self.kernels,
-                          gemm_backend=gemm_backend, attention_backend=attention_backend)
+                          gemm_backend=gemm_backend, attention_backend=attention_backend, fuse_reduce=fuse_reduce)
         self.model = DecoderModel(self.spec, self.rt)
         specs = self.model.tensor_specs()
         if isinstance(tensors_or_folder, (str, os.PathLike)):
@@ -152,6 +152,7 @@ class Engine:
         tables = self.cache.begin_step(slots, n_new)
         graphable = self.use_graphs and all(n == 1 for n in n_new)
         ctx = self.packer.pack(slots, tokens, before, want_l, tables, bucket_tables=graphable)
+        ctx.kernels = self.kernels
         if graphable:
             logits = self._graph_step(ctx)
         else:

@@ -44,6 +44,44 @@ class StepContext:
     host_q_len: Tuple[int, ...] = ()
     host_kv_before: Tuple[int, ...] = ()
     host_slots: Tuple[int, ...] = ()
+    # Deferred sums.  In a step of a few tokens a product may leave its partial sums in the
+    # GEMM workspace and hand the adding-up to the part that reads the result next, which
+    # fuses it with its own work (the next norm, the rotary encoding).  `deferred` maps the
+    # tensor that is still to be completed (by its data pointer) to (handle, kind): kind
+    # "residual" means tensor += sum, "store" means tensor = sum.  A part that does not
+    # know about this calls `resolve(tensor)` first, or is handed a resolved tensor by the
+    # block.  At most one sum is deferred at a time.
+    deferred: dict = field(default_factory=dict)
+    kernels: object = None
+
+    def defer(self, tensor: torch.Tensor, handle, kind: str) -> None:
+        self.deferred[tensor.data_ptr()] = (handle, kind)
+
+    def take_deferred(self, tensor: torch.Tensor):
+        """(handle, kind) if `tensor` is waiting for a deferred sum (which the caller now
+        owns and must add), else None."""
+        return self.deferred.pop(tensor.data_ptr(), None)
+
+    def resolve(self, tensor: torch.Tensor) -> torch.Tensor:
+        """Complete `tensor` now with the plain reduce kernel, if a sum is deferred on it."""
+        d = self.deferred.pop(tensor.data_ptr(), None)
+        if d is not None:
+            handle, kind = d
+            if self.kernels is None:
+                from ..csrc.api import get_kernels
+                self.kernels = get_kernels()
+            if kind == "residual":
+                self.kernels.streamk_reduce(handle, tensor, residual=tensor)
+            else:
+                self.kernels.streamk_reduce(handle, tensor)
+        return tensor
+
+    def drop_deferred(self) -> None:
+        """Forget sums nobody will read (the step wants no logits)."""
+        for handle, _ in self.deferred.values():
+            if self.kernels is not None and self.kernels.pending_partial is handle:
+                self.kernels.pending_partial = None
+        self.deferred.clear()
 
 
 class StepPacker:

@@ -76,6 +76,9 @@ class DecoderModel:
                 view.page_table = ctx.page_tables[view.group]
             h = self.blocks[entry.layer].forward(h, ctx, view, cache.state_view(e))
         if ctx.n_want == 0:
+            ctx.drop_deferred()
             return None
+        if not getattr(self.final_norm, "accepts_deferred", False):
+            ctx.resolve(h)
         x = self.final_norm.forward(h, ctx, row_index=ctx.want_rows, rows=ctx.n_want)
         return self.head.forward(x)

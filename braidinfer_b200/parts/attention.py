@@ -67,12 +67,13 @@ class GQAAttention(Mixer):
         if cache is None:
             raise RuntimeError("gqa_attention needs a cache view")
         rt = self.rt
-        qkv = self.qkv.forward(x)
+        fused = getattr(self.pe, "accepts_deferred", False)
+        qkv = self.qkv.forward(x, defer_to=ctx if fused else None)
         self.pe.encode_and_store(qkv, self.nqh, self.nkh, ctx, cache)
         rows = x.shape[0]
         out = rt.empty(rows, self.nqh * self.hd)
         self._attend(qkv, out, ctx, cache)
-        return self.o.forward(out, residual=residual)
+        return self.o.forward(out, residual=residual, defer_to=ctx)
 
     def _attend(self, qkv, out, ctx, cache) -> None:
         """Pick the attention kernel for this step.  float32 runs, and runs that ask for

@@ -65,7 +65,9 @@ class Mixer(Part):
     def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx, cache, state) -> torch.Tensor:
         """x: normed tokens [rows, width] (run dtype); residual: [rows, width] float32.
 
-        Returns residual + mix(x) as float32 (it may write into `residual`).
+        Returns residual + mix(x) as float32 (it may write into `residual`).  A built-in
+        mixer may leave the last sum to the next norm (`ctx.defer`, see
+        StepContext.deferred); whoever needs the value at once calls `ctx.resolve(t)`.
         `cache` is this run's `LayerCache` view or None; `state` is a uint8
         tensor [slots, state_bytes] for this layer or None.  Rows are the
         step's tokens packed sequence after sequence, padded rows last.

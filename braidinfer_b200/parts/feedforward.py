@@ -37,4 +37,4 @@ class SwiGLU(FeedForward):
 
     def forward(self, x, residual, ctx):
         act = self.gate_up.forward(x, swiglu=True)
-        return self.down.forward(act, residual=residual)
+        return self.down.forward(act, residual=residual, defer_to=ctx)

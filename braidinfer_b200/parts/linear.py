@@ -44,10 +44,13 @@ class Linear:
         return sum(self.out_features)
 
     def forward(self, x: torch.Tensor, *, out_dtype: Optional[torch.dtype] = None,
-                residual: Optional[torch.Tensor] = None, swiglu: bool = False) -> torch.Tensor:
+                residual: Optional[torch.Tensor] = None, swiglu: bool = False, defer_to=None) -> torch.Tensor:
         """x [rows, in].  Plain: returns [rows, out] in `out_dtype` (default x's type).
         `residual` (float32 [rows, out]): returns residual + product, written in place.
-        `swiglu`: the weight holds gate rows then up rows; returns silu(gate) * up."""
+        `swiglu`: the weight holds gate rows then up rows; returns silu(gate) * up.
+        `defer_to` (a StepContext): when the product runs in its stream-k form, leave the
+        adding-up of its partial sums to whoever reads the result next
+        (`StepContext.deferred`); the returned tensor is complete only after that."""
         K = self.rt.kernels
         w = self.weight
         rows = x.shape[0]
@@ -67,8 +70,12 @@ class Linear:
             K.cast(y, y2)
             return y2
         use_tc = (self.rt.gemm_backend == "auto" and x.dtype == torch.bfloat16 and K.gemm_tc_eligible(x, w))
+        can_defer = (defer_to is not None and use_tc and rows <= _STREAM_K_MAX_ROWS and not swiglu
+                     and self.rt.fuse_reduce and K.pending_partial is None)
         if residual is not None:
-            if use_tc:
+            if can_defer:
+                defer_to.defer(residual, K.gemm_tc_partial(x, w), "residual")
+            elif use_tc:
                 K.gemm_tc(x, w, residual, residual=residual, stream_k=rows <= _STREAM_K_MAX_ROWS)
             else:
                 K.gemm_simt(x, w, residual, residual=residual)
@@ -84,7 +91,9 @@ class Linear:
                 K.silu_mul(gu, out)
             return out
         out = torch.empty((rows, w_rows), dtype=out_dtype or x.dtype, device=x.device)
-        if use_tc:
+        if can_defer:
+            defer_to.defer(out, K.gemm_tc_partial(x, w), "store")
+        elif use_tc:
             K.gemm_tc(x, w, out, stream_k=rows <= _STREAM_K_MAX_ROWS)
         else:
             K.gemm_simt(x, w, out)

@@ -16,6 +16,8 @@ from .spec import TensorSpec
 class RMSNorm(Norm):
     """params: width, eps, name (tensor name under the prefix)."""
 
+    accepts_deferred = True      # adds a deferred residual sum in the same kernel as the norm
+
     def __init__(self, params, prefix, runtime) -> None:
         super().__init__(params, prefix, runtime)
         self.width = int(params["width"])
@@ -33,5 +35,12 @@ class RMSNorm(Norm):
                 rows: Optional[int] = None) -> torch.Tensor:
         n = rows if rows is not None else x.shape[0]
         out = self.rt.empty(n, self.width)
-        self.rt.kernels.rmsnorm(x, self.weight, out, self.eps, row_index=row_index)
+        d = ctx.take_deferred(x) if ctx is not None else None
+        if d is not None:
+            handle, kind = d
+            if kind != "residual":
+                raise RuntimeError("a norm can only complete a deferred residual sum")
+            self.rt.kernels.streamk_reduce_norm(handle, x, self.weight, out, self.eps, row_index=row_index)
+        else:
+            self.rt.kernels.rmsnorm(x, self.weight, out, self.eps, row_index=row_index)
         return out

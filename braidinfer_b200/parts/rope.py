@@ -18,6 +18,8 @@ from .base import POSITION_ENCODINGS, PositionEncoding
 class RotaryEncoding(PositionEncoding):
     """params: head_dim, theta, rope_dim (default head_dim), pairing ("half" | "adjacent")."""
 
+    accepts_deferred = True      # adds a deferred q/k/v product in the same kernel as the rotation
+
     def __init__(self, params, prefix, runtime) -> None:
         super().__init__(params, prefix, runtime)
         self.head_dim = int(params["head_dim"])
@@ -36,6 +38,17 @@ class RotaryEncoding(PositionEncoding):
         """Rotate the query and key heads of qkv [rows, (nqh + 2 nkh) * hd] in place and
         write keys and values into `cache` (a LayerCache, or None / read-only: no write)."""
         writable = cache is not None and not cache.read_only
+        d = ctx.take_deferred(qkv)
+        if d is not None:
+            handle, kind = d
+            if kind != "store" or qkv.dtype != torch.bfloat16:
+                raise RuntimeError("the rotary encoding can only complete a deferred bfloat16 product")
+            self.rt.kernels.streamk_reduce_rope_kv(
+                handle, qkv, self.inv_freq, ctx.positions, ctx.token_seq,
+                cache.page_table if writable else None, cache.storage if writable else None,
+                nqh, nkh, self.head_dim, self.rope_dim, self.pairing == "adjacent",
+                cache.page_size if cache is not None else 1)
+            return
         self.rt.kernels.rope_kv_write(
             qkv, self.inv_freq, ctx.positions, ctx.token_seq,
             cache.page_table if writable else None, cache.storage if writable else None,

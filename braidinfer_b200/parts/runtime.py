@@ -17,6 +17,9 @@ class Runtime:
     # (tests compare the two).
     gemm_backend: str = "auto"
     attention_backend: str = "auto"
+    # Let products of a few tokens leave their partial sums to the next norm or to the
+    # rotary encoding, which add them up in their own kernel (fewer launches per step).
+    fuse_reduce: bool = True
 
     @property
     def is_f32(self) -> bool:

@@ -350,3 +350,60 @@ def test_sampling_chain(K, vocab):
             lo = P.sample(lg[i].cpu(), history=hist[i], logit_bias=bias[i], **dict(kw, u=max(0.0, c["u"] - 1e-5)))
             hi = P.sample(lg[i].cpu(), history=hist[i], logit_bias=bias[i], **dict(kw, u=min(1.0, c["u"] + 1e-5)))
             assert got[i] in (lo, hi), (i, c, got[i], want)
+
+
+@pytest.mark.parametrize("n, width, k", [(8, 4096, 1024), (3, 331, 520), (64, 1000, 256), (1, 72, 64), (20, 16384, 128)])
+@pytest.mark.parametrize("od", [torch.float32, torch.bfloat16])
+def test_fused_reduce_residual_norm(K, n, width, k, od):
+    """Partial products of a stream-k GEMM + residual + RMSNorm in one kernel, against the
+    three kernels run one after the other."""
+    x, w = rnd(n, k, dtype=torch.bfloat16, scale=0.5), rnd(width, k, dtype=torch.bfloat16, scale=0.2, seed=1)
+    h0 = rnd(n, width, seed=2)
+    nw = (1 + rnd(width, scale=0.1, seed=3)).bfloat16()
+    h_ref = h0.clone()
+    K.gemm_tc(x, w, h_ref, residual=h_ref, stream_k=True)
+    out_ref = torch.empty(n, width, device=DEV, dtype=od)
+    K.rmsnorm(h_ref, nw, out_ref, 1e-5)
+    h = h0.clone()
+    out = torch.full((n, width), 9.0, device=DEV, dtype=od)
+    K.streamk_reduce_norm(K.gemm_tc_partial(x, w), h, nw, out, 1e-5)
+    assert torch.equal(h, h_ref)
+    tol = 2e-6 if od == torch.float32 else 1 / 128
+    assert ((out.double() - out_ref.double()).abs() <= tol * out_ref.double().abs() + 1e-6).all()
+    # gathered rows: h is left alone, rows may repeat or be absent
+    idx = torch.tensor([n - 1, 0, -1, 0], dtype=torch.int32, device=DEV)
+    h = h0.clone()
+    out2 = torch.full((4, width), 9.0, device=DEV, dtype=od)
+    K.streamk_reduce_norm(K.gemm_tc_partial(x, w), h, nw, out2, 1e-5, row_index=idx)
+    assert torch.equal(h, h0)
+    for r, srow in enumerate([n - 1, 0, -1, 0]):
+        if srow < 0:
+            assert float(out2[r].abs().max()) == 0.0
+        else:
+            assert ((out2[r].double() - out_ref[srow].double()).abs() <= tol * out_ref[srow].double().abs() + 1e-6).all()
+    assert K.pending_partial is None
+
+
+@pytest.mark.parametrize("pairing, hd, nqh, nkh", [("half", 128, 8, 2), ("adjacent", 48, 5, 3), ("half", 16, 4, 2)])
+def test_fused_reduce_rope_cache_write(K, pairing, hd, nqh, nkh):
+    """Partial products + rotation + cache write in one kernel, against product then rope_kv_write."""
+    k, theta = 512, 1e4
+    seqs = [(60, 10), (0, 3), (200, 1)]
+    rows = sum(n for _, n in seqs) + 2
+    pos = [p for b, n in seqs for p in range(b, b + n)] + [0, 0]
+    seq = [i for i, (b, n) in enumerate(seqs) for _ in range(n)] + [-1, -1]
+    t = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    x = rnd(rows, k, dtype=torch.bfloat16, scale=0.5)
+    w = rnd((nqh + 2 * nkh) * hd, k, dtype=torch.bfloat16, scale=0.2, seed=1)
+    inv = P.inv_freq(hd, theta).to(DEV)
+    cache_a, table = make_cache(3, [b + n for b, n in seqs], nkh, hd, torch.bfloat16)
+    cache_b = cache_a.clone()
+    qkv_a = torch.empty(rows, w.shape[0], device=DEV, dtype=torch.bfloat16)
+    K.gemm_tc(x, w, qkv_a, stream_k=True)
+    K.rope_kv_write(qkv_a, inv, t(pos), t(seq), table, cache_a, nqh, nkh, hd, hd, pairing == "adjacent", 64)
+    qkv_b = torch.zeros(rows, w.shape[0], device=DEV, dtype=torch.bfloat16)
+    K.streamk_reduce_rope_kv(K.gemm_tc_partial(x, w), qkv_b, inv, t(pos), t(seq), table, cache_b, nqh, nkh, hd, hd,
+                             pairing == "adjacent", 64)
+    K.check_device_errors()
+    assert torch.equal(qkv_a[:-2], qkv_b[:-2]) and torch.equal(cache_a, cache_b)
+    assert float(qkv_b[-2:].abs().max()) == 0.0              # padding rows are not written

@@ -175,3 +175,19 @@ def test_trace_run_as_a_program(tmp_path):
         assert max_err(torch.from_numpy(s0[0]), orc.logits(toks[0])[3]) < tol
         assert max_err(torch.from_numpy(s0[2]), orc.logits(toks[1])[1]) < tol
         assert max_err(torch.from_numpy(s2[0]), orc.logits(toks[0])[5]) < tol
+
+
+def test_fused_and_unfused_reduces_agree(model):
+    """Steps of a few tokens leave the adding-up of their stream-k products to the next norm
+    and to the rotary encoding; switching that off must give the same logits."""
+    name, folder, orc, prompts = model
+    outs = []
+    for fuse in (True, False):
+        eng = engine(folder, "bfloat16", fuse_reduce=fuse, use_graphs=False)
+        slots = [eng.open() for _ in prompts[:3]]
+        a = eng.step(list(zip(slots, prompts[:3])), want="last")
+        b = eng.step([(s, [7]) for s in slots], want="last")
+        c = eng.step([(s, [9, 11]) for s in slots], want="all")
+        outs.append(torch.cat([a, b, c]).clone())
+        eng.check()
+    assert (outs[0] - outs[1]).abs().max().item() < 1e-6
