@@ -193,8 +193,14 @@ class Kernels:
             lib.braid_attn_mma.argtypes = [c_void_p] * 9 + [c_int] * 12 + [c_float, c_void_p]
             lib.braid_attn_mma_partial_floats.restype = c_longlong
             lib.braid_attn_mma_partial_floats.argtypes = [c_int, c_int, c_int]
+            lib.braid_attn_mma_decode_slots.restype = c_int
+            lib.braid_attn_mma_decode_slots.argtypes = [c_int]
+            lib.decode_slots = lib.braid_attn_mma_decode_slots(1)     # CTAs of the few-token kernel held at once
             self._attn_libs[head_dim] = lib
         return lib
+
+    def attn_decode_slots(self, head_dim: int) -> int:
+        return self.attn_mma_library(head_dim).decode_slots
 
     def attn_mma(self, q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, page_table: torch.Tensor,
                  q_start: torch.Tensor, q_len: torch.Tensor, kv_before: torch.Tensor, token_seq: torch.Tensor,

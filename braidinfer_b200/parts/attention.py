@@ -19,10 +19,6 @@ from .linear import Linear
 from .spec import CacheRequest, PartSpec, TensorSpec
 
 
-# One-warp CTAs of the few-token attention kernel to aim for (148 SMs, several each).
-_DECODE_CTAS = 148 * 6
-
-
 @MIXERS.register("gqa_attention")
 class GQAAttention(Mixer):
     """params: hidden_size, num_heads, num_kv_heads, head_dim, window (int | None),
@@ -93,7 +89,8 @@ class GQAAttention(Mixer):
             ctas = ctx.n_seqs * self.nkh * -(-g // 16)
             span = min(ctx.max_kv_len, self.window) if self.window else ctx.max_kv_len
             tiles = max(1, -(-span // 32))
-            n_splits = max(1, min(-(-_DECODE_CTAS // ctas), tiles // 2, 64))
+            # one wave of CTAs over the device, and at least four key tiles a slice
+            n_splits = max(1, min(K.attn_decode_slots(self.hd) // ctas, tiles // 4, 64))
         K.attn_mma(qkv, out, cache.storage, cache.page_table, ctx.q_start, ctx.q_len, ctx.kv_before, ctx.token_seq,
                    ctx.n_seqs, ctx.max_q_len, self.nqh, self.nkh, self.hd, self.window, self.scale,
                    n_splits=n_splits, few_tokens=few)
