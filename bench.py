@@ -156,14 +156,17 @@ def run_ours(args):
     pk = peaks()
     cfg_dict = preset("mistral_7b_v03")
     full_layers = cfg_dict["num_hidden_layers"]
+    if args.quick and not args.layers:
+        args.layers = 4
     if args.layers:
         cfg_dict["num_hidden_layers"] = args.layers
     n_layers = cfg_dict["num_hidden_layers"]
     B, prompt_len, gen_len, ctx_len = args.batch, 2048, 256, 4096
     steps, warmup = args.steps, max(3, args.warmup)
     t0 = time.time()
-    engine = Engine.from_random(cfg_dict, seed=0, dtype="bfloat16", on_device=True, max_tokens=64 * ctx_len,
-                                max_slots=64, verbose=True)
+    cache_seqs = B if args.quick else 64
+    engine = Engine.from_random(cfg_dict, seed=0, dtype="bfloat16", on_device=True, max_tokens=cache_seqs * ctx_len,
+                                max_slots=64, use_graphs=not args.no_graphs, verbose=True)
     cfg = engine.config
     model = Model(engine, max_batch=64)
     g = torch.Generator().manual_seed(0)
@@ -205,15 +208,18 @@ def run_ours(args):
                 "frac": achieved / pk["hbm_gbs"], "peak_source": pk["source"], "bytes_per_step": step_bytes}
 
     # ---- the same through the Python entry point: host tokens in, host tokens out
-    outs = model.generate(prompts_for(B), SamplingParams.greedy(), stop_tokens=(), max_new_tokens=min(steps, gen_len) + 1)
-    st = model.last_stats
-    e2e = {"value": st.decode_tokens / st.decode_seconds if st.decode_seconds > 0 else 0.0, "unit": "tokens/s",
-           "h2d_bytes_per_step": engine.packer.h2d_bytes_last, "d2h_bytes_per_step": B * 4 + 16,
-           "prefill_tokens_per_s": st.prompt_tokens / st.prefill_seconds if st.prefill_seconds > 0 else 0.0}
+    e2e = None
+    if not args.quick:
+        outs = model.generate(prompts_for(B), SamplingParams.greedy(), stop_tokens=(),
+                              max_new_tokens=min(steps, gen_len) + 1)
+        st = model.last_stats
+        e2e = {"value": st.decode_tokens / st.decode_seconds if st.decode_seconds > 0 else 0.0, "unit": "tokens/s",
+               "h2d_bytes_per_step": engine.packer.h2d_bytes_last, "d2h_bytes_per_step": B * 4 + 16,
+               "prefill_tokens_per_s": st.prompt_tokens / st.prefill_seconds if st.prefill_seconds > 0 else 0.0}
 
     # ---- other batch sizes
     points = {}
-    for b in (1, 64):
+    for b in (() if args.quick else (1, 64)):
         k = min(steps, 64)
         s2, _, _ = device_timed_decode(engine, engine.kernels, prompts_for(b), k, warmup)
         points[f"decode_b{b}"] = b * k / s2
@@ -229,7 +235,7 @@ def run_ours(args):
                    "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
                    "rope_theta": cfg.rope_theta, "rms_eps": cfg.rms_norm_eps, "global_batch": B,
                    "seq_len": ctx_len, "prompt_len": prompt_len, "context_at_timing": int(avg_ctx),
-                   "cache_tokens": 64 * ctx_len, "parallelism": "single GPU",
+                   "cache_tokens": cache_seqs * ctx_len, "parallelism": "single GPU",
                    "l2": "inputs (14.5 GB of weights) exceed L2; no flush"},
         "e2e": e2e, "gpu_launches": launches, "clocks": clocks, "prefill": prefill, "roofline": roofline,
         "points": points, "setup_seconds": time.time() - t0,
@@ -253,6 +259,10 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (0: all)")
+    ap.add_argument("--quick", action="store_true",
+                    help="a small case for profilers: 4 layers unless --layers says otherwise, a cache for this batch "
+                         "only, no batch-1/64 points and no end-to-end run; the number it prints is not a bench value")
+    ap.add_argument("--no-graphs", action="store_true", help="launch every step kernel by kernel")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
