@@ -214,7 +214,7 @@ def run_ours(args):
                               max_new_tokens=min(steps, gen_len) + 1)
         st = model.last_stats
         e2e = {"value": st.decode_tokens / st.decode_seconds if st.decode_seconds > 0 else 0.0, "unit": "tokens/s",
-               "h2d_bytes_per_step": engine.packer.h2d_bytes_last, "d2h_bytes_per_step": B * 4 + 16,
+               "h2d_bytes_per_step": engine.packer.h2d_bytes_last, "d2h_bytes_per_step": B * 4,
                "prefill_tokens_per_s": st.prompt_tokens / st.prefill_seconds if st.prefill_seconds > 0 else 0.0}
 
     # ---- other batch sizes

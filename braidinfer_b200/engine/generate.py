@@ -121,9 +121,10 @@ class GenerationLoop:
             logits = eng.step([(slots[i], list(prompts[i])) for i in live], want="last")
             first = True
             while live:
-                hist = [list(prompts[i]) + generated[i] for i in live]
+                now_live = list(live)
                 toks = self.sampler.choose(logits, [plist[i] for i in live], [seeds[i] for i in live],
-                                           live, [len(generated[i]) for i in live], hist)
+                                           live, [len(generated[i]) for i in live],
+                                           lambda: [list(prompts[i]) + generated[i] for i in now_live])
                 now = time.perf_counter()
                 self.stats.steps += 1
                 if first:
@@ -150,6 +151,9 @@ class GenerationLoop:
                 live = nxt
                 if live:
                     logits = eng.step(entries, want="last")
+            check = getattr(eng, "check", None)
+            if check is not None:
+                check()                                    # sticky device error flags, once per batch
         finally:
             for s in slots.values():                       # only on an error: nothing stays held
                 eng.close(s)

@@ -84,6 +84,11 @@ class StepContext:
         self.deferred.clear()
 
 
+class _Shaped:
+    def __init__(self, shape):
+        self.shape = shape
+
+
 class StepPacker:
     """Builds a step's integer tables on the host and moves them to the device in one copy."""
 
@@ -111,6 +116,8 @@ class StepPacker:
         """`bucket_tables` widens every page table to a power-of-two number of columns (at
         least 8), so that steps of the same shape lay their tables out identically."""
         n_seqs = len(slots)
+        if bucket_tables and all(len(t) == 1 for t in tokens) and all(len(w) <= 1 for w in want):
+            return self._pack_one_token_each(slots, tokens, kv_before, want, tables)
         if bucket_tables:
             wide = []
             for t in tables:
@@ -158,6 +165,61 @@ class StepPacker:
         self._copied.record()
         self.h2d_bytes_last = total * 4
 
+        return self._context(dev, parts, offs, tables, rows, n_tokens, n_seqs, q_len, kv_before, slots, want_rows)
+
+    def _pack_one_token_each(self, slots, tokens, kv_before, want, tables) -> StepContext:
+        """The same layout as `pack` for the common step of generation (one token a
+        sequence, page tables widened to a power-of-two width), written straight into the
+        pinned buffer."""
+        n = len(slots)
+        rows = -(-n // self.row_multiple) * self.row_multiple
+        want_rows = [i for i, w in enumerate(want) if w]
+        for w in want:
+            if w and w[0] != 0:
+                raise IndexError(f"wanted place {w[0]} is outside the 1 token that the sequence brings")
+        wide = []
+        for t in tables:
+            cols = max(8, 1 << (t.shape[1] - 1).bit_length())
+            wide.append((t, cols))
+        sizes = [rows, rows, rows, n, n, n, n, len(want_rows)] + [n * c for _, c in wide]
+        offs, total = [], 0
+        for sz in sizes:
+            offs.append(total)
+            total += -(-sz // 4) * 4
+        pinned, dev = self._buffers(max(total, 4))
+        if self._copied is not None:
+            self._copied.synchronize()
+        pn = pinned.numpy()
+        ar = np.arange(n, dtype=np.int32)
+        pn[offs[0]:offs[0] + rows] = 0
+        pn[offs[0]:offs[0] + n] = [t[0] for t in tokens]
+        pn[offs[1]:offs[1] + rows] = 0
+        pn[offs[1]:offs[1] + n] = kv_before
+        pn[offs[2]:offs[2] + rows] = -1
+        pn[offs[2]:offs[2] + n] = ar
+        pn[offs[3]:offs[3] + n] = ar
+        pn[offs[4]:offs[4] + n] = 1
+        pn[offs[5]:offs[5] + n] = kv_before
+        pn[offs[6]:offs[6] + n] = slots
+        pn[offs[7]:offs[7] + len(want_rows)] = want_rows
+        shapes = []
+        for g, (t, cols) in enumerate(wide):
+            v = pn[offs[8 + g]:offs[8 + g] + n * cols].reshape(n, cols)
+            v[:, :t.shape[1]] = t
+            v[:, t.shape[1]:] = -1
+            shapes.append((n, cols))
+        dev[:total].copy_(pinned[:total], non_blocking=True)
+        self._copied = torch.cuda.Event()
+        self._copied.record()
+        self.h2d_bytes_last = total * 4
+
+        class _Sized:                      # what `_context` needs of the parts: their sizes
+            def __init__(self, size): self.size = size
+        parts = [_Sized(sz) for sz in sizes]
+        return self._context(dev, parts, offs, [_Shaped(s) for s in shapes], rows, n, n, [1] * n, kv_before, slots,
+                             want_rows)
+
+    def _context(self, dev, parts, offs, tables, rows, n_tokens, n_seqs, q_len, kv_before, slots, want_rows):
         def view(k: int, shape=None) -> torch.Tensor:
             v = dev[offs[k]:offs[k] + parts[k].size]
             return v if shape is None else v.view(shape)

@@ -18,15 +18,21 @@ from .rng import entropy_seed, uniform
 
 
 class Sampler:
+    # The device's error flags are sticky; they are read every this many draws (and by
+    # `Engine.check()` whenever the caller wants), not after every draw.
+    CHECK_EVERY = 32
+
     def __init__(self, kernels, device) -> None:
         self.K = kernels
         self.device = device
+        self._draws = 0
 
     def choose(self, logits: torch.Tensor, params: Sequence[SamplingParams], seeds: Sequence[int],
-               sequence_ids: Sequence[int], steps: Sequence[int],
-               histories: Optional[Sequence[Sequence[int]]] = None) -> List[int]:
+               sequence_ids: Sequence[int], steps: Sequence[int], histories=None) -> List[int]:
         """logits [rows, vocab] float32 on the device -> one token id per row (host ints).
-        `histories[i]` is what the repetition penalty looks at (prompt + generated)."""
+        `histories` is a list, or a function returning the list, of what the repetition
+        penalty looks at for each row (prompt + generated); it is only asked for when some
+        row has a penalty."""
         rows, vocab = logits.shape
         out = torch.empty(rows, dtype=torch.int32, device=self.device)
         if all(p.is_plain_greedy for p in params):
@@ -34,6 +40,8 @@ class Sampler:
             return self._read(out)
         f = np.zeros((5, rows), dtype=np.float32)      # temperature, top_p, min_p, rep_penalty, uniform
         k = np.zeros(rows, dtype=np.int32)
+        if callable(histories):
+            histories = histories() if any(p.repetition_penalty != 1.0 for p in params) else None
         hist_off, hist_tok, hist_cnt = [0], [], []
         bias_off, bias_tok, bias_val = [0], [], []
         for i, p in enumerate(params):
@@ -71,5 +79,7 @@ class Sampler:
 
     def _read(self, out: torch.Tensor) -> List[int]:
         toks = out.tolist()                    # synchronises: the step's results are complete here
-        self.K.check_device_errors()
+        self._draws += 1
+        if self._draws % self.CHECK_EVERY == 0:
+            self.K.check_device_errors()
         return toks

@@ -40,7 +40,7 @@ class FakeEngine:
 
 class ArgmaxSampler:
     def choose(self, logits, params, seeds, ids, steps, hist):
-        self.last = (list(ids), list(steps), [list(h) for h in hist])
+        self.last = (list(ids), list(steps), [list(h) for h in hist()])
         return logits.argmax(-1).tolist()
 
 
