@@ -34,6 +34,18 @@ def _ptr(t: Optional[torch.Tensor]):
     return None if t is None else t.data_ptr()
 
 
+def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """The weight layout of the SwiGLU epilogue: blocks of 32 rows, each the gate rows
+    [16t, 16t+16) followed by the up rows [16t, 16t+16); rows past the true size are zero."""
+    inter, k = gate.shape
+    blocks = -(-inter // 16)
+    g = torch.zeros((blocks * 16, k), dtype=gate.dtype, device=gate.device)
+    u = torch.zeros_like(g)
+    g[:inter] = gate
+    u[:inter] = up
+    return torch.cat([g.view(blocks, 16, k), u.view(blocks, 16, k)], dim=1).reshape(blocks * 32, k).contiguous()
+
+
 class PartialProduct:
     """Partial products of a stream-k GEMM waiting in the workspace to be added up."""
 
@@ -246,11 +258,14 @@ class Kernels:
     def gemm_tc(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, residual: Optional[torch.Tensor] = None,
                 swiglu: bool = False, block_n: int = 0, stream_k: bool = False) -> None:
         """bfloat16 x [n, k] times w [m, k]^T on the tensor cores.  With `swiglu`, w holds
-        gate rows then up rows and out is [n, m/2].  `stream_k` spreads the weight stream
+        gate and up rows interleaved in blocks of 16 (`interleave_gate_up`) and out is [n, I].  `stream_k` spreads the weight stream
         evenly over all SMs whatever the shape (for a few tokens) and adds a reduce kernel."""
         n, k = x.shape
         w_rows = w.shape[0]
-        m = w_rows // 2 if swiglu else w_rows
+        m = out.shape[1] if swiglu else w_rows
+        if swiglu and w_rows != 2 * (-(-m // 16) * 16):
+            raise KernelError(f"the SwiGLU epilogue wants {2 * (-(-m // 16) * 16)} interleaved weight rows for "
+                              f"{m} outputs, got {w_rows} (see interleave_gate_up)")
         mode = 2 if swiglu else (1 if residual is not None else 0)
         ws = None
         if stream_k:
@@ -290,7 +305,7 @@ class Kernels:
 
     def streamk_reduce(self, p: "PartialProduct", out: torch.Tensor, residual: Optional[torch.Tensor] = None,
                        swiglu: bool = False) -> None:
-        m = p.w_rows // 2 if swiglu else p.w_rows
+        m = out.shape[1] if swiglu else p.w_rows
         mode = 2 if swiglu else (1 if residual is not None else 0)
         self._close_partial(p)
         self.launches += 1

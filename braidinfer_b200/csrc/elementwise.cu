@@ -70,12 +70,82 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const TW* __restrict
     for (int i = threadIdx.x; i < width; i += blockDim.x) o[i] = from_f32<TO>(xr[i] * scale * to_f32(w[i]));
 }
 
+// Rows whose width is a multiple of 4 (and at most 4 * 8 * 512): one pass over x with
+// 16-byte loads, the row kept in registers between the sum of squares and the scaling.
+template <typename TW, typename TO, int PER>
+__global__ void __launch_bounds__(512)
+rmsnorm_vec_kernel(const float* __restrict__ x, const TW* __restrict__ w, TO* __restrict__ out,
+                   const int* __restrict__ row_index, int rows, int width, float eps) {
+    pdl_trigger();
+    pdl_wait();
+    __shared__ float red[32];
+    const int r = blockIdx.x;
+    const int src = row_index ? row_index[r] : r;
+    TO* o = out + (size_t)r * width;
+    const int groups = width >> 2;
+    if (src < 0) {
+        for (int g = threadIdx.x; g < groups; g += blockDim.x)
+            for (int e = 0; e < 4; ++e) o[g * 4 + e] = from_f32<TO>(0.f);
+        return;
+    }
+    const float4* xr = reinterpret_cast<const float4*>(x + (size_t)src * width);
+    float4 v[PER];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+        const int g = threadIdx.x + i * blockDim.x;
+        if (g < groups) {
+            v[i] = xr[g];
+            ss = fmaf(v[i].x, v[i].x, ss); ss = fmaf(v[i].y, v[i].y, ss);
+            ss = fmaf(v[i].z, v[i].z, ss); ss = fmaf(v[i].w, v[i].w, ss);
+        }
+    }
+    ss = block_sum(ss, red);
+    const float scale = rsqrtf(ss / (float)width + eps);
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+        const int g = threadIdx.x + i * blockDim.x;
+        if (g < groups) {
+            const int c = g * 4;
+            const float y0 = v[i].x * scale * to_f32(w[c]), y1 = v[i].y * scale * to_f32(w[c + 1]);
+            const float y2 = v[i].z * scale * to_f32(w[c + 2]), y3 = v[i].w * scale * to_f32(w[c + 3]);
+            if (sizeof(TO) == 2) {
+                __nv_bfloat162 a = __floats2bfloat162_rn(y0, y1), b = __floats2bfloat162_rn(y2, y3);
+                uint2 pk;
+                pk.x = *reinterpret_cast<unsigned int*>(&a);
+                pk.y = *reinterpret_cast<unsigned int*>(&b);
+                *reinterpret_cast<uint2*>(o + c) = pk;
+            } else {
+                *reinterpret_cast<float4*>(o + c) = make_float4(y0, y1, y2, y3);
+            }
+        }
+    }
+}
+
 extern "C" int braid_rmsnorm(const float* x, const void* w, int w_dtype, void* out, int out_dtype,
                              const int* row_index, int rows, int width, float eps, void* stream) {
     if (rows <= 0) return BRAID_OK;
     if (width <= 0) BRAID_REFUSE("rmsnorm: width=%d must be positive", width);
     cudaStream_t s = (cudaStream_t)stream;
     const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
+    const bool aligned = (width % 4 == 0) && (((uintptr_t)x & 15) == 0) && (((uintptr_t)out & 15) == 0);
+    if (aligned && width <= 4 * 8 * threads) {
+        const int per = (width / 4 + threads - 1) / threads;          // float4 groups a thread
+#define BRAID_RMSV(TW, TO)                                                                                           \
+        do {                                                                                                         \
+            if (per <= 1) braid_launch(rmsnorm_vec_kernel<TW, TO, 1>, dim3(rows), dim3(threads), 0, s, x, (const TW*)w, (TO*)out, row_index, rows, width, eps); \
+            else if (per <= 2) braid_launch(rmsnorm_vec_kernel<TW, TO, 2>, dim3(rows), dim3(threads), 0, s, x, (const TW*)w, (TO*)out, row_index, rows, width, eps); \
+            else if (per <= 4) braid_launch(rmsnorm_vec_kernel<TW, TO, 4>, dim3(rows), dim3(threads), 0, s, x, (const TW*)w, (TO*)out, row_index, rows, width, eps); \
+            else braid_launch(rmsnorm_vec_kernel<TW, TO, 8>, dim3(rows), dim3(threads), 0, s, x, (const TW*)w, (TO*)out, row_index, rows, width, eps); \
+        } while (0)
+        if (w_dtype == BRAID_F32 && out_dtype == BRAID_F32) BRAID_RMSV(float, float);
+        else if (w_dtype == BRAID_F32 && out_dtype == BRAID_BF16) BRAID_RMSV(float, __nv_bfloat16);
+        else if (w_dtype == BRAID_BF16 && out_dtype == BRAID_F32) BRAID_RMSV(__nv_bfloat16, float);
+        else if (w_dtype == BRAID_BF16 && out_dtype == BRAID_BF16) BRAID_RMSV(__nv_bfloat16, __nv_bfloat16);
+        else BRAID_REFUSE("rmsnorm: unknown dtype codes w=%d out=%d", w_dtype, out_dtype);
+#undef BRAID_RMSV
+        BRAID_LAUNCH_CHECK();
+    }
 #define BRAID_RMS(TW, TO) braid_launch(rmsnorm_kernel<TW, TO>, dim3(rows), dim3(threads), 0, s, x, (const TW*)w, (TO*)out, row_index, rows, width, eps)
     if (w_dtype == BRAID_F32 && out_dtype == BRAID_F32) BRAID_RMS(float, float);
     else if (w_dtype == BRAID_F32 && out_dtype == BRAID_BF16) BRAID_RMS(float, __nv_bfloat16);
@@ -200,6 +270,94 @@ __global__ void rope_kv_kernel(RopeKvArgs a) {
     }
 }
 
+// One block per token; angles computed once per (token, pair) and shared by all heads;
+// 16-byte loads and stores.  Needs head_dim and rope_dim to be multiples of 2 * VEC
+// (VEC = 8 for bfloat16, 4 for float32) and 16-byte aligned rows.
+template <typename T>
+__global__ void __launch_bounds__(256)
+rope_kv_vec_kernel(RopeKvArgs a) {
+    pdl_trigger();
+    pdl_wait();
+    constexpr int VEC = 16 / sizeof(T);
+    extern __shared__ float cs_sn[];                   // [rope_dim / 2] cosines, then sines
+    const int row = blockIdx.x;
+    const int seq = a.token_seq[row];
+    if (seq < 0) return;
+    const int pos = a.positions[row];
+    const int half = a.rope_dim / 2;
+    for (int p = threadIdx.x; p < half; p += blockDim.x) sincosf((float)pos * a.inv_freq[p], &cs_sn[half + p], &cs_sn[p]);
+    const int width = (a.nqh + 2 * a.nkh) * a.hd;
+    T* base = (T*)a.qkv + (size_t)row * width;
+    T* kdst = nullptr;
+    T* vdst = nullptr;
+    if (a.cache) {
+        const int block = pos / a.page_size, off = pos - block * a.page_size;
+        int page = (block < a.table_cols) ? a.page_table[(size_t)seq * a.table_cols + block] : -1;
+        if (page < 0 || page >= a.num_pages) {
+            if (threadIdx.x == 0) atomicExch(a.error_flag, 1);
+        } else {
+            kdst = (T*)a.cache + (((size_t)page * 2) * a.nkh * a.page_size + off) * a.hd;       // + kvh * page_size * hd
+            vdst = kdst + (size_t)a.nkh * a.page_size * a.hd;
+        }
+    }
+    __syncthreads();
+    const int rot_vecs = a.adjacent ? a.rope_dim / VEC : half / VEC;      // vectors a head's rotation takes
+    const int pass_vecs = (a.hd - a.rope_dim) / VEC;                      // unrotated tail of a q/k head
+    const int qk_heads = a.nqh + a.nkh;
+    const int per_head = rot_vecs + pass_vecs;
+    for (int item = threadIdx.x; item < qk_heads * per_head; item += blockDim.x) {
+        const int head = item / per_head, j = item - head * per_head;
+        T* h = base + (size_t)head * a.hd;
+        T* dst = (head >= a.nqh && kdst) ? kdst + (size_t)(head - a.nqh) * a.page_size * a.hd : nullptr;
+        if (j >= rot_vecs) {                            // tail beyond rope_dim: keys copy through to the cache
+            const int i0 = a.rope_dim + (j - rot_vecs) * VEC;
+            if (dst) *reinterpret_cast<uint4*>(dst + i0) = *reinterpret_cast<const uint4*>(h + i0);
+            continue;
+        }
+        T x0[VEC], x1[VEC];
+        if (a.adjacent) {
+            const int i0 = j * VEC;                     // VEC / 2 pairs (2p, 2p + 1)
+            *reinterpret_cast<uint4*>(x0) = *reinterpret_cast<const uint4*>(h + i0);
+#pragma unroll
+            for (int e = 0; e < VEC; e += 2) {
+                const int p = (i0 + e) >> 1;
+                const float c = cs_sn[p], sn = cs_sn[half + p];
+                const float u = to_f32(x0[e]), v = to_f32(x0[e + 1]);
+                x0[e] = from_f32<T>(u * c - v * sn);
+                x0[e + 1] = from_f32<T>(u * sn + v * c);
+            }
+            *reinterpret_cast<uint4*>(h + i0) = *reinterpret_cast<const uint4*>(x0);
+            if (dst) *reinterpret_cast<uint4*>(dst + i0) = *reinterpret_cast<const uint4*>(x0);
+        } else {
+            const int i0 = j * VEC;                     // VEC pairs (p, p + half)
+            *reinterpret_cast<uint4*>(x0) = *reinterpret_cast<const uint4*>(h + i0);
+            *reinterpret_cast<uint4*>(x1) = *reinterpret_cast<const uint4*>(h + i0 + half);
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) {
+                const float c = cs_sn[i0 + e], sn = cs_sn[half + i0 + e];
+                const float u = to_f32(x0[e]), v = to_f32(x1[e]);
+                x0[e] = from_f32<T>(u * c - v * sn);
+                x1[e] = from_f32<T>(u * sn + v * c);
+            }
+            *reinterpret_cast<uint4*>(h + i0) = *reinterpret_cast<const uint4*>(x0);
+            *reinterpret_cast<uint4*>(h + i0 + half) = *reinterpret_cast<const uint4*>(x1);
+            if (dst) {
+                *reinterpret_cast<uint4*>(dst + i0) = *reinterpret_cast<const uint4*>(x0);
+                *reinterpret_cast<uint4*>(dst + i0 + half) = *reinterpret_cast<const uint4*>(x1);
+            }
+        }
+    }
+    if (vdst) {
+        const int hv = a.hd / VEC;
+        const T* vsrc = base + (size_t)qk_heads * a.hd;
+        for (int item = threadIdx.x; item < a.nkh * hv; item += blockDim.x) {
+            const int kvh = item / hv, j = item - kvh * hv;
+            *reinterpret_cast<uint4*>(vdst + (size_t)kvh * a.page_size * a.hd + j * VEC) =
+                *reinterpret_cast<const uint4*>(vsrc + (size_t)kvh * a.hd + j * VEC);
+        }
+    }
+}
+
 extern "C" int braid_rope_kv_write(void* qkv, int dtype, const float* inv_freq, const int* positions,
                                    const int* token_seq, const int* page_table, void* cache,
                                    int rows, int nqh, int nkh, int hd, int rope_dim, int adjacent,
@@ -211,9 +369,17 @@ extern "C" int braid_rope_kv_write(void* qkv, int dtype, const float* inv_freq, 
     if (nqh + 2 * nkh > 65535) BRAID_REFUSE("rope_kv_write: %d heads exceed the grid limit", nqh + 2 * nkh);
     RopeKvArgs a{qkv, inv_freq, positions, token_seq, page_table, cache, rows, nqh, nkh, hd, rope_dim, adjacent,
                  page_size, table_cols, num_pages, error_flag};
+    cudaStream_t s = (cudaStream_t)stream;
+    const int vec = dtype == BRAID_F32 ? 4 : 8;
+    if ((dtype == BRAID_F32 || dtype == BRAID_BF16) && hd % (2 * vec) == 0 && rope_dim % (2 * vec) == 0 &&
+        (((uintptr_t)qkv | (uintptr_t)cache) & 15) == 0) {
+        const size_t smem = (size_t)rope_dim * sizeof(float);
+        if (dtype == BRAID_F32) braid_launch(rope_kv_vec_kernel<float>, dim3(rows), dim3(256), smem, s, a);
+        else braid_launch(rope_kv_vec_kernel<__nv_bfloat16>, dim3(rows), dim3(256), smem, s, a);
+        BRAID_LAUNCH_CHECK();
+    }
     dim3 grid(rows, nqh + 2 * nkh);
     const int threads = hd >= 128 ? 64 : 32;
-    cudaStream_t s = (cudaStream_t)stream;
     if (dtype == BRAID_F32) braid_launch(rope_kv_kernel<float>, dim3(grid), dim3(threads), 0, s, a);
     else if (dtype == BRAID_BF16) braid_launch(rope_kv_kernel<__nv_bfloat16>, dim3(grid), dim3(threads), 0, s, a);
     else BRAID_REFUSE("rope_kv_write: unknown dtype code %d", dtype);

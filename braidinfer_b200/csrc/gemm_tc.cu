@@ -16,8 +16,9 @@
 //   warps 2..5  epilogue: tcgen05.ld of their 32 lanes, then one of
 //                 0  store in bfloat16 or float32,
 //                 1  float32 residual sum: out = res + product,
-//                 2  SwiGLU: w holds gate rows [0, I) and up rows [I, 2I); two
-//                    accumulators share the token tile; out = silu(gate) * up,
+//                 2  SwiGLU: w interleaves gate and up rows in blocks of 16, so each
+//                    epilogue warp holds 16 outputs' gate (lanes 0..15) and up (lanes
+//                    16..31) and pairs them with a shuffle; out = silu(gate) * up,
 //                 3  float32 partial sums of a run of k blocks ("stream-k"), added up
 //                    by a reduce kernel with one of the epilogues above.
 //
@@ -127,14 +128,13 @@ struct GemmTcArgs {
 
 template <int BLOCK_N, int MODE>
 struct TcCfg {
-    static constexpr int kAccs = (MODE == 2) ? 2 : 1;
-    static constexpr int kABytes = TC_BLOCK_M * TC_BLOCK_K * 2 * kAccs;
+    static constexpr int kABytes = TC_BLOCK_M * TC_BLOCK_K * 2;
     static constexpr int kBBytes = BLOCK_N * TC_BLOCK_K * 2;
     static constexpr int kStageBytes = kABytes + kBBytes;
     static constexpr int kBudget = 200 * 1024;
     static constexpr int kStagesRaw = kBudget / kStageBytes;
     static constexpr int kStages = kStagesRaw > 10 ? 10 : kStagesRaw;
-    static constexpr int kAccCols = BLOCK_N * kAccs;                       // columns of one accumulator buffer
+    static constexpr int kAccCols = BLOCK_N;                               // columns of one accumulator buffer
     static constexpr int kAccBufs = (kAccCols * 2 <= 512) ? 2 : 1;          // two: the epilogue overlaps the next tile
     static constexpr int kTmemCols = (kAccCols * kAccBufs) < 32 ? 32 : (kAccCols * kAccBufs);
     static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /* alignment */ + 256 /* barriers */;
@@ -249,7 +249,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                         mbar_expect_tx(&full[n], Cfg::kStageBytes);
                         const int kx = (t.kb_begin + i) * TC_BLOCK_K;
                         tma_load_2d(&map_w, &full[n], sa, kx, t.m0);
-                        if (MODE == 2) tma_load_2d(&map_w, &full[n], sa + TC_BLOCK_M * TC_BLOCK_K * 2, kx, a.m_out + t.m0);
                     }
             }
             pdl_wait();
@@ -266,7 +265,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                         if (!ok) break;
                         mbar_expect_tx(&full[stage], Cfg::kStageBytes);
                         tma_load_2d(&map_w, &full[stage], sa, kx, t.m0);
-                        if (MODE == 2) tma_load_2d(&map_w, &full[stage], sa + TC_BLOCK_M * TC_BLOCK_K * 2, kx, a.m_out + t.m0);
                     }
                     tma_load_2d(&map_x, &full[stage], sb, kx, t.n0);
                     if (++stage == Cfg::kStages) { stage = 0; phase ^= 1u; }
@@ -297,9 +295,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                         const uint32_t koff = k * TC_UMMA_K * 2;     // bytes along the 128-byte row
                         const uint32_t accum = (i > 0 || k > 0) ? 1u : 0u;
                         umma_bf16(tmem_d, umma_desc_sw128(sa + koff), umma_desc_sw128(sb + koff), idesc, accum);
-                        if (MODE == 2)
-                            umma_bf16(tmem_d + BLOCK_N, umma_desc_sw128(sa + TC_BLOCK_M * TC_BLOCK_K * 2 + koff),
-                                      umma_desc_sw128(sb + koff), idesc, accum);
                     }
                     umma_commit(&empty[stage]);
                     if (++stage == Cfg::kStages) { stage = 0; phase ^= 1u; }
@@ -320,7 +315,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         TcWalk<BLOCK_N, MODE> walk(a);
         TcUnit t;
         while (ok && walk.next(t)) {
-            const int m = t.m0 + quarter * 32 + lane;
+            // mode 2: every 32 weight rows are 16 gate rows then the 16 up rows of the same outputs,
+            // so a warp's lanes 0..15 hold gate and lanes 16..31 hold up of outputs [m - lane % 16 ...]
+            const int m = (MODE == 2) ? (t.m0 + quarter * 32) / 2 + (lane & 15) : t.m0 + quarter * 32 + lane;
             ok = mbar_wait(&acc_full[buf], (full_phase >> buf) & 1u, abort_flag);
             if (!ok) break;
             tc_fence_after();
@@ -331,12 +328,34 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 float v[16];
                 tmem_ld16(trow + c0, v);
                 if (MODE == 2) {
-                    float up[16];
-                    tmem_ld16(trow + BLOCK_N + c0, up);
+                    // The halves of a warp swap values; the gate half then finishes the even
+                    // columns and the up half the odd ones, so all lanes compute and store.
+                    const bool is_up = (lane & 16) != 0;
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) v[i] = v[i] / (1.f + expf(-v[i])) * up[i];
+                    for (int i = 0; i < 16; ++i) {
+                        const float o = __shfl_xor_sync(0xffffffffu, v[i], 16);
+                        if ((i & 1) == (is_up ? 1 : 0)) {
+                            const float g = is_up ? o : v[i], u = is_up ? v[i] : o;
+                            // silu(g) * u with the fast exponential and division: a few ulp, far inside
+                            // the bfloat16 rounding of the result, and no slow path for the infinities
+                            // that exp(-g) reaches (g / inf = 0 is the right limit)
+                            v[i] = __fdividef(g, 1.f + __expf(-g)) * u;
+                        }
+                    }
+                    if (m < a.m_out) {
+                        const size_t o0 = (size_t)(t.n0 + c0) * a.ldo + m;
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            if ((i & 1) != (is_up ? 1 : 0)) continue;
+                            if (t.n0 + c0 + i >= a.n_rows) break;
+                            if (a.out_dtype == BRAID_F32) ((float*)a.out)[o0 + (size_t)i * a.ldo] = v[i];
+                            else ((__nv_bfloat16*)a.out)[o0 + (size_t)i * a.ldo] = __float2bfloat16_rn(v[i]);
+                        }
+                    }
+                    continue;
                 }
-                if (m < a.m_out) {
+                const bool mine = true;
+                if (mine && m < a.m_out) {
                     if (MODE == 3) {
                         // slot layout [n_rows][128]: this thread's output feature is column quarter * 32 + lane
                         float* dst = (float*)a.out + ((size_t)t.slot * a.n_rows + t.n0 + c0) * TC_BLOCK_M + quarter * 32 + lane;
@@ -392,22 +411,15 @@ __global__ void streamk_reduce_kernel(StreamK k, void* __restrict__ out, const f
     if (i >= (long long)k.n_rows * groups) return;
     const int n = (int)(i / groups), m = (int)(i - (long long)n * groups) * 4;
     float v[4];
-    if (MODE == 2 && (m_out & 3) == 0) {
-        const float4 g4 = streamk_sum4(k, streamk_span(k, n, m), n, m);
-        const float4 u4 = streamk_sum4(k, streamk_span(k, n, m_out + m), n, m_out + m);
+    if (MODE == 2) {
+        // interleaved rows: outputs [16t, 16t+16) have gate in columns 32t.. and up in 32t+16..
+        const int gc = (m / 16) * 32 + (m % 16);
+        const float4 g4 = streamk_sum4(k, streamk_span(k, n, gc), n, gc);
+        const float4 u4 = streamk_sum4(k, streamk_span(k, n, gc + 16), n, gc + 16);
         v[0] = g4.x / (1.f + expf(-g4.x)) * u4.x;
         v[1] = g4.y / (1.f + expf(-g4.y)) * u4.y;
         v[2] = g4.z / (1.f + expf(-g4.z)) * u4.z;
         v[3] = g4.w / (1.f + expf(-g4.w)) * u4.w;
-    } else if (MODE == 2) {
-        // gate column m and up column m_out + m are not aligned alike: element by element
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            if (m + e >= m_out) { v[e] = 0.f; continue; }
-            const float g = streamk_sum(k, streamk_span(k, n, m + e), n, m + e);
-            const float u = streamk_sum(k, streamk_span(k, n, m_out + m + e), n, m_out + m + e);
-            v[e] = g / (1.f + expf(-g)) * u;
-        }
     } else {
         const float4 s4 = streamk_sum4(k, streamk_span(k, n, m), n, m);
         v[0] = s4.x; v[1] = s4.y; v[2] = s4.z; v[3] = s4.w;
@@ -514,7 +526,9 @@ extern "C" long long braid_gemm_tc_workspace_bytes(int n_rows, int w_rows, int k
 }
 
 // x: [n_rows, k_in] bf16 (row stride ldx); w: [w_rows, k_in] bf16 (row stride ldw), where
-// w_rows = m_out, or 2 * m_out for the SwiGLU epilogue.  stream_k != 0 balances the
+// w_rows = m_out; for the SwiGLU epilogue w_rows = 2 * ceil(m_out / 16) * 16 and the rows are
+// interleaved in blocks of 16: block t holds gate rows [16t, 16t+16) then up rows [16t, 16t+16)
+// (rows past m_out are zero).  stream_k != 0 balances the
 // weight stream over all SMs for any shape (meant for a few tokens) and needs
 // `workspace`.  block_n = 0 picks the token tile.  With stream_k and plan_out != null only
 // the partial products are computed; plan_out receives {grid, max_segs, total_kb,
@@ -531,7 +545,7 @@ extern "C" int braid_gemm_tc(const void* x, const void* w, void* out, const floa
     if (mode == 1 && (!res || out_dtype != BRAID_F32)) BRAID_REFUSE("gemm_tc: the residual epilogue writes float32 and needs res");
     if (out_dtype != BRAID_F32 && out_dtype != BRAID_BF16) BRAID_REFUSE("gemm_tc: unknown out dtype code %d", out_dtype);
     if (!error_flag) BRAID_REFUSE("gemm_tc: error_flag is required");
-    const int w_rows = (mode == 2) ? 2 * m_out : m_out;
+    const int w_rows = (mode == 2) ? 2 * ((m_out + 15) / 16) * 16 : m_out;
     if (block_n == 0) block_n = stream_k ? pick_block_n(n_rows) : pick_block_n(n_rows);
     if (stream_k && !workspace) BRAID_REFUSE("gemm_tc: the stream-k form needs a workspace");
     cudaStream_t s = (cudaStream_t)stream;
@@ -543,7 +557,7 @@ extern "C" int braid_gemm_tc(const void* x, const void* w, void* out, const floa
     if (rc) return rc;
 
     if (!stream_k) {
-        const int m_tiles = (m_out + TC_BLOCK_M - 1) / TC_BLOCK_M;
+        const int m_tiles = (w_rows + TC_BLOCK_M - 1) / TC_BLOCK_M;
         const int n_tiles = (n_rows + block_n - 1) / block_n;
         GemmTcArgs a{out, res, n_rows, m_out, k_in, ldo, out_dtype, m_tiles, n_tiles, 0, error_flag};
         const long long units = (long long)m_tiles * n_tiles;

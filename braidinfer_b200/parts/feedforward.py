@@ -23,7 +23,7 @@ class SwiGLU(FeedForward):
         self.inter = int(p["intermediate_size"])
         self.gate_up = Linear(runtime, [prefix + p.get("gate_proj", "mlp.gate_proj.weight"),
                                         prefix + p.get("up_proj", "mlp.up_proj.weight")],
-                              [self.inter, self.inter], self.hidden)
+                              [self.inter, self.inter], self.hidden, gate_up=True)
         self.down = Linear(runtime, [prefix + p.get("down_proj", "mlp.down_proj.weight")], [self.hidden], self.inter)
 
     def tensor_specs(self) -> Dict[str, TensorSpec]:

@@ -19,12 +19,18 @@ _STREAM_K_MAX_ROWS = 64
 
 
 class Linear:
-    def __init__(self, rt, names: Sequence[str], out_features: Sequence[int], in_features: int) -> None:
+    def __init__(self, rt, names: Sequence[str], out_features: Sequence[int], in_features: int,
+                 gate_up: bool = False) -> None:
+        """`gate_up`: the two tensors are the gate and up halves of a SwiGLU; where the
+        tensor-core kernel will run them, they are stored interleaved in blocks of 16 rows
+        for its epilogue instead of stacked."""
         self.rt = rt
         self.names = list(names)
         self.out_features = list(out_features)
         self.in_features = in_features
         self.weight: Optional[torch.Tensor] = None
+        self.gate_up = gate_up
+        self.interleaved = False
 
     def tensor_specs(self) -> Dict[str, TensorSpec]:
         return {n: TensorSpec((o, self.in_features)) for n, o in zip(self.names, self.out_features)}
@@ -33,6 +39,12 @@ class Linear:
         parts = [tensors[n] for n in self.names]
         if len({p.dtype for p in parts}) > 1:
             parts = [p.float() for p in parts]
+        if (self.gate_up and len(parts) == 2 and parts[0].dtype == torch.bfloat16 and self.rt.gemm_backend == "auto"
+                and self.rt.act_dtype == torch.bfloat16 and self.in_features % 8 == 0 and self.rt.kernels is not None):
+            from ..csrc.api import interleave_gate_up
+            self.weight = interleave_gate_up(parts[0], parts[1])
+            self.interleaved = True
+            return
         self.weight = parts[0] if len(parts) == 1 else torch.cat(parts, dim=0).contiguous()
 
     def share(self, weight: torch.Tensor) -> None:
@@ -81,9 +93,12 @@ class Linear:
                 K.gemm_simt(x, w, residual, residual=residual)
             return residual
         if swiglu:
-            inter = w_rows // 2
+            inter = self.out_features[0]
             out = torch.empty((rows, inter), dtype=out_dtype or x.dtype, device=x.device)
-            if use_tc:
+            if self.interleaved:
+                if not use_tc:
+                    raise RuntimeError("interleaved gate/up weights need the tensor-core product; its input rows "
+                                       "must be 16-byte aligned bfloat16")
                 K.gemm_tc(x, w, out, swiglu=True, stream_k=rows <= _STREAM_K_MAX_ROWS)
             else:
                 gu = torch.empty((rows, w_rows), dtype=x.dtype, device=x.device)

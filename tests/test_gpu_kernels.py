@@ -280,15 +280,17 @@ def test_tensor_core_matrix_product(K, n, m, k, sk):
 
 
 @pytest.mark.parametrize("n, inter, k, sk", [(300, 384, 512, False), (17, 200, 96, False), (20, 256, 2048, True),
-                                             (64, 1000, 520, True), (8, 14336, 512, True)])
+                                             (64, 1000, 520, True), (8, 14336, 512, True), (700, 1000, 264, False),
+                                             (2048, 176, 64, False), (5, 63, 128, True)])
 def test_tensor_core_swiglu_epilogue(K, n, inter, k, sk):
+    from braidinfer_b200.csrc.api import interleave_gate_up
     x = rnd(n, k, dtype=torch.bfloat16, scale=0.5)
     w = rnd(2 * inter, k, dtype=torch.bfloat16, scale=0.2, seed=1)
     ref = x.double() @ w.double().t()
     g, u = ref[:, :inter], ref[:, inter:]
     want = g / (1 + torch.exp(-g)) * u
     out = torch.full((n, inter), 9.0, device=DEV, dtype=torch.bfloat16)
-    K.gemm_tc(x, w, out, swiglu=True, stream_k=sk)
+    K.gemm_tc(x, interleave_gate_up(w[:inter], w[inter:]), out, swiglu=True, stream_k=sk)
     assert ((out.double() - want).abs() <= want.abs() / 100 + 1e-3).all()
 
 
