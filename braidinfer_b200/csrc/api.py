@@ -88,6 +88,8 @@ class Kernels:
                                           c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                           c_void_p, c_void_p]
         L.braid_cast.argtypes = [c_void_p, c_int, c_void_p, c_int, c_longlong, c_void_p]
+        L.braid_gather_i32.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_void_p]
+        L.braid_gather_i32.restype = c_int
         L.braid_attn_simple.argtypes = [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                                         c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                         c_float, c_void_p]
@@ -164,6 +166,11 @@ class Kernels:
         self.launches += 1
         self._check(self.lib.braid_cast(src.data_ptr(), dtype_code(src.dtype), dst.data_ptr(),
                                         dtype_code(dst.dtype), src.numel(), self._stream()), "cast")
+
+    def gather_i32(self, src: torch.Tensor, index: torch.Tensor, dst: torch.Tensor) -> None:
+        self.launches += 1
+        self._check(self.lib.braid_gather_i32(src.data_ptr(), index.data_ptr(), dst.data_ptr(), index.numel(),
+                                              self._stream()), "gather_i32")
 
     def rope_kv_write(self, qkv: torch.Tensor, inv_freq: torch.Tensor, positions: torch.Tensor,
                       token_seq: torch.Tensor, page_table: Optional[torch.Tensor], cache: Optional[torch.Tensor],

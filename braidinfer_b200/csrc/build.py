@@ -127,6 +127,12 @@ def build_library(name: str, sources: Sequence[str], defines: Sequence[str] = ()
         tmp_target = work / target.name
         _run([nvcc, "-shared", *ARCH_FLAGS, "-cudart", "static", "-o", str(tmp_target), *objs], "linking")
         os.replace(tmp_target, target)       # atomic: concurrent builders agree on the result
+        for old in out_dir.glob(f"lib{name}-*.so"):      # libraries of earlier sources are of no use
+            if old != target:
+                try:
+                    old.unlink()
+                except OSError:
+                    pass
     finally:
         done.set()
         shutil.rmtree(work, ignore_errors=True)

@@ -406,3 +406,18 @@ extern "C" int braid_cast(const void* in, int in_dtype, void* out, int out_dtype
     else BRAID_REFUSE("cast: unsupported dtype codes %d -> %d", in_dtype, out_dtype);
     BRAID_LAUNCH_CHECK();
 }
+
+// ------------------------------------------------------------------ int32 gather
+// dst[i] = src[index[i]]: feeds the tokens a sampler left on the device into the next step.
+__global__ void gather_i32_kernel(const int* __restrict__ src, const int* __restrict__ index, int* __restrict__ dst, int n) {
+    pdl_trigger();
+    pdl_wait();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) dst[i] = src[index[i]];
+}
+
+extern "C" int braid_gather_i32(const int* src, const int* index, int* dst, int n, void* stream) {
+    if (n <= 0) return BRAID_OK;
+    braid_launch(gather_i32_kernel, dim3((n + 127) / 128), dim3(128), 0, (cudaStream_t)stream, src, index, dst, n);
+    BRAID_LAUNCH_CHECK();
+}

@@ -120,13 +120,19 @@ class Engine:
 
     # ------------------------------------------------------------------ the step
     def step(self, entries: Sequence[Tuple[int, Sequence[int]]],
-             want: Union[str, Sequence[Sequence[int]], None] = "last") -> Optional[torch.Tensor]:
+             want: Union[str, Sequence[Sequence[int]], None] = "last",
+             device_tokens: Optional[Tuple[torch.Tensor, Sequence[int]]] = None) -> Optional[torch.Tensor]:
         """Run `entries` = [(slot, tokens), ...] as one batch.
 
         `want` says whose logits come back: "last" (each sequence's last token), "all",
         None, or for each sequence a list of places among the tokens it brings.
         Returns float32 logits [wanted, vocab] on the device, in the order of the
-        entries and of their wanted places (None if nothing is wanted)."""
+        entries and of their wanted places (None if nothing is wanted).
+
+        `device_tokens` = (int32 tensor on the device, rows): in a step of one token a
+        sequence, take entry i's token from tensor[rows[i]] instead of from `entries`
+        (whose token is then a placeholder), so that a sampler's output can feed the next
+        step without a round trip through the host."""
         if not entries:
             return None
         slots = [int(s) for s, _ in entries]
@@ -151,8 +157,14 @@ class Engine:
         n_new = [len(t) for t in tokens]
         tables = self.cache.begin_step(slots, n_new)
         graphable = self.use_graphs and all(n == 1 for n in n_new)
-        ctx = self.packer.pack(slots, tokens, before, want_l, tables, bucket_tables=graphable)
+        if device_tokens is not None and not all(n == 1 for n in n_new):
+            raise ValueError("device_tokens needs a step of one token a sequence")
+        ctx = self.packer.pack(slots, tokens, before, want_l, tables,
+                               bucket_tables=graphable or device_tokens is not None,
+                               token_source_rows=device_tokens[1] if device_tokens is not None else None)
         ctx.kernels = self.kernels
+        if device_tokens is not None:
+            self.kernels.gather_i32(device_tokens[0], self.packer.token_source_view, ctx.token_ids)
         if graphable:
             logits = self._graph_step(ctx)
         else:

@@ -18,6 +18,8 @@ import time
 from dataclasses import dataclass, field
 from typing import Callable, List, Optional, Sequence, Union
 
+import torch
+
 from ..sampling.params import SamplingParams
 from ..sampling.rng import entropy_seed
 
@@ -74,10 +76,11 @@ def plan_batches(prompt_lens: Sequence[int], max_new_tokens: Sequence[int], capa
 
 
 class GenerationLoop:
-    def __init__(self, engine, sampler, max_batch: int = 64) -> None:
+    def __init__(self, engine, sampler, max_batch: int = 64, pipeline: bool = True) -> None:
         self.engine = engine
         self.sampler = sampler
         self.max_batch = max_batch
+        self.pipeline = pipeline
         self.stats = GenerationStats()
 
     def generate(self, prompts: Sequence[Sequence[int]],
@@ -106,9 +109,74 @@ class GenerationLoop:
         capacity = getattr(self.engine, "max_tokens")
         batches = plan_batches([len(prompts[i]) for i in todo], [mlist[i] for i in todo], capacity,
                                min(self.max_batch, getattr(self.engine, "max_slots", self.max_batch)))
+        pipelined = (self.pipeline and hasattr(self.sampler, "choose_async")
+                     and all(p.repetition_penalty == 1.0 for p in plist))
         for b in batches:
-            self._run_batch([todo[j] for j in b], prompts, plist, seeds, mlist, stop, results)
+            run = self._run_batch_pipelined if pipelined else self._run_batch
+            run([todo[j] for j in b], prompts, plist, seeds, mlist, stop, results)
         return results   # type: ignore[return-value]
+
+    def _run_batch_pipelined(self, ids, prompts, plist, seeds, mlist, stop, results) -> None:
+        """The same decisions as `_run_batch`, with the host off the critical path: the
+        tokens a step chose stay on the device and feed the next step at once, while their
+        copy to the host (for stop tokens and the results) overlaps that step.  A sequence
+        that turns out to have stopped has then run one step too many; its result is
+        dropped and its slot freed.  Sequences known to end by length are not continued."""
+        eng, smp = self.engine, self.sampler
+        self.stats.batches += 1
+        slots = {i: eng.open() for i in ids}
+        generated = {i: [] for i in ids}
+        try:
+            live = list(ids)
+            t0 = time.perf_counter()
+            logits = eng.step([(slots[i], list(prompts[i])) for i in live], want="last")
+            pending = smp.choose_async(logits, [plist[i] for i in live], [seeds[i] for i in live], live,
+                                       [0] * len(live))
+            first = True
+            while live:
+                cont = [i for i in live if len(generated[i]) + 1 < mlist[i]]       # may go on after this token
+                nxt_logits = None
+                if cont:
+                    rows = [live.index(i) for i in cont]
+                    nxt_logits = eng.step([(slots[i], [0]) for i in cont], want="last",
+                                          device_tokens=(pending.device, rows))
+                toks = pending.read()
+                now = time.perf_counter()
+                self.stats.steps += 1
+                if first:
+                    self.stats.prefill_seconds += now - t0
+                    self.stats.prompt_tokens += sum(len(prompts[i]) for i in live)
+                    first = False
+                else:
+                    self.stats.decode_seconds += now - t0
+                    self.stats.decode_tokens += len(live)
+                t0 = now
+                survivors = []
+                for i, tok in zip(live, toks):
+                    if tok in stop:
+                        results[i] = Completion(generated[i], "stop", len(prompts[i]))
+                    else:
+                        generated[i].append(tok)
+                        if len(generated[i]) >= mlist[i]:
+                            results[i] = Completion(generated[i], "length", len(prompts[i]))
+                    if results[i] is not None:
+                        eng.close(slots.pop(i))
+                    else:
+                        survivors.append(i)
+                if survivors:
+                    if survivors != cont:              # some stopped: keep the rows of those that go on
+                        keep = torch.tensor([cont.index(i) for i in survivors], device=nxt_logits.device)
+                        nxt_logits = nxt_logits.index_select(0, keep)
+                    pending = smp.choose_async(nxt_logits, [plist[i] for i in survivors],
+                                               [seeds[i] for i in survivors], survivors,
+                                               [len(generated[i]) for i in survivors])
+                live = survivors
+            check = getattr(eng, "check", None)
+            if check is not None:
+                check()
+        finally:
+            for s in slots.values():
+                eng.close(s)
 
     def _run_batch(self, ids, prompts, plist, seeds, mlist, stop, results) -> None:
         eng = self.engine

@@ -112,12 +112,15 @@ class StepPacker:
         return self._pinned, self._dev
 
     def pack(self, slots: Sequence[int], tokens: Sequence[Sequence[int]], kv_before: Sequence[int],
-             want: Sequence[Sequence[int]], tables: Sequence[np.ndarray], bucket_tables: bool = False) -> StepContext:
+             want: Sequence[Sequence[int]], tables: Sequence[np.ndarray], bucket_tables: bool = False,
+             token_source_rows: Optional[Sequence[int]] = None) -> StepContext:
         """`bucket_tables` widens every page table to a power-of-two number of columns (at
         least 8), so that steps of the same shape lay their tables out identically."""
         n_seqs = len(slots)
         if bucket_tables and all(len(t) == 1 for t in tokens) and all(len(w) <= 1 for w in want):
-            return self._pack_one_token_each(slots, tokens, kv_before, want, tables)
+            return self._pack_one_token_each(slots, tokens, kv_before, want, tables, token_source_rows)
+        if token_source_rows is not None:
+            raise ValueError("tokens can be taken from the device only in steps of one token a sequence")
         if bucket_tables:
             wide = []
             for t in tables:
@@ -167,7 +170,7 @@ class StepPacker:
 
         return self._context(dev, parts, offs, tables, rows, n_tokens, n_seqs, q_len, kv_before, slots, want_rows)
 
-    def _pack_one_token_each(self, slots, tokens, kv_before, want, tables) -> StepContext:
+    def _pack_one_token_each(self, slots, tokens, kv_before, want, tables, token_source_rows=None) -> StepContext:
         """The same layout as `pack` for the common step of generation (one token a
         sequence, page tables widened to a power-of-two width), written straight into the
         pinned buffer."""
@@ -181,7 +184,7 @@ class StepPacker:
         for t in tables:
             cols = max(8, 1 << (t.shape[1] - 1).bit_length())
             wide.append((t, cols))
-        sizes = [rows, rows, rows, n, n, n, n, len(want_rows)] + [n * c for _, c in wide]
+        sizes = [rows, rows, rows, n, n, n, n, len(want_rows)] + [n * c for _, c in wide] + [n]
         offs, total = [], 0
         for sz in sizes:
             offs.append(total)
@@ -208,10 +211,13 @@ class StepPacker:
             v[:, :t.shape[1]] = t
             v[:, t.shape[1]:] = -1
             shapes.append((n, cols))
+        src_k = 8 + len(wide)                       # where each row's token lies in the sampler's output
+        pn[offs[src_k]:offs[src_k] + n] = token_source_rows if token_source_rows is not None else ar
         dev[:total].copy_(pinned[:total], non_blocking=True)
         self._copied = torch.cuda.Event()
         self._copied.record()
         self.h2d_bytes_last = total * 4
+        self.token_source_view = dev[offs[src_k]:offs[src_k] + n]
 
         class _Sized:                      # what `_context` needs of the parts: their sizes
             def __init__(self, size): self.size = size

@@ -77,9 +77,61 @@ class Sampler:
                       bias_off=bo, bias_tok=bt if bias_tok else None, bias_val=bv)
         return self._read(out)
 
+    def choose_async(self, logits: torch.Tensor, params: Sequence[SamplingParams], seeds: Sequence[int],
+                     sequence_ids: Sequence[int], steps: Sequence[int]) -> "PendingTokens":
+        """Like `choose` for rows that need no history (no repetition penalty): launches the
+        choice and the copy of the tokens to pinned host memory and returns at once.  The
+        tokens stay on the device too (`PendingTokens.device`), where the next step can read them."""
+        if any(p.repetition_penalty != 1.0 for p in params):
+            raise ValueError("choose_async cannot apply a repetition penalty: it needs the tokens on the host")
+        rows, vocab = logits.shape
+        out = torch.empty(rows, dtype=torch.int32, device=self.device)
+        if all(p.is_plain_greedy for p in params):
+            self.K.argmax(logits, out)
+        else:
+            f = np.zeros((4, rows), dtype=np.float32)
+            k = np.zeros(rows, dtype=np.int32)
+            bias_off, bias_tok, bias_val = [0], [], []
+            for i, p in enumerate(params):
+                f[0, i], f[1, i], f[2, i] = p.temperature, p.top_p, p.min_p
+                f[3, i] = uniform(seeds[i], sequence_ids[i], steps[i])
+                k[i] = p.top_k
+                for tok, delta in (p.logit_bias or ()):
+                    bias_tok.append(tok)
+                    bias_val.append(delta)
+                bias_off.append(len(bias_tok))
+            fd = torch.from_numpy(f).to(self.device, non_blocking=True)
+            idev = torch.from_numpy(np.concatenate([k, np.asarray(bias_off, np.int32),
+                                                    np.asarray(bias_tok, np.int32)]).astype(np.int32)).to(self.device)
+            bv = torch.tensor(bias_val, dtype=torch.float32, device=self.device) if bias_val else None
+            work = torch.empty((rows, vocab), dtype=torch.float32, device=self.device)
+            self.K.sample(logits, work, out, fd[0], fd[3], top_k=idev[:rows], top_p=fd[1], min_p=fd[2],
+                          bias_off=idev[rows:2 * rows + 1], bias_tok=idev[2 * rows + 1:] if bias_tok else None,
+                          bias_val=bv)
+        host = torch.empty(rows, dtype=torch.int32, pin_memory=True)
+        host.copy_(out, non_blocking=True)
+        done = torch.cuda.Event()
+        done.record()
+        return PendingTokens(self, out, host, done)
+
     def _read(self, out: torch.Tensor) -> List[int]:
         toks = out.tolist()                    # synchronises: the step's results are complete here
         self._draws += 1
         if self._draws % self.CHECK_EVERY == 0:
             self.K.check_device_errors()
         return toks
+
+
+class PendingTokens:
+    """Tokens chosen on the device whose copy to the host is under way."""
+
+    def __init__(self, sampler: Sampler, device: torch.Tensor, host: torch.Tensor, done) -> None:
+        self.sampler, self.device, self.host, self.done = sampler, device, host, done
+
+    def read(self) -> List[int]:
+        self.done.synchronize()
+        s = self.sampler
+        s._draws += 1
+        if s._draws % s.CHECK_EVERY == 0:
+            s.K.check_device_errors()
+        return self.host.tolist()

@@ -110,3 +110,50 @@ def test_edge_cases():
     with pytest.raises(RuntimeError):
         GenerationLoop(eng, ArgmaxSampler()).generate([[1], [2]], max_new_tokens=4)
     assert not eng.live                                               # nothing stays held after an error
+
+
+class DeviceTokenEngine(FakeEngine):
+    """A stand-in whose step can take its tokens from a tensor the sampler left behind."""
+
+    def step(self, entries, want="last", device_tokens=None):
+        if device_tokens is not None:
+            tensor, rows = device_tokens
+            entries = [(s, [int(tensor[r])]) for (s, _), r in zip(entries, rows)]
+        return super().step(entries, want)
+
+
+class AsyncArgmaxSampler(ArgmaxSampler):
+    class Pending:
+        def __init__(self, toks):
+            self.device = torch.tensor(toks, dtype=torch.int32)
+            self._toks = toks
+
+        def read(self):
+            return list(self._toks)
+
+    def choose_async(self, logits, params, seeds, ids, steps):
+        self.async_calls = getattr(self, "async_calls", 0) + 1
+        return self.Pending(logits.argmax(-1).tolist())
+
+
+def test_pipelined_loop_makes_the_same_decisions():
+    prompts = [[1], [20], [7, 8]]
+    kw = dict(max_new_tokens=[6, 6, 2], stop_tokens=[4])
+    want = GenerationLoop(FakeEngine(), ArgmaxSampler()).generate(prompts, **kw)
+    eng, smp = DeviceTokenEngine(), AsyncArgmaxSampler()
+    got = GenerationLoop(eng, smp).generate(prompts, **kw)
+    assert smp.async_calls > 0
+    assert [(o.tokens, o.finish_reason) for o in got] == [(o.tokens, o.finish_reason) for o in want]
+    assert got[0].tokens == [2, 3] and got[0].finish_reason == "stop"
+    assert got[2].tokens == [9, 10] and got[2].finish_reason == "length"
+    assert not eng.live and sorted(eng.closed) == [0, 1, 2]
+    # the sequence that ends by length is not run past its last token; the one that meets
+    # a stop token has run one step too many, whose result is dropped
+    fed = {s: [t for call in eng.calls for (slot, toks) in call for t in toks if slot == s] for s in (0, 1, 2)}
+    assert fed[2] == [7, 8, 9] and fed[0] == [1, 2, 3, 4] and fed[1] == [20, 21, 22, 23, 24, 25]
+    # a repetition penalty needs the tokens on the host: the plain loop runs instead
+    from braidinfer_b200.sampling import SamplingParams
+    smp2 = AsyncArgmaxSampler()
+    GenerationLoop(DeviceTokenEngine(), smp2).generate([[1]], params=SamplingParams(temperature=0.0, repetition_penalty=1.2),
+                                                       max_new_tokens=3)
+    assert getattr(smp2, "async_calls", 0) == 0
