@@ -131,7 +131,7 @@ class Kernels:
         if any(flags):
             self._error_flag.zero_()
             names = ["cache write outside the sequence's pages", "tensor-core GEMM wait ran out",
-                     "NaN among the logits", "attention kernel wait ran out"]
+                     "NaN among the logits", "tcgen05 attention wait ran out"]
             raise KernelError("device error: " + "; ".join(n for n, f in zip(names, flags) if f))
 
     # ------------------------------------------------------------------ row-wise kernels
@@ -212,11 +212,37 @@ class Kernels:
             lib.braid_attn_mma.argtypes = [c_void_p] * 9 + [c_int] * 12 + [c_float, c_void_p]
             lib.braid_attn_mma_partial_floats.restype = c_longlong
             lib.braid_attn_mma_partial_floats.argtypes = [c_int, c_int, c_int]
+            lib.braid_attn_tc_supported.restype = c_int
+            lib.has_tc = bool(lib.braid_attn_tc_supported())
+            if lib.has_tc:
+                lib.braid_attn_tc.restype = c_int
+                lib.braid_attn_tc.argtypes = [c_void_p, c_void_p, c_void_p, c_longlong] + [c_void_p] * 4 + [c_int] * 10 + \
+                                             [c_float, c_void_p, c_void_p]
             lib.braid_attn_mma_decode_slots.restype = c_int
             lib.braid_attn_mma_decode_slots.argtypes = [c_int]
             lib.decode_slots = lib.braid_attn_mma_decode_slots(1)     # CTAs of the few-token kernel held at once
             self._attn_libs[head_dim] = lib
         return lib
+
+    @staticmethod
+    def attn_tc_supports(head_dim: int) -> bool:
+        return head_dim in (64, 128)
+
+    def attn_tc(self, q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, page_table: torch.Tensor,
+                q_start: torch.Tensor, q_len: torch.Tensor, kv_before: torch.Tensor, n_seqs: int, max_q_len: int,
+                nqh: int, nkh: int, hd: int, window: Optional[int], scale: float) -> None:
+        """bfloat16 attention of prompts over the cache on tcgen05 (head sizes 64 and 128)."""
+        lib = self.attn_mma_library(hd)
+        if not lib.has_tc:
+            raise KernelError(f"the tcgen05 attention is built for head sizes 64 and 128, not {hd}")
+        self.launches += 1
+        cache_rows = cache.shape[0] * cache.shape[1] * cache.shape[2] * cache.shape[3]
+        rc = lib.braid_attn_tc(q.data_ptr(), out.data_ptr(), cache.data_ptr(), cache_rows, page_table.data_ptr(),
+                               q_start.data_ptr(), q_len.data_ptr(), kv_before.data_ptr(), q.stride(0), out.stride(0),
+                               out.shape[0], n_seqs, max_q_len, nqh, nkh, hd, page_table.shape[1], int(window or 0),
+                               float(scale), self._error_flag.data_ptr() + 12, self._stream())
+        if rc != 0:
+            raise KernelError(f"attn_tc: {lib.braid_last_error().decode(errors='replace')} (code {rc})")
 
     def attn_decode_slots(self, head_dim: int) -> int:
         return self.attn_mma_library(head_dim).decode_slots

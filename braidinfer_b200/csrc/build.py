@@ -29,7 +29,7 @@ COMMON_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "--expt
 # Sources that do not depend on a model size.
 CORE_SOURCES = ["errors.cu", "elementwise.cu", "attn_simple.cu", "gemm_simt.cu", "gemm_tc.cu",
                 "fused_reduce.cu", "sampling.cu"]
-HEADERS = ["common.cuh", "streamk.cuh", "attn_noalloc.h"]
+HEADERS = ["common.cuh", "streamk.cuh", "tcgen05.cuh", "attn_noalloc.h"]
 
 
 class BuildError(RuntimeError):
@@ -148,5 +148,5 @@ def core_library(verbose: bool = True) -> Path:
 def attention_library(head_dim: int, verbose: bool = True) -> Path:
     """The tensor-core attention kernels compiled for one head size (what a model needs
     is compiled when the model is first built)."""
-    return build_library(f"braidinfer_attn_hd{head_dim}", ["errors.cu", "attn_mma.cu"],
+    return build_library(f"braidinfer_attn_hd{head_dim}", ["errors.cu", "attn_mma.cu", "attn_tc.cu"],
                          defines=[f"-DBRAID_HD={head_dim}"], verbose=verbose)

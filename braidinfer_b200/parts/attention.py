@@ -73,9 +73,11 @@ class GQAAttention(Mixer):
 
     def _attend(self, qkv, out, ctx, cache) -> None:
         """Pick the attention kernel for this step.  float32 runs, and runs that ask for
-        the plain kernels, use the one-warp-per-query kernel for everything; bfloat16
-        runs use the tensor-core kernel, slicing the context when the step brings few
-        tokens so that a handful of sequences still fills the machine."""
+        the plain kernels, use the one-warp-per-query kernel for everything.  bfloat16
+        runs use the tcgen05 kernel for prompts (head sizes 64 and 128; "mma" as the
+        backend keeps them on the mma.sync kernel, which also serves every other head
+        size), and the mma.sync kernel with the context sliced for steps of few tokens,
+        so that a handful of sequences still fills the machine."""
         K = self.rt.kernels
         plain = (self.rt.is_f32 or self.rt.attention_backend == "plain" or not K.attn_mma_supports(self.hd))
         if plain:
@@ -83,6 +85,10 @@ class GQAAttention(Mixer):
                           self.nqh, self.nkh, self.hd, cache.page_size, self.window, self.scale)
             return
         few = ctx.max_q_len <= 8
+        if not few and self.rt.attention_backend == "auto" and K.attn_tc_supports(self.hd):
+            K.attn_tc(qkv, out, cache.storage, cache.page_table, ctx.q_start, ctx.q_len, ctx.kv_before,
+                      ctx.n_seqs, ctx.max_q_len, self.nqh, self.nkh, self.hd, self.window, self.scale)
+            return
         n_splits = 1
         if few:
             g = self.nqh // self.nkh

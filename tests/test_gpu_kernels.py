@@ -170,6 +170,11 @@ def attention_case(K, which, dtype, hd, nqh, nkh, seqs, window, n_splits=1, few=
     out = torch.full((rows + 1, nqh * hd), 9.0, device=DEV, dtype=dtype)
     if which == "simple":
         K.attn_simple(qkv, out, cache, table, t(pos), t(seq), nqh, nkh, hd, 64, window, 1 / math.sqrt(hd))
+    elif which == "tc":
+        out.zero_()
+        K.attn_tc(qkv, out, cache, table, t(q_start), t([n for _, n in seqs]), t([b for b, _ in seqs]),
+                  len(seqs), max(n for _, n in seqs), nqh, nkh, hd, window, 1 / math.sqrt(hd))
+        K.check_device_errors()
     else:
         K.attn_mma(qkv, out, cache, table, t(q_start), t([n for _, n in seqs]), t([b for b, _ in seqs]), t(seq),
                    len(seqs), max(n for _, n in seqs), nqh, nkh, hd, window, 1 / math.sqrt(hd),
@@ -209,6 +214,20 @@ def test_tensor_core_attention_kernel(K, hd, nqh, nkh, seqs, window):
     assert worst < 2e-2
 
 
+@pytest.mark.parametrize("hd, nqh, nkh, seqs, window", [
+    (128, 8, 2, [(0, 300), (100, 50)], None),
+    (128, 32, 8, [(0, 129), (0, 1), (63, 2), (0, 64)], None),
+    (128, 4, 4, [(0, 400)], 130),
+    (128, 6, 2, [(5, 260), (300, 40)], 64),            # a group of 3: 126 of the 128 rows in use
+    (64, 8, 2, [(0, 200), (5, 90)], None),
+    (64, 5, 1, [(0, 270)], 100),
+    (64, 16, 16, [(128, 128)], None),
+])
+def test_tcgen05_attention_kernel(K, hd, nqh, nkh, seqs, window):
+    worst, _, _ = attention_case(K, "tc", torch.bfloat16, hd, nqh, nkh, seqs, window)
+    assert worst < 2e-2
+
+
 @pytest.mark.parametrize("hd, nqh, nkh, seqs, window, splits", [
     (128, 32, 8, [(2047, 1), (100, 1), (0, 1), (63, 1), (64, 1)], None, 8),
     (128, 32, 8, [(700, 1), (100, 1)], 128, 4),
@@ -222,10 +241,10 @@ def test_tensor_core_attention_sliced_context(K, hd, nqh, nkh, seqs, window, spl
     assert worst < 2e-2
 
 
-@pytest.mark.parametrize("which", ["simple", "mma", "mma_sliced"])
+@pytest.mark.parametrize("which", ["simple", "mma", "mma_sliced", "tc"])
 def test_a_far_key_among_hundreds_and_the_windows_edge(K, which):
     kw = dict(n_splits=7, few=True) if which == "mma_sliced" else {}
-    name = "simple" if which == "simple" else "mma"
+    name = which if which in ("simple", "tc") else "mma"
     hd, nqh, nkh = 64, 4, 2
     # a key at position 3, 700 tokens back, owns the softmax: the output is its value
     worst, out, qs = attention_case(K, name, torch.bfloat16, hd, nqh, nkh, [(703, 1)], None, plant=(0, 0, 3), **kw)
