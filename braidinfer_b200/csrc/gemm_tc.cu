@@ -245,34 +245,34 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             if (!ok) break;
             tc_fence_after();
             const uint32_t trow = tmem_base + buf * Cfg::kAccCols + ((uint32_t)(quarter * 32) << 16);
+            constexpr int CH = BLOCK_N >= 32 ? 32 : 16;       // columns per tensor-memory load and wait
 #pragma unroll 1
-            for (int c0 = 0; c0 < BLOCK_N; c0 += 16) {
+            for (int c0 = 0; c0 < BLOCK_N; c0 += CH) {
                 if (t.n0 + c0 >= a.n_rows) break;
-                float v[16];
-                tmem_ld16(trow + c0, v);
+                float v[CH];
+                if (CH == 32) tmem_ld32(trow + c0, v);
+                else tmem_ld16(trow + c0, v);
                 if (MODE == 2) {
                     // The halves of a warp swap values; the gate half then finishes the even
                     // columns and the up half the odd ones, so all lanes compute and store.
                     const bool is_up = (lane & 16) != 0;
+                    const size_t o0 = (size_t)(t.n0 + c0 + (is_up ? 1 : 0)) * a.ldo + m;
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        const float o = __shfl_xor_sync(0xffffffffu, v[i], 16);
-                        if ((i & 1) == (is_up ? 1 : 0)) {
-                            const float g = is_up ? o : v[i], u = is_up ? v[i] : o;
-                            // silu(g) * u with the fast exponential and division: a few ulp, far inside
-                            // the bfloat16 rounding of the result, and no slow path for the infinities
-                            // that exp(-g) reaches (g / inf = 0 is the right limit)
-                            v[i] = __fdividef(g, 1.f + __expf(-g)) * u;
-                        }
-                    }
-                    if (m < a.m_out) {
-                        const size_t o0 = (size_t)(t.n0 + c0) * a.ldo + m;
-#pragma unroll
-                        for (int i = 0; i < 16; ++i) {
-                            if ((i & 1) != (is_up ? 1 : 0)) continue;
-                            if (t.n0 + c0 + i >= a.n_rows) break;
-                            if (a.out_dtype == BRAID_F32) ((float*)a.out)[o0 + (size_t)i * a.ldo] = v[i];
-                            else ((__nv_bfloat16*)a.out)[o0 + (size_t)i * a.ldo] = __float2bfloat16_rn(v[i]);
+                    for (int p2 = 0; p2 < CH / 2; ++p2) {
+                        // columns 2 p2 (finished by the gate half) and 2 p2 + 1 (by the up half): every
+                        // lane computes, none idles
+                        const float from_up = __shfl_xor_sync(0xffffffffu, v[2 * p2], 16);        // gate lanes get up's value
+                        const float from_gate = __shfl_xor_sync(0xffffffffu, v[2 * p2 + 1], 16);  // up lanes get gate's value
+                        const float g = is_up ? from_gate : v[2 * p2];
+                        const float u = is_up ? v[2 * p2 + 1] : from_up;
+                        // silu(g) * u with the fast exponential and division: a few ulp, far inside
+                        // the bfloat16 rounding of the result, and no slow path for the infinities
+                        // that exp(-g) reaches (g / inf = 0 is the right limit)
+                        const float y = __fdividef(g, 1.f + __expf(-g)) * u;
+                        const int n = t.n0 + c0 + 2 * p2 + (is_up ? 1 : 0);
+                        if (m < a.m_out && n < a.n_rows) {
+                            if (a.out_dtype == BRAID_F32) ((float*)a.out)[o0 + (size_t)(2 * p2) * a.ldo] = y;
+                            else ((__nv_bfloat16*)a.out)[o0 + (size_t)(2 * p2) * a.ldo] = __float2bfloat16_rn(y);
                         }
                     }
                     continue;
@@ -283,22 +283,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                         // slot layout [n_rows][128]: this thread's output feature is column quarter * 32 + lane
                         float* dst = (float*)a.out + ((size_t)t.slot * a.n_rows + t.n0 + c0) * TC_BLOCK_M + quarter * 32 + lane;
 #pragma unroll
-                        for (int i = 0; i < 16; ++i)
+                        for (int i = 0; i < CH; ++i)
                             if (t.n0 + c0 + i < a.n_rows) dst[(size_t)i * TC_BLOCK_M] = v[i];
                     } else if (MODE == 1) {
                         // all loads of the residual first: out may be res itself, which would
                         // otherwise chain every load behind the store before it
                         const size_t o0 = (size_t)(t.n0 + c0) * a.ldo + m;
-                        float r[16];
+                        float r[CH];
 #pragma unroll
-                        for (int i = 0; i < 16; ++i) r[i] = (t.n0 + c0 + i < a.n_rows) ? a.res[o0 + (size_t)i * a.ldo] : 0.f;
+                        for (int i = 0; i < CH; ++i) r[i] = (t.n0 + c0 + i < a.n_rows) ? a.res[o0 + (size_t)i * a.ldo] : 0.f;
 #pragma unroll
-                        for (int i = 0; i < 16; ++i)
+                        for (int i = 0; i < CH; ++i)
                             if (t.n0 + c0 + i < a.n_rows) ((float*)a.out)[o0 + (size_t)i * a.ldo] = r[i] + v[i];
                     } else {
                         const size_t o0 = (size_t)(t.n0 + c0) * a.ldo + m;
 #pragma unroll
-                        for (int i = 0; i < 16; ++i) {
+                        for (int i = 0; i < CH; ++i) {
                             if (t.n0 + c0 + i >= a.n_rows) break;
                             if (a.out_dtype == BRAID_F32) ((float*)a.out)[o0 + (size_t)i * a.ldo] = v[i];
                             else ((__nv_bfloat16*)a.out)[o0 + (size_t)i * a.ldo] = __float2bfloat16_rn(v[i]);
