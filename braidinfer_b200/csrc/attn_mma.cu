@@ -77,7 +77,9 @@ __global__ void __launch_bounds__(NW * 32)
 attn_mma_kernel(AttnMmaArgs a) {
     using C = AttnCfg<HD, NW, BN, ST>;
     pdl_trigger();
-    pdl_wait();
+    // What follows up to pdl_wait() reads only the step's tables (copied to the device before
+    // the step's first kernel) and keys and values of positions cached by earlier steps,
+    // which no kernel of this step writes; the queries and the step's own keys come after it.
     extern __shared__ __align__(16) uint8_t smem[];
     uint8_t* sQ = smem;
     uint8_t* sKV = smem + C::Q_BYTES;
@@ -107,17 +109,7 @@ attn_mma_kernel(AttnMmaArgs a) {
     const int head0 = kvh * g + hchunk * hpc;              // first query head of this CTA
     const int n_heads = min(hpc, g - hchunk * hpc);
 
-    // ---- queries into shared memory (rows of absent tokens or heads are zero)
     constexpr int CH = HD / 8;                             // 16-byte chunks per row
-    for (int i = tid; i < C::BM * CH; i += NW * 32) {
-        const int r = i / CH, c = i - r * CH;
-        const int tl = r / hpc, hl = r - tl * hpc;
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (tl < n_tok && hl < n_heads)
-            v = *reinterpret_cast<const uint4*>(a.q + (size_t)(q_start + tok0 + tl) * a.q_row_stride + (size_t)(head0 + hl) * HD + c * 8);
-        *reinterpret_cast<uint4*>(sQ + r * C::ROW + c * 16) = v;
-    }
-
     auto load_tile = [&](int t, int stage) {
         const int key0 = t * BN;
         const int page = table[key0 / PAGE];
@@ -132,11 +124,30 @@ attn_mma_kernel(AttnMmaArgs a) {
             cp_async16(dv + r * C::ROW + c * 16, vbase + (size_t)r * HD + c * 8);
         }
     };
+    // the first tiles of the ring; those that hold only positions cached before this step
+    // are asked for at once, the others after the wait
+    bool early[ST - 1];
+#pragma unroll
+    for (int s = 0; s < ST - 1; ++s) {
+        early[s] = s < n_tiles && (t_lo + s + 1) * BN <= kv_before;
+        if (early[s]) load_tile(t_lo + s, s);
+    }
+    pdl_wait();
+
+    // ---- queries into shared memory (rows of absent tokens or heads are zero)
+    for (int i = tid; i < C::BM * CH; i += NW * 32) {
+        const int r = i / CH, c = i - r * CH;
+        const int tl = r / hpc, hl = r - tl * hpc;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (tl < n_tok && hl < n_heads)
+            v = *reinterpret_cast<const uint4*>(a.q + (size_t)(q_start + tok0 + tl) * a.q_row_stride + (size_t)(head0 + hl) * HD + c * 8);
+        *reinterpret_cast<uint4*>(sQ + r * C::ROW + c * 16) = v;
+    }
 
 #pragma unroll
     for (int s = 0; s < ST - 1; ++s) {
-        if (s < n_tiles) load_tile(t_lo + s, s);
-        cp_async_commit();
+        if (s < n_tiles && !early[s]) load_tile(t_lo + s, s);
+        cp_async_commit();                               // one group a stage, as the loop below counts them
     }
 
     // per-thread rows: r0 = lane / 4 and r0 + 8 of this warp's 16
@@ -268,6 +279,9 @@ attn_mma_kernel(AttnMmaArgs a) {
 }
 
 // Merge the slices of one (row, head): out = sum_s O_s 2^(m_s - M) / sum_s l_s 2^(m_s - M).
+// A thread owns output dimensions; it loads every slice's (m, l, O_d) at once (the loads do
+// not depend on one another) and repeats the few scalar sums of the row itself.
+#define COMBINE_MAX_SPLITS 64
 template <int HD>
 __global__ void attn_combine_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ out,
                                     const int* __restrict__ token_seq, int out_row_stride, int nqh, int n_splits) {
@@ -276,21 +290,34 @@ __global__ void attn_combine_kernel(const float* __restrict__ partial, __nv_bflo
     const int row = blockIdx.x, head = blockIdx.y;
     if (token_seq[row] < 0) return;
     const float* p = partial + ((size_t)row * nqh + head) * n_splits * (HD + 2);
-    float M = -INFINITY;
-    for (int s = 0; s < n_splits; ++s) M = fmaxf(M, p[s * (HD + 2)]);
-    float L = 0.f;
-    for (int s = 0; s < n_splits; ++s) {
-        const float m = p[s * (HD + 2)];
-        if (m != -INFINITY) L += p[s * (HD + 2) + 1] * exp2f(m - M);
-    }
-    const float inv = 1.f / L;
     for (int d = threadIdx.x; d < HD; d += blockDim.x) {
-        float acc = 0.f;
-        for (int s = 0; s < n_splits; ++s) {
-            const float m = p[s * (HD + 2)];
-            if (m != -INFINITY) acc += p[s * (HD + 2) + 2 + d] * exp2f(m - M);
+        float M = -INFINITY, L = 0.f, acc = 0.f;
+        for (int s0 = 0; s0 < n_splits; s0 += 8) {
+            float m[8], l[8], o[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const bool in = s0 + i < n_splits;
+                const float* ps = p + (size_t)(in ? s0 + i : 0) * (HD + 2);
+                m[i] = in ? ps[0] : -INFINITY;
+                l[i] = in ? ps[1] : 0.f;
+                o[i] = in ? ps[2 + d] : 0.f;
+            }
+            float Mn = M;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) Mn = fmaxf(Mn, m[i]);
+            if (Mn == -INFINITY) continue;
+            const float c = exp2f(M - Mn);                 // exp2(-inf) = 0 the first time
+            L *= c;
+            acc *= c;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float wgt = (m[i] == -INFINITY) ? 0.f : exp2f(m[i] - Mn);
+                L = fmaf(l[i], wgt, L);
+                acc = fmaf(o[i], wgt, acc);
+            }
+            M = Mn;
         }
-        out[(size_t)row * out_row_stride + (size_t)head * HD + d] = __float2bfloat16_rn(acc * inv);
+        out[(size_t)row * out_row_stride + (size_t)head * HD + d] = __float2bfloat16_rn(acc / L);
     }
 }
 

@@ -23,7 +23,6 @@ __global__ void __launch_bounds__(RN_THREADS)
 streamk_reduce_norm_kernel(StreamK k, float* h, const TW* __restrict__ w, TO* __restrict__ out,
                            const int* __restrict__ row_index, int width, float eps) {
     pdl_trigger();
-    pdl_wait();
     __shared__ float red[32];
     __shared__ float my_ss;
     cg::cluster_group cluster = cg::this_cluster();
@@ -36,11 +35,16 @@ streamk_reduce_norm_kernel(StreamK k, float* h, const TW* __restrict__ w, TO* __
     const int g0 = rank * per, g1 = min(groups, g0 + per);
     TO* o = out + (size_t)r * width;
     float ss = 0.f;
+    // where this thread's first group of partial sums lies is worked out before the wait
+    const int g_first = g0 + threadIdx.x;
+    StreamKSpan sp_first = {};
+    if (src >= 0 && g_first < g1) sp_first = streamk_span(k, src, g_first * 4);
+    pdl_wait();
     if (src >= 0) {
         float* hr = h + (size_t)src * width;
         for (int g = g0 + threadIdx.x; g < g1; g += RN_THREADS) {
             const int c = g * 4;
-            const float4 s4 = streamk_sum4(k, streamk_span(k, src, c), src, c);
+            const float4 s4 = streamk_sum4(k, g == g_first ? sp_first : streamk_span(k, src, c), src, c);
             const float s[4] = {s4.x, s4.y, s4.z, s4.w};
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
@@ -125,7 +129,8 @@ struct ReduceRopeArgs {
 
 __global__ void streamk_reduce_rope_kv_kernel(ReduceRopeArgs a) {
     pdl_trigger();
-    pdl_wait();
+    // Up to pdl_wait(): the step's tables (on the device before the step's first kernel), the
+    // rotation angle and the places of the partial sums; the partial sums themselves after it.
     const int row = blockIdx.x;
     const int seq = a.token_seq[row];
     if (seq < 0) return;
@@ -150,14 +155,29 @@ __global__ void streamk_reduce_rope_kv_kernel(ReduceRopeArgs a) {
     }
     const int half = a.rope_dim / 2;
     if (is_q || is_k) {
+        // the first pair of this thread (the only one when head_dim / 2 <= blockDim.x)
+        const int p_first = threadIdx.x;
+        float sn0 = 0.f, cs0 = 1.f;
+        StreamKSpan sp0 = {}, sp1 = {};
+        if (p_first < half) {
+            sincosf((float)pos * a.inv_freq[p_first], &sn0, &cs0);
+            sp0 = streamk_span(a.k, row, col0 + (a.adjacent ? 2 * p_first : p_first));
+            sp1 = streamk_span(a.k, row, col0 + (a.adjacent ? 2 * p_first + 1 : p_first + half));
+        }
+        pdl_wait();
         for (int p = threadIdx.x; p < half; p += blockDim.x) {
             const int i0 = a.adjacent ? 2 * p : p;
             const int i1 = a.adjacent ? 2 * p + 1 : p + half;
+            float sn = sn0, cs = cs0;
+            StreamKSpan s0 = sp0, s1 = sp1;
+            if (p != p_first) {
+                sincosf((float)pos * a.inv_freq[p], &sn, &cs);
+                s0 = streamk_span(a.k, row, col0 + i0);
+                s1 = streamk_span(a.k, row, col0 + i1);
+            }
             // the product is rounded to bfloat16 before it is rotated, as after a plain product
-            const float x0 = __bfloat162float(__float2bfloat16_rn(streamk_sum(a.k, streamk_span(a.k, row, col0 + i0), row, col0 + i0)));
-            const float x1 = __bfloat162float(__float2bfloat16_rn(streamk_sum(a.k, streamk_span(a.k, row, col0 + i1), row, col0 + i1)));
-            float sn, cs;
-            sincosf((float)pos * a.inv_freq[p], &sn, &cs);
+            const float x0 = __bfloat162float(__float2bfloat16_rn(streamk_sum(a.k, s0, row, col0 + i0)));
+            const float x1 = __bfloat162float(__float2bfloat16_rn(streamk_sum(a.k, s1, row, col0 + i1)));
             const __nv_bfloat16 y0 = __float2bfloat16_rn(x0 * cs - x1 * sn);
             const __nv_bfloat16 y1 = __float2bfloat16_rn(x0 * sn + x1 * cs);
             dst_row[i0] = y0;
@@ -170,8 +190,13 @@ __global__ void streamk_reduce_rope_kv_kernel(ReduceRopeArgs a) {
             if (dst) dst[i] = y;
         }
     } else {
+        const int i_first = threadIdx.x;
+        StreamKSpan sp0 = {};
+        if (i_first < a.hd) sp0 = streamk_span(a.k, row, col0 + i_first);
+        pdl_wait();
         for (int i = threadIdx.x; i < a.hd; i += blockDim.x) {
-            const __nv_bfloat16 y = __float2bfloat16_rn(streamk_sum(a.k, streamk_span(a.k, row, col0 + i), row, col0 + i));
+            const StreamKSpan s0 = (i == i_first) ? sp0 : streamk_span(a.k, row, col0 + i);
+            const __nv_bfloat16 y = __float2bfloat16_rn(streamk_sum(a.k, s0, row, col0 + i));
             dst_row[i] = y;
             if (dst) dst[i] = y;
         }

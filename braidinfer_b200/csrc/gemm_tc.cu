@@ -328,23 +328,27 @@ template <int MODE>
 __global__ void streamk_reduce_kernel(StreamK k, void* __restrict__ out, const float* __restrict__ res,
                                       int m_out, long long ldo, int out_dtype) {
     pdl_trigger();
-    pdl_wait();
     const int groups = (m_out + 3) / 4;
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= (long long)k.n_rows * groups) return;
     const int n = (int)(i / groups), m = (int)(i - (long long)n * groups) * 4;
+    // where the partial sums lie is arithmetic only: done before the wait for the product
+    // interleaved rows (mode 2): outputs [16t, 16t+16) have gate in columns 32t.. and up in 32t+16..
+    const int c0 = (MODE == 2) ? (m / 16) * 32 + (m % 16) : m;
+    const StreamKSpan sp0 = streamk_span(k, n, c0);
+    StreamKSpan sp1 = sp0;
+    if (MODE == 2) sp1 = streamk_span(k, n, c0 + 16);
+    pdl_wait();
     float v[4];
     if (MODE == 2) {
-        // interleaved rows: outputs [16t, 16t+16) have gate in columns 32t.. and up in 32t+16..
-        const int gc = (m / 16) * 32 + (m % 16);
-        const float4 g4 = streamk_sum4(k, streamk_span(k, n, gc), n, gc);
-        const float4 u4 = streamk_sum4(k, streamk_span(k, n, gc + 16), n, gc + 16);
+        const float4 g4 = streamk_sum4(k, sp0, n, c0);
+        const float4 u4 = streamk_sum4(k, sp1, n, c0 + 16);
         v[0] = g4.x / (1.f + expf(-g4.x)) * u4.x;
         v[1] = g4.y / (1.f + expf(-g4.y)) * u4.y;
         v[2] = g4.z / (1.f + expf(-g4.z)) * u4.z;
         v[3] = g4.w / (1.f + expf(-g4.w)) * u4.w;
     } else {
-        const float4 s4 = streamk_sum4(k, streamk_span(k, n, m), n, m);
+        const float4 s4 = streamk_sum4(k, sp0, n, c0);
         v[0] = s4.x; v[1] = s4.y; v[2] = s4.z; v[3] = s4.w;
     }
 #pragma unroll
