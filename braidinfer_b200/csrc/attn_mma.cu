@@ -352,29 +352,18 @@ extern "C" long long braid_attn_mma_partial_floats(int rows, int nqh, int n_spli
 // CTAs of the few-token kernel (kind 1) that the device holds at once: the context is
 // best sliced so that one wave of CTAs covers the step.
 extern "C" int braid_attn_mma_decode_slots(int kind) {
+    (void)kind;
     int dev = 0, sms = 0, per_sm = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    cudaError_t e;
-    if (kind == 2) {
-        using C = AttnCfg<BRAID_HD, 1, 64, 2>;
-        cudaFuncSetAttribute(attn_mma_kernel<BRAID_HD, 1, 64, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM);
-        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attn_mma_kernel<BRAID_HD, 1, 64, 2>, 32, C::SMEM);
-    } else if (kind == 3) {
-        using C = AttnCfg<BRAID_HD, 2, 32, 3>;
-        cudaFuncSetAttribute(attn_mma_kernel<BRAID_HD, 2, 32, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM);
-        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attn_mma_kernel<BRAID_HD, 2, 32, 3>, 64, C::SMEM);
-    } else {
-        using C = AttnCfg<BRAID_HD, 1, 32, 3>;
-        cudaFuncSetAttribute(attn_mma_kernel<BRAID_HD, 1, 32, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM);
-        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attn_mma_kernel<BRAID_HD, 1, 32, 3>, 32, C::SMEM);
-    }
+    using C = AttnCfg<BRAID_HD, 1, 32, 3>;
+    cudaFuncSetAttribute(attn_mma_kernel<BRAID_HD, 1, 32, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM);
+    cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attn_mma_kernel<BRAID_HD, 1, 32, 3>, 32, C::SMEM);
     if (e != cudaSuccess || per_sm <= 0 || sms <= 0) return 148 * 4;
     return per_sm * sms;
 }
 
-// kind 0: many tokens per sequence (4 warps, tiles of 64 keys); kind 1: few (1 warp, tiles of 32 keys);
-// kinds 2 and 3 are other shapes of the few-token kernel (1 warp x 64 keys, 2 warps x 32 keys).
+// kind 0: many tokens per sequence (4 warps, tiles of 64 keys); kind 1: few (1 warp, tiles of 32 keys).
 extern "C" int braid_attn_mma(const void* q, void* out, void* partial, const void* cache, const int* page_table,
                               const int* q_start, const int* q_len, const int* kv_before, const int* token_seq,
                               int q_row_stride, int out_row_stride, int rows, int n_seqs, int max_q_len,
@@ -393,8 +382,6 @@ extern "C" int braid_attn_mma(const void* q, void* out, void* partial, const voi
     cudaStream_t s = (cudaStream_t)stream;
     int rc;
     if (kind == 0) rc = launch_attn<4, 64, 2>(a, n_seqs, max_q_len, s);
-    else if (kind == 2) rc = launch_attn<1, 64, 2>(a, n_seqs, max_q_len, s);
-    else if (kind == 3) rc = launch_attn<2, 32, 3>(a, n_seqs, max_q_len, s);
     else rc = launch_attn<1, 32, 3>(a, n_seqs, max_q_len, s);
     if (rc) return rc;
     if (n_splits > 1) {

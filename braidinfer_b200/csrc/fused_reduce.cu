@@ -38,7 +38,13 @@ streamk_reduce_norm_kernel(StreamK k, float* h, const TW* __restrict__ w, TO* __
     // where this thread's first group of partial sums lies is worked out before the wait
     const int g_first = g0 + threadIdx.x;
     StreamKSpan sp_first = {};
-    if (src >= 0 && g_first < g1) sp_first = streamk_span(k, src, g_first * 4);
+    float w_first[4] = {0.f, 0.f, 0.f, 0.f};              // the norm's weights of that group: no kernel writes them
+    if (src >= 0 && g_first < g1) {
+        sp_first = streamk_span(k, src, g_first * 4);
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+            if (g_first * 4 + e < width) w_first[e] = to_f32(w[g_first * 4 + e]);
+    }
     pdl_wait();
     if (src >= 0) {
         float* hr = h + (size_t)src * width;
@@ -79,7 +85,7 @@ streamk_reduce_norm_kernel(StreamK k, float* h, const TW* __restrict__ w, TO* __
         for (int e = 0; e < 4; ++e) {
             if (c + e >= width) break;
             const float v = hr[c + e] + s[e];             // written back above by this very thread, or recomputed
-            o[c + e] = from_f32<TO>(v * scale * to_f32(w[c + e]));
+            o[c + e] = from_f32<TO>(v * scale * (g == g_first ? w_first[e] : to_f32(w[c + e])));
         }
     }
 }
