@@ -127,3 +127,152 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped(dtype):
         assert (lg.double().cpu() - want[0]).abs().max() < tol
     finally:
         MIXERS.unregister("toy_running_mean")
+
+
+# ---------------------------------------------------------------------------------------------
+# A toy feed-forward with routing and a toy position encoding, also defined here only.
+#
+# The feed-forward has two experts (small two-layer perceptrons with a tanh) and a router;
+# each token goes to the expert with the larger router logit (the lower index on a tie) and
+# its output is weighted by the softmax probability of that expert.  The position encoding
+# rotates nothing: it adds a learned vector per position (up to 256 positions) to queries
+# and keys and then stores keys and values with the library's own cache-write kernel.
+from braidinfer_b200.parts import FEED_FORWARDS, POSITION_ENCODINGS, FeedForward, PositionEncoding
+
+
+class TopOneExperts(FeedForward):
+    graph_safe = False          # it gathers rows by a data-dependent index: a CUDA graph cannot replay that
+
+    def __init__(self, params, prefix, runtime):
+        super().__init__(params, prefix, runtime)
+        self.width, self.inner, self.n = int(params["width"]), int(params["inner"]), int(params["experts"])
+        self.prefix = prefix
+
+    def tensor_specs(self):
+        d = {self.prefix + "toy.router.weight": TensorSpec((self.n, self.width))}
+        for e in range(self.n):
+            d[self.prefix + f"toy.experts.{e}.w1.weight"] = TensorSpec((self.inner, self.width))
+            d[self.prefix + f"toy.experts.{e}.w2.weight"] = TensorSpec((self.width, self.inner))
+        return d
+
+    def load(self, tensors):
+        self.router = tensors[self.prefix + "toy.router.weight"].float()
+        self.w1 = [tensors[self.prefix + f"toy.experts.{e}.w1.weight"].float() for e in range(self.n)]
+        self.w2 = [tensors[self.prefix + f"toy.experts.{e}.w2.weight"].float() for e in range(self.n)]
+
+    def forward(self, x, residual, ctx):
+        xf = x.float()
+        logits = xf @ self.router.t()                           # router logits in float32
+        prob = torch.softmax(logits, -1)
+        choice = logits.argmax(-1)
+        out = residual.clone()
+        for e in range(self.n):
+            rows = (choice == e).nonzero().flatten()
+            if rows.numel():
+                y = torch.tanh(xf[rows] @ self.w1[e].t()) @ self.w2[e].t()
+                out[rows] += prob[rows, e:e + 1] * y
+        return out
+
+
+class LearnedOffsets(PositionEncoding):
+    def __init__(self, params, prefix, runtime):
+        super().__init__(params, prefix, runtime)
+        self.hd, self.max_pos = int(params["head_dim"]), int(params["max_positions"])
+        self.name = prefix + "toy.position.weight"
+        self.zero_freq = torch.zeros(self.hd // 2, dtype=torch.float32, device=runtime.device)
+
+    def tensor_specs(self):
+        return {self.name: TensorSpec((self.max_pos, self.hd))}
+
+    def load(self, tensors):
+        self.table = tensors[self.name]
+
+    def encode_and_store(self, qkv, nqh, nkh, ctx, cache):
+        rows = ctx.n_tokens
+        pos = ctx.positions[:rows].long()
+        view = qkv[:rows].view(rows, nqh + 2 * nkh, self.hd)
+        view[:, :nqh + nkh] += self.table[pos].to(qkv.dtype)[:, None, :]
+        # angle zero: the library's kernel leaves queries and keys as they are and stores keys and values
+        writable = cache is not None and not cache.read_only
+        self.rt.kernels.rope_kv_write(qkv, self.zero_freq, ctx.positions, ctx.token_seq,
+                                      cache.page_table if writable else None, cache.storage if writable else None,
+                                      nqh, nkh, self.hd, self.hd, False, cache.page_size if cache is not None else 1)
+
+
+def plain_toy_model_2(weights, cfg, tokens):
+    import plain_mistral as P
+    w = {k: v.double() for k, v in weights.items()}
+    T = len(tokens)
+    nqh, nkh, hd = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+    h = P.embedding(w["model.embed_tokens.weight"], tokens, torch.float64)
+    for layer in range(cfg.num_hidden_layers):
+        pre = f"model.layers.{layer}."
+        n = P.rmsnorm(h, w[pre + "input_layernorm.weight"], cfg.rms_norm_eps)
+        off = w[pre + "toy.position.weight"][:T]
+        q = P.linear(n, w[pre + "self_attn.q_proj.weight"]).view(T, nqh, hd) + off[:, None, :]
+        k = P.linear(n, w[pre + "self_attn.k_proj.weight"]).view(T, nkh, hd) + off[:, None, :]
+        v = P.linear(n, w[pre + "self_attn.v_proj.weight"]).view(T, nkh, hd)
+        h = h + P.linear(P.attention(q, k, v, cfg.layer_window(layer)).reshape(T, nqh * hd), w[pre + "self_attn.o_proj.weight"])
+        n = P.rmsnorm(h, w[pre + "post_attention_layernorm.weight"], cfg.rms_norm_eps)
+        logits = n @ w[pre + "toy.router.weight"].t()
+        prob = torch.softmax(logits, -1)
+        choice = logits.argmax(-1)
+        y = torch.zeros_like(h)
+        for e in range(2):
+            m = choice == e
+            y[m] = prob[m, e:e + 1] * (torch.tanh(n[m] @ w[pre + f"toy.experts.{e}.w1.weight"].t())
+                                       @ w[pre + f"toy.experts.{e}.w2.weight"].t())
+        h = h + y
+    h = P.rmsnorm(h, w["model.norm.weight"], cfg.rms_norm_eps)
+    return P.linear(h, w["lm_head.weight"]), None
+
+
+def test_toy_routed_feed_forward_and_toy_position_encoding():
+    from braidinfer_b200.cache import CacheManager
+    from braidinfer_b200.engine import Engine
+    from braidinfer_b200.models import DecoderModel, architecture_for
+    from braidinfer_b200.weights import draw_tensors
+    from tiny import TINY_A, random_prompts
+    FEED_FORWARDS.register("toy_top_one_experts", TopOneExperts)
+    POSITION_ENCODINGS.register("toy_learned_offsets", LearnedOffsets)
+    try:
+        arch = architecture_for(TINY_A)
+        cfg = arch.config_from_dict(TINY_A)
+        base = arch.build_spec(cfg)
+        layers = []
+        for ls in base.layers:
+            mp = dict(ls.mixer.params)
+            mp["position_encoding"] = PartSpec("toy_learned_offsets", {"head_dim": cfg.head_dim, "max_positions": 256})
+            layers.append(dataclasses.replace(
+                ls, mixer=PartSpec("gqa_attention", mp),
+                feed_forward=PartSpec("toy_top_one_experts", {"width": cfg.hidden_size, "inner": 40, "experts": 2})))
+        spec = dataclasses.replace(base, layers=tuple(layers))
+        eng = Engine.from_random(TINY_A, 0, dtype="float32", max_tokens=512, max_slots=3, verbose=False)
+        eng.spec = spec
+        eng.model = DecoderModel(spec, eng.rt)
+        specs = eng.model.tensor_specs()
+        assert "model.layers.1.toy.experts.1.w2.weight" in specs and "model.layers.0.mlp.gate_proj.weight" not in specs
+        drawn = draw_tensors(specs, 9)
+        for n_ in drawn:                                   # make the routing decisive and the offsets matter
+            if n_.endswith("toy.router.weight") or n_.endswith("toy.position.weight"):
+                drawn[n_] = (drawn[n_].float() * 20).bfloat16()
+        eng.model.load({n_: t.to(eng.device).float() for n_, t in drawn.items()})
+        eng.cache = CacheManager(eng.model.cache_plan(), 512, 3, eng.dtype, eng.device)
+        eng.use_graphs = all(p.graph_safe for p in eng.model.all_parts())
+        assert eng.use_graphs is False
+        prompts = random_prompts(cfg.vocab_size, [70, 9], seed=3)
+        w64 = {n_: t.double() for n_, t in drawn.items()}
+        want = [plain_toy_model_2(w64, cfg, p)[0] for p in prompts]
+        slots = [eng.open() for _ in prompts]
+        cut = [66, 5]
+        got = eng.step([(s, p[:c]) for s, p, c in zip(slots, prompts, cut)], want="all")
+        assert (got[:66].double().cpu() - want[0][:66]).abs().max() < 2e-5
+        assert (got[66:].double().cpu() - want[1][:5]).abs().max() < 2e-5
+        for t in range(4):
+            out = eng.step([(slots[i], [prompts[i][cut[i] + t]]) for i in range(2)], want="last")
+            for i in range(2):
+                assert (out[i].double().cpu() - want[i][cut[i] + t]).abs().max() < 2e-5
+        eng.check()
+    finally:
+        FEED_FORWARDS.unregister("toy_top_one_experts")
+        POSITION_ENCODINGS.unregister("toy_learned_offsets")
