@@ -34,18 +34,23 @@ def parse_dtype(name: Union[str, torch.dtype]) -> torch.dtype:
 
 
 class Engine:
-    def __init__(self, config_dict: Mapping, tensors_or_folder, *, dtype="bfloat16", max_tokens: int = 8192,
+    def __init__(self, config_dict: Optional[Mapping], tensors_or_folder, *, dtype="bfloat16", max_tokens: int = 8192,
                  max_slots: Optional[int] = None, device: str = "cuda:0", gemm_backend: str = "auto",
                  attention_backend: str = "auto", row_multiple: int = 1, use_graphs: bool = True,
-                 fuse_reduce: bool = True, verbose: bool = True) -> None:
+                 fuse_reduce: bool = True, verbose: bool = True, spec=None) -> None:
+        """`config_dict` (config.json's content) picks the architecture and its description of
+        parts; or pass a `ModelSpec` as `spec` directly (then `config_dict` may be None)."""
         from ..csrc.api import get_kernels
         self.dtype = parse_dtype(dtype)
         self.device = torch.device(device)
         torch.cuda.set_device(self.device)
         self.kernels = get_kernels(verbose=verbose)
-        self.arch = architecture_for(config_dict)
-        self.config = self.arch.config_from_dict(config_dict)
-        self.spec = self.arch.build_spec(self.config)
+        if spec is None:
+            self.arch = architecture_for(config_dict)
+            self.config = self.arch.config_from_dict(config_dict)
+            self.spec = self.arch.build_spec(self.config)
+        else:
+            self.arch, self.config, self.spec = None, None, spec
         self.rt = Runtime(act_dtype=self.dtype, device=self.device, kernels=self.kernels,
                           gemm_backend=gemm_backend, attention_backend=attention_backend, fuse_reduce=fuse_reduce)
         self.model = DecoderModel(self.spec, self.rt)
@@ -77,6 +82,24 @@ class Engine:
     def from_folder(cls, folder: str, **kw) -> "Engine":
         """A model folder: config.json picks the architecture, safetensors hold the weights."""
         return cls(read_config_json(folder), folder, **kw)
+
+    @classmethod
+    def from_spec(cls, spec, seed: int = 0, *, dtype="bfloat16", device: str = "cuda:0", scale=None, **kw) -> "Engine":
+        """A model described by a `ModelSpec` (any mix of registered parts) with seeded random
+        weights: the tensors its parts ask for are drawn as `write_random_model` draws them.
+        `scale` maps a tensor-name suffix to a factor (for tests that want peaked routers or
+        attention).  Returns the engine; `engine.drawn` keeps the CPU tensors it was built from."""
+        run_dtype = parse_dtype(dtype)
+        drawn = draw_tensors(tensor_specs_of(spec), seed, torch.bfloat16)
+        for suffix, factor in (scale or {}).items():
+            for name in drawn:
+                if name.endswith(suffix):
+                    drawn[name] = (drawn[name].float() * factor).to(torch.bfloat16)
+        dev = torch.device(device)
+        tensors = {n: (t.to(dev) if run_dtype == torch.bfloat16 else t.to(dev).float()) for n, t in drawn.items()}
+        eng = cls(None, tensors, dtype=dtype, device=device, spec=spec, **kw)
+        eng.drawn = drawn
+        return eng
 
     @classmethod
     def from_random(cls, config_dict: Mapping, seed: int = 0, *, dtype="bfloat16", device: str = "cuda:0",

@@ -176,15 +176,11 @@ def test_block_and_schedule_against_the_plain_model(tmp_path):
     toks = random_prompts(cfg.vocab_size, [75], seed=1)[0]
     want = P.forward_logits(read_weights(folder), cfg, toks, torch.float64,
                             schedule=[(0, None), (1, None), (0, None), (1, 1)])
+    from braidinfer_b200.weights import load_tensors, tensor_specs_of
     for dtype in ("float32", "bfloat16"):
-        eng = Engine.from_folder(folder, dtype=dtype, max_tokens=256, verbose=False)
-        # swap the description for the hand-written one and rebuild model and cache from it
-        from braidinfer_b200.models import DecoderModel
-        from braidinfer_b200.weights import load_tensors
-        eng.spec = spec
-        eng.model = DecoderModel(spec, eng.rt)
-        eng.model.load(load_tensors(folder, eng.model.tensor_specs(), eng.dtype, eng.device))
-        eng.cache = CacheManager(eng.model.cache_plan(), 256, 4, eng.dtype, eng.device)
+        run_dtype = torch.float32 if dtype == "float32" else torch.bfloat16
+        tensors = load_tensors(folder, tensor_specs_of(spec), run_dtype, "cuda:0")
+        eng = Engine(None, tensors, spec=spec, dtype=dtype, max_tokens=256, max_slots=4, verbose=False)
         assert eng.cache.groups[0].storage.shape[0] == 3          # three runs keep a cache, one borrows
         s = eng.open()
         got = [eng.step([(s, toks[:70])], want="all")] + [eng.step([(s, [t])], want="last") for t in toks[70:]]

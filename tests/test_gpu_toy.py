@@ -87,18 +87,11 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped(dtype):
         base = arch.build_spec(cfg)
         toy_layer = dataclasses.replace(base.layers[0], mixer=PartSpec("toy_running_mean", {"width": cfg.hidden_size}))
         spec = dataclasses.replace(base, layers=(toy_layer, base.layers[1]))
-        # an engine of the stock model first, then the description is swapped and rebuilt
-        eng = Engine.from_random(TINY_A, 0, dtype=dtype, max_tokens=512, max_slots=3, verbose=False)
-        eng.spec = spec
-        eng.model = DecoderModel(spec, eng.rt)
+        eng = Engine.from_spec(spec, 5, dtype=dtype, max_tokens=512, max_slots=3, verbose=False)
         specs = eng.model.tensor_specs()
         assert "model.layers.0.toy.mix.weight" in specs and "model.layers.0.self_attn.q_proj.weight" not in specs
-        drawn = draw_tensors(specs, 5)
-        eng.model.load({n: (t.to(eng.device) if dtype == "bfloat16" else t.to(eng.device).float())
-                        for n, t in drawn.items()})
-        eng.cache = CacheManager(eng.model.cache_plan(), 512, 3, eng.dtype, eng.device)
-        eng.use_graphs = all(p.graph_safe for p in eng.model.all_parts())
-        assert eng.use_graphs is False
+        drawn = eng.drawn
+        assert eng.use_graphs is False               # the toy mixer said it cannot be replayed by a graph
         assert eng.cache.state_view(0).shape == (3, 4 * (cfg.hidden_size + 1)) and eng.cache.state_view(1) is None
         assert len(eng.cache.groups) == 1 and eng.cache.groups[0].storage.shape[0] == 1     # only layer 1 keeps keys
 
@@ -247,18 +240,12 @@ def test_toy_routed_feed_forward_and_toy_position_encoding():
                 ls, mixer=PartSpec("gqa_attention", mp),
                 feed_forward=PartSpec("toy_top_one_experts", {"width": cfg.hidden_size, "inner": 40, "experts": 2})))
         spec = dataclasses.replace(base, layers=tuple(layers))
-        eng = Engine.from_random(TINY_A, 0, dtype="float32", max_tokens=512, max_slots=3, verbose=False)
-        eng.spec = spec
-        eng.model = DecoderModel(spec, eng.rt)
+        # scaled so that the routing is decisive and the offsets matter
+        eng = Engine.from_spec(spec, 9, dtype="float32", max_tokens=512, max_slots=3, verbose=False,
+                               scale={"toy.router.weight": 20.0, "toy.position.weight": 20.0})
         specs = eng.model.tensor_specs()
         assert "model.layers.1.toy.experts.1.w2.weight" in specs and "model.layers.0.mlp.gate_proj.weight" not in specs
-        drawn = draw_tensors(specs, 9)
-        for n_ in drawn:                                   # make the routing decisive and the offsets matter
-            if n_.endswith("toy.router.weight") or n_.endswith("toy.position.weight"):
-                drawn[n_] = (drawn[n_].float() * 20).bfloat16()
-        eng.model.load({n_: t.to(eng.device).float() for n_, t in drawn.items()})
-        eng.cache = CacheManager(eng.model.cache_plan(), 512, 3, eng.dtype, eng.device)
-        eng.use_graphs = all(p.graph_safe for p in eng.model.all_parts())
+        drawn = eng.drawn
         assert eng.use_graphs is False
         prompts = random_prompts(cfg.vocab_size, [70, 9], seed=3)
         w64 = {n_: t.double() for n_, t in drawn.items()}
