@@ -46,6 +46,7 @@ streamk_reduce_norm_kernel(StreamK k, float* h, const TW* __restrict__ w, TO* __
             if (g_first * 4 + e < width) w_first[e] = to_f32(w[g_first * 4 + e]);
     }
     pdl_wait();
+    float v_first[4] = {0.f, 0.f, 0.f, 0.f};              // the new h of this thread's first group stays in registers
     if (src >= 0) {
         float* hr = h + (size_t)src * width;
         for (int g = g0 + threadIdx.x; g < g1; g += RN_THREADS) {
@@ -57,6 +58,7 @@ streamk_reduce_norm_kernel(StreamK k, float* h, const TW* __restrict__ w, TO* __
                 if (c + e >= width) break;
                 const float v = hr[c + e] + s[e];
                 if (write_back) hr[c + e] = v;
+                if (g == g_first) v_first[e] = v;
                 ss = fmaf(v, v, ss);
             }
         }
@@ -66,28 +68,34 @@ streamk_reduce_norm_kernel(StreamK k, float* h, const TW* __restrict__ w, TO* __
     cluster.sync();
     float total = 0.f;
     for (int b = 0; b < csize; ++b) total += *cluster.map_shared_rank(&my_ss, b);
-    cluster.sync();                                       // nobody leaves while its sum may still be read
     if (src < 0) {
         for (int g = g0 + threadIdx.x; g < g1; g += RN_THREADS)
             for (int e = 0; e < 4 && g * 4 + e < width; ++e) o[g * 4 + e] = from_f32<TO>(0.f);
-        return;
-    }
-    const float scale = rsqrtf(total / (float)width + eps);
-    const float* hr = h + (size_t)src * width;
-    for (int g = g0 + threadIdx.x; g < g1; g += RN_THREADS) {
-        const int c = g * 4;
-        float s[4] = {0.f, 0.f, 0.f, 0.f};
-        if (!write_back) {
-            const float4 s4 = streamk_sum4(k, streamk_span(k, src, c), src, c);
-            s[0] = s4.x; s[1] = s4.y; s[2] = s4.z; s[3] = s4.w;
-        }
+    } else {
+        const float scale = rsqrtf(total / (float)width + eps);
+        const float* hr = h + (size_t)src * width;
+        for (int g = g0 + threadIdx.x; g < g1; g += RN_THREADS) {
+            const int c = g * 4;
+            if (g == g_first) {
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            if (c + e >= width) break;
-            const float v = hr[c + e] + s[e];             // written back above by this very thread, or recomputed
-            o[c + e] = from_f32<TO>(v * scale * (g == g_first ? w_first[e] : to_f32(w[c + e])));
+                for (int e = 0; e < 4; ++e)
+                    if (c + e < width) o[c + e] = from_f32<TO>(v_first[e] * scale * w_first[e]);
+                continue;
+            }
+            float s[4] = {0.f, 0.f, 0.f, 0.f};
+            if (!write_back) {
+                const float4 s4 = streamk_sum4(k, streamk_span(k, src, c), src, c);
+                s[0] = s4.x; s[1] = s4.y; s[2] = s4.z; s[3] = s4.w;
+            }
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                if (c + e >= width) break;
+                const float v = hr[c + e] + s[e];             // written back above by this very thread, or recomputed
+                o[c + e] = from_f32<TO>(v * scale * to_f32(w[c + e]));
+            }
         }
     }
+    cluster.sync();                                       // nobody leaves while its sum may still be read
 }
 
 extern "C" int braid_streamk_reduce_norm(const float* partial, const int* plan, int n_rows, float* h, const void* w,
