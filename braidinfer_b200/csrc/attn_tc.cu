@@ -2,18 +2,22 @@
 // (tcgen05), compiled for one head size: -DBRAID_HD=64 or 128.
 //
 // A CTA owns 128 rows: the query heads of one kv head (up to 128 of them) for 128 / heads
-// consecutive tokens of one sequence, and walks the visible keys in tiles of 128 (two
-// 64-position pages).
+// consecutive tokens of one sequence, and walks the visible keys one 64-position page at
+// a time.  Two CTAs share an SM (half its shared memory, tensor memory and registers
+// each), so that one's chain of dependent steps runs under the other's.
 //
-//   warp 0      TMA: the query tile once, then key and value tiles into a two-stage ring
-//               (cp.async.bulk.tensor, 128-byte swizzle, no multicast);
+//   warp 0      TMA: the query tile once, then key tiles and value tiles into two rings of
+//               two stages (cp.async.bulk.tensor, 128-byte swizzle, no multicast);
 //   warp 1      one lane issues S = Q K^T (accumulator in tensor memory, two buffers) and,
-//               once the softmax warps have written P, O_tile = P V;
-//   warps 2..9  two threads per row, 64 keys and 64 output dimensions each: read S from
-//               tensor memory, mask, running maximum (the two halves of a row meet in shared
-//               memory) and denominator in float32, P = exp2(s - m) rounded to bfloat16 into
-//               shared memory (the A operand of the second product), then add O_tile into the
-//               row's float32 output held in registers, rescaled when the maximum moved.
+//               once the softmax warps have written P, O += P V, accumulated in tensor memory;
+//   warps 2..5  one thread per row: read the 64 scores of S from tensor memory, mask,
+//               running maximum and denominator in float32, P = exp2(s - m) rounded to
+//               bfloat16 into shared memory (the A operand of the second product).
+//
+// The running maximum m is only raised when a tile's maximum exceeds it by more than 8
+// (in the exponent of two), and then the thread scales its row of O in tensor memory by
+// exp2(m_old - m_new) before the next product adds to it.  In between, probabilities are
+// at most 2^8; the denominator is taken against the same m, so the quotient is exact.
 //
 // Keys are K-major for the first product; values are read MN-major by the second one,
 // straight from the [position][head_dim] layout of the cache, so nothing is transposed.
@@ -35,17 +39,18 @@
 #define BRAID_ATTN_TC 1
 
 #define FA_BM 128
-#define FA_BN 128
+#define FA_BN 64                                 // keys per tile: one page
 #define FA_PAGE 64
-#define FA_THREADS 320                          // TMA warp, MMA warp, 8 softmax warps
+#define FA_THREADS 192                           // TMA warp, MMA warp, 4 softmax warps
 #define FA_HB (BRAID_HD / 64)                    // 64-element blocks of the head dimension
-#define FA_BLOCK_BYTES (128 * 128)               // [128 rows][64 elements] bf16, 128-byte rows
-#define FA_Q_BYTES (FA_HB * FA_BLOCK_BYTES)
-#define FA_KV_BYTES (FA_HB * FA_BLOCK_BYTES)     // one K or one V tile
-#define FA_STAGE_BYTES (2 * FA_KV_BYTES)
-#define FA_P_BYTES (2 * FA_BLOCK_BYTES)
-#define FA_SMEM (FA_Q_BYTES + 2 * FA_STAGE_BYTES + FA_P_BYTES + 1024 + 128 + 2 * 2 * 128 * 4)
-#define FA_TMEM_COLS 512                          // S0 [0,128) S1 [128,256) O_tile [256, 256 + HD)
+#define FA_QBLOCK_BYTES (128 * 128)              // [128 rows][64 elements] bf16, 128-byte rows
+#define FA_KBLOCK_BYTES (64 * 128)               // [64 positions][64 elements]
+#define FA_Q_BYTES (FA_HB * FA_QBLOCK_BYTES)
+#define FA_KV_BYTES (FA_HB * FA_KBLOCK_BYTES)    // one K or one V tile
+#define FA_P_BYTES (128 * 128)                   // [128 rows][64 keys]
+#define FA_SMEM (FA_Q_BYTES + 4 * FA_KV_BYTES + FA_P_BYTES + 128)
+#define FA_TMEM_COLS 256                         // S0 [0,64) S1 [64,128) O [128, 128 + HD)
+#define FA_RAISE 8.f                             // how far a tile's maximum may exceed m before m is raised
 
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;
@@ -72,13 +77,27 @@ __device__ __forceinline__ void tmem_ld32x2(uint32_t taddr, float* v) {
 #pragma unroll
     for (int i = 0; i < 64; ++i) v[i] = __uint_as_float(r[i]);
 }
-// BRAID_HD / 2 consecutive columns (32 or 64).
-__device__ __forceinline__ void tmem_ld_od(uint32_t taddr, float* v) {
-#if BRAID_HD == 128
-    tmem_ld32x2(taddr, v);
-#else
-    tmem_ld32(taddr, v);
-#endif
+// The reverse: 64 consecutive columns of this thread's lane written back.
+__device__ __forceinline__ void tmem_st32x2(uint32_t taddr, const float* v) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h)
+        asm volatile(
+            "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+            "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+            :: "r"(taddr + h * 32),
+               "r"(__float_as_uint(v[h * 32 + 0])), "r"(__float_as_uint(v[h * 32 + 1])), "r"(__float_as_uint(v[h * 32 + 2])),
+               "r"(__float_as_uint(v[h * 32 + 3])), "r"(__float_as_uint(v[h * 32 + 4])), "r"(__float_as_uint(v[h * 32 + 5])),
+               "r"(__float_as_uint(v[h * 32 + 6])), "r"(__float_as_uint(v[h * 32 + 7])), "r"(__float_as_uint(v[h * 32 + 8])),
+               "r"(__float_as_uint(v[h * 32 + 9])), "r"(__float_as_uint(v[h * 32 + 10])), "r"(__float_as_uint(v[h * 32 + 11])),
+               "r"(__float_as_uint(v[h * 32 + 12])), "r"(__float_as_uint(v[h * 32 + 13])), "r"(__float_as_uint(v[h * 32 + 14])),
+               "r"(__float_as_uint(v[h * 32 + 15])), "r"(__float_as_uint(v[h * 32 + 16])), "r"(__float_as_uint(v[h * 32 + 17])),
+               "r"(__float_as_uint(v[h * 32 + 18])), "r"(__float_as_uint(v[h * 32 + 19])), "r"(__float_as_uint(v[h * 32 + 20])),
+               "r"(__float_as_uint(v[h * 32 + 21])), "r"(__float_as_uint(v[h * 32 + 22])), "r"(__float_as_uint(v[h * 32 + 23])),
+               "r"(__float_as_uint(v[h * 32 + 24])), "r"(__float_as_uint(v[h * 32 + 25])), "r"(__float_as_uint(v[h * 32 + 26])),
+               "r"(__float_as_uint(v[h * 32 + 27])), "r"(__float_as_uint(v[h * 32 + 28])), "r"(__float_as_uint(v[h * 32 + 29])),
+               "r"(__float_as_uint(v[h * 32 + 30])), "r"(__float_as_uint(v[h * 32 + 31]))
+            : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 
 struct AttnTcArgs {
@@ -89,30 +108,37 @@ struct AttnTcArgs {
     const int* kv_before;
     int out_row_stride, nqh, nkh, table_cols, window;
     float scale_log2;
+    int num_pages;
     int* error_flag;
 };
 
-__global__ void __launch_bounds__(FA_THREADS, 1)
+__global__ void __launch_bounds__(FA_THREADS, 2)
 attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv, AttnTcArgs a) {
     constexpr int HD = BRAID_HD;
     pdl_trigger();
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    // the swizzled tiles want 1024-byte alignment; two CTAs an SM leave no room for slack, so
+    // the start of dynamic shared memory is checked instead of rounded up
+    extern __shared__ __align__(1024) uint8_t smem[];
+    if (smem_u32(smem) & 1023u) {
+        if (threadIdx.x == 0) atomicExch(a.error_flag, 1);
+        return;
+    }
     uint8_t* sQ = smem;
-    uint8_t* sKV = sQ + FA_Q_BYTES;
-    uint8_t* sP = sKV + 2 * FA_STAGE_BYTES;
+    uint8_t* sK = sQ + FA_Q_BYTES;                 // [2 stages]
+    uint8_t* sV = sK + 2 * FA_KV_BYTES;            // [2 stages]
+    uint8_t* sP = sV + 2 * FA_KV_BYTES;
     uint64_t* bars = (uint64_t*)(sP + FA_P_BYTES);
     uint64_t* q_full = bars;            // [1]
-    uint64_t* kv_full = bars + 1;       // [2]
-    uint64_t* kv_empty = bars + 3;      // [2]
-    uint64_t* s_full = bars + 5;        // [2]
-    uint64_t* s_empty = bars + 7;       // [2]
-    uint64_t* p_ready = bars + 9;       // [1]
-    uint64_t* o_full = bars + 10;       // [1]
-    uint64_t* o_empty = bars + 11;      // [1]
-    uint32_t* tmem_slot = (uint32_t*)(bars + 12);
+    uint64_t* k_full = bars + 1;        // [2]
+    uint64_t* k_empty = bars + 3;       // [2]
+    uint64_t* v_full = bars + 5;        // [2]
+    uint64_t* v_empty = bars + 7;       // [2]
+    uint64_t* s_full = bars + 9;        // [2]
+    uint64_t* s_empty = bars + 11;      // [2]
+    uint64_t* p_ready = bars + 13;      // [1]
+    uint64_t* pv_done = bars + 14;      // [1]
+    uint32_t* tmem_slot = (uint32_t*)(bars + 15);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
-    float* xchg = (float*)(bars + 16);                    // [2 parities][2 halves][128 rows]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = a.nqh / a.nkh;
@@ -126,10 +152,11 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
         for (int s = 0; s < 2; ++s) {
-            mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1);
-            mbar_init(&s_full[s], 1); mbar_init(&s_empty[s], 256);
+            mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1);
+            mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1);
+            mbar_init(&s_full[s], 1); mbar_init(&s_empty[s], 128);
         }
-        mbar_init(p_ready, 256); mbar_init(o_full, 1); mbar_init(o_empty, 256);
+        mbar_init(p_ready, 128); mbar_init(pv_done, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -139,6 +166,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tmem_o = tmem_base + 128;
     pdl_wait();
 
     const int q_len = a.q_len[seq];
@@ -158,32 +186,31 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             mbar_expect_tx(q_full, (uint32_t)(hpc * tpc * 128 * FA_HB));      // the box is hpc x tpc rows of 128 bytes
 #pragma unroll
             for (int hb = 0; hb < FA_HB; ++hb)
-                tma_load_3d(&map_q, q_full, sQ + hb * FA_BLOCK_BYTES, hb * 64, head0, q_start + tok0);
+                tma_load_3d(&map_q, q_full, sQ + hb * FA_QBLOCK_BYTES, hb * 64, head0, q_start + tok0);
             const int* table = a.page_table + (size_t)seq * a.table_cols;
             bool ok = true;
             for (int j = 0; j < n_tiles && ok; ++j) {
                 const int st = j & 1;
-                ok = mbar_wait(&kv_empty[st], (uint32_t)((j >> 1) & 1) ^ 1u, abort_flag);
-                if (!ok) break;
-                uint8_t* sK = sKV + st * FA_STAGE_BYTES;
-                uint8_t* sV = sK + FA_KV_BYTES;
-                mbar_expect_tx(&kv_full[st], FA_STAGE_BYTES);
-                const int block0 = (t_lo + j) * (FA_BN / FA_PAGE);
-                const int page0 = table[block0];
-#pragma unroll
-                for (int pg = 0; pg < FA_BN / FA_PAGE; ++pg) {
-                    // a page the sequence does not have (yet) is stood in for by the tile's first
-                    // page: its keys are masked, and its values are finite
-                    int page = (block0 + pg < a.table_cols) ? table[block0 + pg] : -1;
-                    if (page < 0) page = page0;
-                    const int krow = ((page * 2 + 0) * a.nkh + kvh) * FA_PAGE;
-                    const int vrow = ((page * 2 + 1) * a.nkh + kvh) * FA_PAGE;
-#pragma unroll
-                    for (int hb = 0; hb < FA_HB; ++hb) {
-                        tma_load_2d(&map_kv, &kv_full[st], sK + hb * FA_BLOCK_BYTES + pg * FA_PAGE * 128, hb * 64, krow);
-                        tma_load_2d(&map_kv, &kv_full[st], sV + hb * FA_BLOCK_BYTES + pg * FA_PAGE * 128, hb * 64, vrow);
-                    }
+                const uint32_t ph = (uint32_t)((j >> 1) & 1) ^ 1u;
+                int page = (t_lo + j < a.table_cols) ? table[t_lo + j] : -1;
+                if (page < 0 || page >= a.num_pages) {          // a visible position without a page: the table is broken
+                    atomicExch(a.error_flag, 1);
+                    page = 0;
                 }
+                const int krow = ((page * 2 + 0) * a.nkh + kvh) * FA_PAGE;
+                const int vrow = ((page * 2 + 1) * a.nkh + kvh) * FA_PAGE;
+                ok = mbar_wait(&k_empty[st], ph, abort_flag);
+                if (!ok) break;
+                mbar_expect_tx(&k_full[st], FA_KV_BYTES);
+#pragma unroll
+                for (int hb = 0; hb < FA_HB; ++hb)
+                    tma_load_2d(&map_kv, &k_full[st], sK + st * FA_KV_BYTES + hb * FA_KBLOCK_BYTES, hb * 64, krow);
+                ok = mbar_wait(&v_empty[st], ph, abort_flag);
+                if (!ok) break;
+                mbar_expect_tx(&v_full[st], FA_KV_BYTES);
+#pragma unroll
+                for (int hb = 0; hb < FA_HB; ++hb)
+                    tma_load_2d(&map_kv, &v_full[st], sV + st * FA_KV_BYTES + hb * FA_KBLOCK_BYTES, hb * 64, vrow);
             }
         }
     } else if (warp == 1) {
@@ -192,105 +219,119 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             constexpr uint32_t idesc_pv = umma_idesc_bf16_b_mn(FA_BM, HD);
             bool ok = mbar_wait(q_full, 0, abort_flag);
             auto issue_pv = [&](int i) -> bool {
-                if (!mbar_wait(p_ready, (uint32_t)(i & 1), abort_flag)) return false;
-                if (!mbar_wait(o_empty, (uint32_t)(i & 1) ^ 1u, abort_flag)) return false;
+                const int st = i & 1;
+                if (!mbar_wait(&v_full[st], (uint32_t)((i >> 1) & 1), abort_flag)) return false;
+                if (!mbar_wait(p_ready, (uint32_t)(i & 1), abort_flag)) return false;     // P written, O rescaled
                 tc_fence_after();
-                const uint32_t sV = smem_u32(sKV + (i & 1) * FA_STAGE_BYTES + FA_KV_BYTES);
+                const uint32_t sVa = smem_u32(sV + st * FA_KV_BYTES);
                 const uint32_t sPa = smem_u32(sP);
 #pragma unroll
                 for (int ks = 0; ks < FA_BN / 16; ++ks)
-                    umma_bf16(tmem_base + 256,
-                              umma_desc_sw128(sPa + (ks >> 2) * FA_BLOCK_BYTES + (ks & 3) * 32),
-                              umma_desc_sw128_mn(sV + ks * 16 * 128, FA_BLOCK_BYTES), idesc_pv, ks > 0 ? 1u : 0u);
-                umma_commit(o_full);
-                umma_commit(&kv_empty[i & 1]);
+                    umma_bf16(tmem_o, umma_desc_sw128(sPa + ks * 32),
+                              umma_desc_sw128_mn(sVa + ks * 16 * 128, FA_KBLOCK_BYTES), idesc_pv, (i > 0 || ks > 0) ? 1u : 0u);
+                umma_commit(pv_done);
+                umma_commit(&v_empty[st]);
                 return true;
             };
             for (int j = 0; j < n_tiles && ok; ++j) {
                 const int st = j & 1;
                 const uint32_t ph = (uint32_t)((j >> 1) & 1);
-                ok = mbar_wait(&kv_full[st], ph, abort_flag) && mbar_wait(&s_empty[st], ph ^ 1u, abort_flag);
+                ok = mbar_wait(&k_full[st], ph, abort_flag) && mbar_wait(&s_empty[st], ph ^ 1u, abort_flag);
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t sQa = smem_u32(sQ), sK = smem_u32(sKV + st * FA_STAGE_BYTES);
+                const uint32_t sQa = smem_u32(sQ), sKa = smem_u32(sK + st * FA_KV_BYTES);
 #pragma unroll
-                for (int ks = 0; ks < HD / 16; ++ks) {
-                    const uint32_t off = (ks >> 2) * FA_BLOCK_BYTES + (ks & 3) * 32;
-                    umma_bf16(tmem_base + st * 128, umma_desc_sw128(sQa + off), umma_desc_sw128(sK + off), idesc_qk,
-                              ks > 0 ? 1u : 0u);
-                }
+                for (int ks = 0; ks < HD / 16; ++ks)
+                    umma_bf16(tmem_base + st * FA_BN,
+                              umma_desc_sw128(sQa + (ks >> 2) * FA_QBLOCK_BYTES + (ks & 3) * 32),
+                              umma_desc_sw128(sKa + (ks >> 2) * FA_KBLOCK_BYTES + (ks & 3) * 32), idesc_qk, ks > 0 ? 1u : 0u);
                 umma_commit(&s_full[st]);
+                umma_commit(&k_empty[st]);
                 if (j > 0) ok = issue_pv(j - 1);
             }
             if (ok && n_tiles > 0) issue_pv(n_tiles - 1);
         }
     } else if (active) {
         const int quarter = warp & 3;                          // tensor-memory lanes 32 * quarter ...
-        const int half = (warp - 2) >> 2;                      // keys / output dims [64 * half, 64 * half + 64)
         const int r = quarter * 32 + lane;                     // this thread's row
         const int tl = r / hpc, hl = r - tl * hpc;
         const bool valid = tl < n_tok && hl < n_heads;
         const int pos = valid ? pos_min + tl : -1;
         const int lo = (a.window > 0) ? pos - a.window + 1 : 0;
         const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
-        constexpr int OD = HD / 2;                             // output dimensions a thread keeps
-        float o[OD];
-#pragma unroll
-        for (int i = 0; i < OD; ++i) o[i] = 0.f;
-        float m = -INFINITY, l = 0.f, corr_prev = 1.f;
+        float m = -INFINITY, l = 0.f;
         bool ok = true;
         for (int j = 0; j < n_tiles && ok; ++j) {
             const int st = j & 1;
             ok = mbar_wait(&s_full[st], (uint32_t)((j >> 1) & 1), abort_flag);
+            ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
-            const int key0 = (t_lo + j) * FA_BN + half * 64;
-            const bool all_visible = ((t_lo + j) * FA_BN + FA_BN - 1 <= pos_min) &&
-                                     (a.window == 0 || (t_lo + j) * FA_BN >= pos_max - a.window + 1);
             float sv[64];
-            tmem_ld32x2(tmem_base + st * 128 + half * 64 + lane_addr, sv);
-            float mx = -INFINITY;
+            tmem_ld32x2(tmem_base + st * FA_BN + lane_addr, sv);
+            tc_fence_before();
+            mbar_arrive(&s_empty[st]);                         // the scores are in registers: the buffer may take tile j + 2
+            const int key0 = (t_lo + j) * FA_BN;
+            const bool all_visible = (key0 + FA_BN - 1 <= pos_min) && (a.window == 0 || key0 >= pos_max - a.window + 1);
+            float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
             if (all_visible) {
                 if (valid) {
 #pragma unroll
-                    for (int i = 0; i < 64; ++i) mx = fmaxf(mx, sv[i]);
+                    for (int i = 0; i < 64; i += 4) {
+                        mx0 = fmaxf(mx0, sv[i]); mx1 = fmaxf(mx1, sv[i + 1]);
+                        mx2 = fmaxf(mx2, sv[i + 2]); mx3 = fmaxf(mx3, sv[i + 3]);
+                    }
                 }
             } else {
 #pragma unroll
-                for (int i = 0; i < 64; ++i) {
-                    const int key = key0 + i;
-                    if (!(key <= pos && key >= lo)) sv[i] = -INFINITY;
-                    mx = fmaxf(mx, sv[i]);
+                for (int i = 0; i < 64; i += 4) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int key = key0 + i + e;
+                        if (!(key <= pos && key >= lo)) sv[i + e] = -INFINITY;
+                    }
+                    mx0 = fmaxf(mx0, sv[i]); mx1 = fmaxf(mx1, sv[i + 1]);
+                    mx2 = fmaxf(mx2, sv[i + 2]); mx3 = fmaxf(mx3, sv[i + 3]);
                 }
             }
-            // the two halves of the row agree on the maximum
-            float* xm = xchg + (j & 1) * 256;
-            xm[half * 128 + r] = mx;
-            asm volatile("bar.sync 1, 256;" ::: "memory");
-            mx = fmaxf(mx, xm[(half ^ 1) * 128 + r]) * a.scale_log2;   // scale > 0 commutes with the maximum
-            const float m_new = fmaxf(m, mx);
-            const float ms = (m_new == -INFINITY) ? 0.f : m_new;
-            const float corr = fast_exp2(m - ms);
-            m = m_new;
+            const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * a.scale_log2;   // scale > 0 commutes with the maximum
+            // raise m only when the tile towers over it; -inf + 8 = -inf, so the first finite maximum always does
+            const bool raise = mx > m + FA_RAISE;
+            const float factor = raise ? fast_exp2(m - mx) : 1.f;                     // exp2(-inf) = 0: nothing was summed yet
+            if (raise) m = mx;
+            const float ms = (m == -INFINITY) ? 0.f : m;
             // probabilities, rounded to bfloat16 (kept in registers until the P buffer is free)
-            float sum = 0.f;
+            float sum0 = 0.f, sum1 = 0.f;
             const bool dead = !valid && all_visible;
             uint32_t pk[32];
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
                 const float p0 = dead ? 0.f : fast_exp2(fmaf(sv[2 * i], a.scale_log2, -ms));
                 const float p1 = dead ? 0.f : fast_exp2(fmaf(sv[2 * i + 1], a.scale_log2, -ms));
-                sum += p0 + p1;
+                sum0 += p0;
+                sum1 += p1;
                 __nv_bfloat162 b = __floats2bfloat162_rn(p0, p1);
                 pk[i] = *reinterpret_cast<uint32_t*>(&b);
             }
-            l = l * corr + sum;
-            // the second product of the tile before reads the P buffer until o_full completes
+            l = l * factor + (sum0 + sum1);
             if (j > 0) {
-                ok = mbar_wait(o_full, (uint32_t)((j - 1) & 1), abort_flag);
+                // the second product of the tile before reads the P buffer and writes O until pv_done completes
+                ok = mbar_wait(pv_done, (uint32_t)((j - 1) & 1), abort_flag);
+                ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
+                tc_fence_after();
+                if (__any_sync(0xffffffffu, raise)) {          // tensor-memory loads and stores take the whole warp
+#pragma unroll
+                    for (int h = 0; h < HD / 64; ++h) {
+                        float ov[64];
+                        tmem_ld32x2(tmem_o + h * 64 + lane_addr, ov);
+#pragma unroll
+                        for (int i = 0; i < 64; ++i) ov[i] *= factor;
+                        tmem_st32x2(tmem_o + h * 64 + lane_addr, ov);
+                    }
+                }
             }
-            uint8_t* prow = sP + half * FA_BLOCK_BYTES + r * 128;      // this thread's 128-byte row of block `half`
+            uint8_t* prow = sP + r * 128;                      // this thread's 128-byte row
 #pragma unroll
             for (int c8 = 0; c8 < 8; ++c8)
                 *reinterpret_cast<uint4*>(prow + ((c8 ^ (r & 7)) << 4)) =
@@ -298,45 +339,29 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             tc_fence_before();
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             mbar_arrive(p_ready);
-            mbar_arrive(&s_empty[st]);
-            // the output of the tile before, rescaled by how far the maximum moved since
-            if (j > 0) {
-                tc_fence_after();
-                float ov[OD];
-                tmem_ld_od(tmem_base + 256 + half * OD + lane_addr, ov);
-#pragma unroll
-                for (int i = 0; i < OD; ++i) o[i] = fmaf(o[i], corr_prev, ov[i]);
-                tc_fence_before();
-                mbar_arrive(o_empty);
-            }
-            corr_prev = corr;
         }
         if (ok && n_tiles > 0) {
-            ok = mbar_wait(o_full, (uint32_t)((n_tiles - 1) & 1), abort_flag);
+            ok = mbar_wait(pv_done, (uint32_t)((n_tiles - 1) & 1), abort_flag);
+            ok = __all_sync(0xffffffffu, ok);
             if (ok) {
                 tc_fence_after();
-                float ov[OD];
-                tmem_ld_od(tmem_base + 256 + half * OD + lane_addr, ov);
+                const float inv = 1.f / l;
+                __nv_bfloat16* dst = a.out + (size_t)(q_start + tok0 + tl) * a.out_row_stride + (size_t)(head0 + hl) * HD;
 #pragma unroll
-                for (int i = 0; i < OD; ++i) o[i] = fmaf(o[i], corr_prev, ov[i]);
-                // the two halves of the row add their denominators
-                float* xl = xchg + (n_tiles & 1) * 256;
-                xl[half * 128 + r] = l;
-                asm volatile("bar.sync 1, 256;" ::: "memory");
-                l += xl[(half ^ 1) * 128 + r];
-                if (valid) {
-                    const float inv = 1.f / l;
-                    __nv_bfloat16* dst = a.out + (size_t)(q_start + tok0 + tl) * a.out_row_stride +
-                                         (size_t)(head0 + hl) * HD + half * OD;
+                for (int h = 0; h < HD / 64; ++h) {
+                    float ov[64];
+                    tmem_ld32x2(tmem_o + h * 64 + lane_addr, ov);
+                    if (valid) {
 #pragma unroll
-                    for (int c = 0; c < OD; c += 8) {
-                        uint32_t w[4];
+                        for (int c = 0; c < 64; c += 8) {
+                            uint32_t w[4];
 #pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            __nv_bfloat162 b = __floats2bfloat162_rn(o[c + 2 * i] * inv, o[c + 2 * i + 1] * inv);
-                            w[i] = *reinterpret_cast<uint32_t*>(&b);
+                            for (int i = 0; i < 4; ++i) {
+                                __nv_bfloat162 b = __floats2bfloat162_rn(ov[c + 2 * i] * inv, ov[c + 2 * i + 1] * inv);
+                                w[i] = *reinterpret_cast<uint32_t*>(&b);
+                            }
+                            *reinterpret_cast<uint4*>(dst + h * 64 + c) = make_uint4(w[0], w[1], w[2], w[3]);
                         }
-                        *reinterpret_cast<uint4*>(dst + c) = make_uint4(w[0], w[1], w[2], w[3]);
                     }
                 }
             }
@@ -417,8 +442,9 @@ extern "C" int braid_attn_tc(const void* q, void* out, const void* cache, long l
     const long long gx = (max_q_len + tpc - 1) / tpc;
     if (gx > 0x7fffffffLL || (long long)nkh * hchunks > 65535 || n_seqs > 65535)
         BRAID_REFUSE("attn_tc: the step exceeds the grid limits");
+    const long long num_pages = cache_rows / (2LL * nkh * FA_PAGE);
     AttnTcArgs a{(__nv_bfloat16*)out, page_table, q_start, q_len, kv_before, out_row_stride, nqh, nkh, table_cols, window,
-                 scale * 1.4426950408889634f, error_flag};
+                 scale * 1.4426950408889634f, (int)num_pages, error_flag};
     braid_launch(attn_tc_kernel, dim3((unsigned)gx, nkh * hchunks, n_seqs), dim3(FA_THREADS), FA_SMEM,
                  (cudaStream_t)stream, mq, mkv, a);
     BRAID_LAUNCH_CHECK();

@@ -258,6 +258,9 @@ def test_a_far_key_among_hundreds_and_the_windows_edge(K, which):
     if which != "mma_sliced":
         worst, out, qs = attention_case(K, name, torch.bfloat16, hd, nqh, nkh, [(0, 704)], None, plant=(0, 650, 1))
         assert worst < 3e-2 and abs(float(out[650].float().mean()) - 5.0) < 0.1
+        # and at key 640, ten tiles in: what was summed before under a small maximum has to be scaled down
+        worst, out, qs = attention_case(K, name, torch.bfloat16, hd, nqh, nkh, [(0, 704)], None, plant=(0, 650, 640))
+        assert worst < 3e-2 and abs(float(out[650].float().mean()) - 5.0) < 0.1
 
 
 @pytest.mark.parametrize("n, m, k", [(5, 70, 33), (64, 64, 64), (130, 200, 96), (1, 331, 120)])
