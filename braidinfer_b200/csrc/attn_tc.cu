@@ -6,13 +6,19 @@
 // a time.  Two CTAs share an SM (half its shared memory, tensor memory and registers
 // each), so that one's chain of dependent steps runs under the other's.
 //
-//   warp 0      TMA: the query tile once, then key tiles and value tiles into two rings of
-//               two stages (cp.async.bulk.tensor, 128-byte swizzle, no multicast);
+//   warp 0      TMA: the query tile once, then key tiles into a ring of two stages and
+//               value tiles into a ring of three, each as soon as its stage is free
+//               (cp.async.bulk.tensor, 128-byte swizzle, no multicast);
 //   warp 1      one lane issues S = Q K^T (accumulator in tensor memory, two buffers) and,
 //               once the softmax warps have written P, O += P V, accumulated in tensor memory;
 //   warps 2..5  one thread per row: read the 64 scores of S from tensor memory, mask,
-//               running maximum and denominator in float32, P = exp2(s - m) rounded to
-//               bfloat16 into shared memory (the A operand of the second product).
+//               running maximum and denominator in float32, and write P = exp2(s - m),
+//               rounded to bfloat16, back into tensor memory over the first half of the
+//               row's scores: the second product takes P from there as its A operand.
+//
+// Products issued by one thread run in the order issued, so S of tile j + 2 overwrites the
+// buffer of tile j only after the second product of tile j has read P from it; the softmax
+// warps therefore never wait for a product except to rescale O (below) and at the end.
 //
 // The running maximum m is only raised when a tile's maximum exceeds it by more than 8
 // (in the exponent of two), and then the thread scales its row of O in tensor memory by
@@ -47,9 +53,11 @@
 #define FA_KBLOCK_BYTES (64 * 128)               // [64 positions][64 elements]
 #define FA_Q_BYTES (FA_HB * FA_QBLOCK_BYTES)
 #define FA_KV_BYTES (FA_HB * FA_KBLOCK_BYTES)    // one K or one V tile
-#define FA_P_BYTES (128 * 128)                   // [128 rows][64 keys]
-#define FA_SMEM (FA_Q_BYTES + 4 * FA_KV_BYTES + FA_P_BYTES + 128)
-#define FA_TMEM_COLS 256                         // S0 [0,64) S1 [64,128) O [128, 128 + HD)
+#define FA_KST 2                                 // stages of the key ring
+#define FA_VST 3                                 // stages of the value ring
+#define FA_BAR_BYTES 192
+#define FA_SMEM (FA_Q_BYTES + (FA_KST + FA_VST) * FA_KV_BYTES + FA_BAR_BYTES)
+#define FA_TMEM_COLS 256                         // S0 [0,64) S1 [64,128) (P over their first 32 columns), O [128, 128 + HD)
 #define FA_RAISE 8.f                             // how far a tile's maximum may exceed m before m is raised
 
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -77,6 +85,51 @@ __device__ __forceinline__ void tmem_ld32x2(uint32_t taddr, float* v) {
 #pragma unroll
     for (int i = 0; i < 64; ++i) v[i] = __uint_as_float(r[i]);
 }
+// tcgen05.mma with the A operand in tensor memory (rows in lanes, K packed two bfloat16 a column).
+__device__ __forceinline__ void umma_bf16_ta(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// The same two instructions with the descriptors given as (low word, high word): the issuing thread
+// shares its scheduler with softmax warps, so every instruction it does not run counts.  A
+// descriptor's start address lives in its low word; the high word is the same for all tiles of a kind.
+__device__ __forceinline__ void umma_ss_lohi(uint32_t tmem_d, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi,
+                                             uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "setp.ne.b32 p, %6, 0;\n\t"
+        "mov.b64 da, {%1, %2};\n\t"
+        "mov.b64 db, {%3, %4};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}"
+        ::"r"(tmem_d), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_ts_lohi(uint32_t tmem_d, uint32_t tmem_a, uint32_t b_lo, uint32_t b_hi,
+                                             uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}"
+        ::"r"(tmem_d), "r"(tmem_a), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit_addr(uint32_t bar_addr) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_addr) : "memory");
+}
+// 32 consecutive columns of this thread's lane written (no wait).
+__device__ __forceinline__ void tmem_st32_nowait(uint32_t taddr, const uint32_t* w) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+        "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+        :: "r"(taddr), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]), "r"(w[8]),
+           "r"(w[9]), "r"(w[10]), "r"(w[11]), "r"(w[12]), "r"(w[13]), "r"(w[14]), "r"(w[15]), "r"(w[16]), "r"(w[17]),
+           "r"(w[18]), "r"(w[19]), "r"(w[20]), "r"(w[21]), "r"(w[22]), "r"(w[23]), "r"(w[24]), "r"(w[25]), "r"(w[26]),
+           "r"(w[27]), "r"(w[28]), "r"(w[29]), "r"(w[30]), "r"(w[31])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 // The reverse: 64 consecutive columns of this thread's lane written back.
 __device__ __forceinline__ void tmem_st32x2(uint32_t taddr, const float* v) {
 #pragma unroll
@@ -124,20 +177,22 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         return;
     }
     uint8_t* sQ = smem;
-    uint8_t* sK = sQ + FA_Q_BYTES;                 // [2 stages]
-    uint8_t* sV = sK + 2 * FA_KV_BYTES;            // [2 stages]
-    uint8_t* sP = sV + 2 * FA_KV_BYTES;
-    uint64_t* bars = (uint64_t*)(sP + FA_P_BYTES);
-    uint64_t* q_full = bars;            // [1]
-    uint64_t* k_full = bars + 1;        // [2]
-    uint64_t* k_empty = bars + 3;       // [2]
-    uint64_t* v_full = bars + 5;        // [2]
-    uint64_t* v_empty = bars + 7;       // [2]
-    uint64_t* s_full = bars + 9;        // [2]
-    uint64_t* s_empty = bars + 11;      // [2]
-    uint64_t* p_ready = bars + 13;      // [1]
-    uint64_t* pv_done = bars + 14;      // [1]
-    uint32_t* tmem_slot = (uint32_t*)(bars + 15);
+    uint8_t* sK = sQ + FA_Q_BYTES;                 // [FA_KST]
+    uint8_t* sV = sK + FA_KST * FA_KV_BYTES;       // [FA_VST]
+    uint64_t* bars = (uint64_t*)(sV + FA_VST * FA_KV_BYTES);
+    uint64_t* q_full = bars;                       // [1]
+    uint64_t* k_full = q_full + 1;                 // [FA_KST]
+    uint64_t* k_empty = k_full + FA_KST;           // [FA_KST]
+    uint64_t* v_full = k_empty + FA_KST;           // [FA_VST]
+    uint64_t* v_empty = v_full + FA_VST;           // [FA_VST]
+    uint64_t* s_full = v_empty + FA_VST;           // [2]
+    // two p_ready barriers take turns: the softmax warps may finish tile j + 1 before the MMA warp has
+    // looked at tile j's (it issues S of tile j + 1 first, and may then wait for a value tile), and a
+    // single barrier two phases ahead reads like one that has not moved
+    uint64_t* p_ready = s_full + 2;                // [2]
+    uint64_t* pv_done = p_ready + 2;               // [1]
+    uint32_t* tmem_slot = (uint32_t*)(pv_done + 1);
+    static_assert((1 + 2 * FA_KST + 2 * FA_VST + 5) * 8 + 8 <= FA_BAR_BYTES, "the barriers outgrow their bytes");
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -151,12 +206,10 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
 
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
-        for (int s = 0; s < 2; ++s) {
-            mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1);
-            mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1);
-            mbar_init(&s_full[s], 1); mbar_init(&s_empty[s], 128);
-        }
-        mbar_init(p_ready, 128); mbar_init(pv_done, 1);
+        for (int s = 0; s < FA_KST; ++s) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); }
+        for (int s = 0; s < FA_VST; ++s) { mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1); }
+        mbar_init(&s_full[0], 1); mbar_init(&s_full[1], 1);
+        mbar_init(&p_ready[0], 128); mbar_init(&p_ready[1], 128); mbar_init(pv_done, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -188,29 +241,33 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             for (int hb = 0; hb < FA_HB; ++hb)
                 tma_load_3d(&map_q, q_full, sQ + hb * FA_QBLOCK_BYTES, hb * 64, head0, q_start + tok0);
             const int* table = a.page_table + (size_t)seq * a.table_cols;
-            bool ok = true;
-            for (int j = 0; j < n_tiles && ok; ++j) {
-                const int st = j & 1;
-                const uint32_t ph = (uint32_t)((j >> 1) & 1) ^ 1u;
-                int page = (t_lo + j < a.table_cols) ? table[t_lo + j] : -1;
-                if (page < 0 || page >= a.num_pages) {          // a visible position without a page: the table is broken
-                    atomicExch(a.error_flag, 1);
-                    page = 0;
+            // key and value tiles go out independently, each as soon as its stage is free
+            int jk = 0, jv = 0;
+            uint32_t idle = 0;
+            while (jk < n_tiles || jv < n_tiles) {
+                bool moved = false;
+                const bool k_turn = jk < n_tiles && mbar_try_wait(&k_empty[jk % FA_KST], (uint32_t)((jk / FA_KST) & 1) ^ 1u);
+                const bool v_turn = !k_turn && jv < n_tiles && mbar_try_wait(&v_empty[jv % FA_VST], (uint32_t)((jv / FA_VST) & 1) ^ 1u);
+                if (k_turn || v_turn) {
+                    const int j = k_turn ? jk : jv;
+                    int page = (t_lo + j < a.table_cols) ? table[t_lo + j] : -1;
+                    if (page < 0 || page >= a.num_pages) {          // a visible position without a page: the table is broken
+                        atomicExch(a.error_flag, 1);
+                        page = 0;
+                    }
+                    const int row = ((page * 2 + (k_turn ? 0 : 1)) * a.nkh + kvh) * FA_PAGE;
+                    const int st = k_turn ? jk % FA_KST : jv % FA_VST;
+                    uint64_t* bar = k_turn ? &k_full[st] : &v_full[st];
+                    uint8_t* dst = (k_turn ? sK : sV) + st * FA_KV_BYTES;
+                    mbar_expect_tx(bar, FA_KV_BYTES);
+#pragma unroll
+                    for (int hb = 0; hb < FA_HB; ++hb) tma_load_2d(&map_kv, bar, dst + hb * FA_KBLOCK_BYTES, hb * 64, row);
+                    if (k_turn) ++jk; else ++jv;
+                    moved = true;
                 }
-                const int krow = ((page * 2 + 0) * a.nkh + kvh) * FA_PAGE;
-                const int vrow = ((page * 2 + 1) * a.nkh + kvh) * FA_PAGE;
-                ok = mbar_wait(&k_empty[st], ph, abort_flag);
-                if (!ok) break;
-                mbar_expect_tx(&k_full[st], FA_KV_BYTES);
-#pragma unroll
-                for (int hb = 0; hb < FA_HB; ++hb)
-                    tma_load_2d(&map_kv, &k_full[st], sK + st * FA_KV_BYTES + hb * FA_KBLOCK_BYTES, hb * 64, krow);
-                ok = mbar_wait(&v_empty[st], ph, abort_flag);
-                if (!ok) break;
-                mbar_expect_tx(&v_full[st], FA_KV_BYTES);
-#pragma unroll
-                for (int hb = 0; hb < FA_HB; ++hb)
-                    tma_load_2d(&map_kv, &v_full[st], sV + st * FA_KV_BYTES + hb * FA_KBLOCK_BYTES, hb * 64, vrow);
+                if (moved) { idle = 0; continue; }
+                if (++idle >= TC_SPIN_LIMIT) { *abort_flag = 1; break; }
+                if ((idle & 1023u) == 1023u && *abort_flag) break;
             }
         }
     } else if (warp == 1) {
@@ -218,38 +275,52 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             constexpr uint32_t idesc_qk = umma_idesc_bf16(FA_BM, FA_BN);
             constexpr uint32_t idesc_pv = umma_idesc_bf16_b_mn(FA_BM, HD);
             bool ok = mbar_wait(q_full, 0, abort_flag);
-            auto issue_pv = [&](int i) -> bool {
-                const int st = i & 1;
-                if (!mbar_wait(&v_full[st], (uint32_t)((i >> 1) & 1), abort_flag)) return false;
-                if (!mbar_wait(p_ready, (uint32_t)(i & 1), abort_flag)) return false;     // P written, O rescaled
+            // operand descriptors differ only in their start address (bits 0..13 of the low word, in 16-byte units)
+            const uint64_t dq = umma_desc_sw128(smem_u32(sQ));
+            const uint64_t dk = umma_desc_sw128(smem_u32(sK));
+            const uint64_t dv = umma_desc_sw128_mn(smem_u32(sV), FA_KBLOCK_BYTES);
+            const uint32_t q_lo = (uint32_t)dq, k_lo = (uint32_t)dk, v_lo = (uint32_t)dv;
+            const uint32_t kq_hi = (uint32_t)(dq >> 32), v_hi = (uint32_t)(dv >> 32);
+            const uint32_t bar0 = smem_u32(bars);                        // barrier i lies at bar0 + 8 i
+            const uint32_t a_k_empty = bar0 + 8 * (uint32_t)(k_empty - bars), a_v_empty = bar0 + 8 * (uint32_t)(v_empty - bars);
+            const uint32_t a_s_full = bar0 + 8 * (uint32_t)(s_full - bars), a_pv_done = bar0 + 8 * (uint32_t)(pv_done - bars);
+            auto issue_pv = [&](int i, int st) -> bool {
+                if (!mbar_wait(&v_full[st], (uint32_t)((i / FA_VST) & 1), abort_flag)) return false;
+                if (!mbar_wait(&p_ready[i & 1], (uint32_t)((i >> 1) & 1), abort_flag)) return false;     // P written, O rescaled
                 tc_fence_after();
-                const uint32_t sVa = smem_u32(sV + st * FA_KV_BYTES);
-                const uint32_t sPa = smem_u32(sP);
+                const uint32_t vs_lo = v_lo + (uint32_t)((st * FA_KV_BYTES) >> 4);
+                const uint32_t tp = tmem_base + (i & 1) * FA_BN;
+                umma_ts_lohi(tmem_o, tp, vs_lo, v_hi, idesc_pv, i > 0 ? 1u : 0u);
 #pragma unroll
-                for (int ks = 0; ks < FA_BN / 16; ++ks)
-                    umma_bf16(tmem_o, umma_desc_sw128(sPa + ks * 32),
-                              umma_desc_sw128_mn(sVa + ks * 16 * 128, FA_KBLOCK_BYTES), idesc_pv, (i > 0 || ks > 0) ? 1u : 0u);
-                umma_commit(pv_done);
-                umma_commit(&v_empty[st]);
+                for (int ks = 1; ks < FA_BN / 16; ++ks)
+                    umma_ts_lohi(tmem_o, tp + ks * 8, vs_lo + (uint32_t)((ks * 16 * 128) >> 4), v_hi, idesc_pv, 1u);
+                umma_commit_addr(a_pv_done);
+                umma_commit_addr(a_v_empty + 8 * st);
                 return true;
             };
+            int kst = 0, vst = 0;                  // ring stages of key tile j and of value tile j - 1
             for (int j = 0; j < n_tiles && ok; ++j) {
-                const int st = j & 1;
-                const uint32_t ph = (uint32_t)((j >> 1) & 1);
-                ok = mbar_wait(&k_full[st], ph, abort_flag) && mbar_wait(&s_empty[st], ph ^ 1u, abort_flag);
+                ok = mbar_wait(&k_full[kst], (uint32_t)((j / FA_KST) & 1), abort_flag);
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t sQa = smem_u32(sQ), sKa = smem_u32(sK + st * FA_KV_BYTES);
+                // S of tile j goes where S and P of tile j - 2 were: the second product of tile j - 2
+                // was issued before this one, and products run in the order issued
+                const uint32_t ks_lo = k_lo + (uint32_t)((kst * FA_KV_BYTES) >> 4);
+                const uint32_t ts = tmem_base + (j & 1) * FA_BN;
 #pragma unroll
-                for (int ks = 0; ks < HD / 16; ++ks)
-                    umma_bf16(tmem_base + st * FA_BN,
-                              umma_desc_sw128(sQa + (ks >> 2) * FA_QBLOCK_BYTES + (ks & 3) * 32),
-                              umma_desc_sw128(sKa + (ks >> 2) * FA_KBLOCK_BYTES + (ks & 3) * 32), idesc_qk, ks > 0 ? 1u : 0u);
-                umma_commit(&s_full[st]);
-                umma_commit(&k_empty[st]);
-                if (j > 0) ok = issue_pv(j - 1);
+                for (int ks = 0; ks < HD / 16; ++ks) {
+                    const uint32_t qoff = ((ks >> 2) * FA_QBLOCK_BYTES + (ks & 3) * 32) >> 4, koff = ((ks >> 2) * FA_KBLOCK_BYTES + (ks & 3) * 32) >> 4;
+                    umma_ss_lohi(ts, q_lo + qoff, kq_hi, ks_lo + koff, kq_hi, idesc_qk, ks > 0 ? 1u : 0u);
+                }
+                umma_commit_addr(a_s_full + 8 * (j & 1));
+                umma_commit_addr(a_k_empty + 8 * kst);
+                if (++kst == FA_KST) kst = 0;
+                if (j > 0) {
+                    ok = issue_pv(j - 1, vst);
+                    if (++vst == FA_VST) vst = 0;
+                }
             }
-            if (ok && n_tiles > 0) issue_pv(n_tiles - 1);
+            if (ok && n_tiles > 0) issue_pv(n_tiles - 1, vst);
         }
     } else if (active) {
         const int quarter = warp & 3;                          // tensor-memory lanes 32 * quarter ...
@@ -269,8 +340,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             tc_fence_after();
             float sv[64];
             tmem_ld32x2(tmem_base + st * FA_BN + lane_addr, sv);
-            tc_fence_before();
-            mbar_arrive(&s_empty[st]);                         // the scores are in registers: the buffer may take tile j + 2
             const int key0 = (t_lo + j) * FA_BN;
             const bool all_visible = (key0 + FA_BN - 1 <= pos_min) && (a.window == 0 || key0 >= pos_max - a.window + 1);
             float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
@@ -299,46 +368,40 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             const bool raise = mx > m + FA_RAISE;
             const float factor = raise ? fast_exp2(m - mx) : 1.f;                     // exp2(-inf) = 0: nothing was summed yet
             if (raise) m = mx;
-            const float ms = (m == -INFINITY) ? 0.f : m;
-            // probabilities, rounded to bfloat16 (kept in registers until the P buffer is free)
+            // a row that is no query (past the tile's tokens or heads) sums nothing: exp2(-inf) = 0
+            const float ms = (!valid && all_visible) ? INFINITY : ((m == -INFINITY) ? 0.f : m);
+            // probabilities, rounded to bfloat16
             float sum0 = 0.f, sum1 = 0.f;
-            const bool dead = !valid && all_visible;
             uint32_t pk[32];
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
-                const float p0 = dead ? 0.f : fast_exp2(fmaf(sv[2 * i], a.scale_log2, -ms));
-                const float p1 = dead ? 0.f : fast_exp2(fmaf(sv[2 * i + 1], a.scale_log2, -ms));
+                const float p0 = fast_exp2(fmaf(sv[2 * i], a.scale_log2, -ms));
+                const float p1 = fast_exp2(fmaf(sv[2 * i + 1], a.scale_log2, -ms));
                 sum0 += p0;
                 sum1 += p1;
                 __nv_bfloat162 b = __floats2bfloat162_rn(p0, p1);
                 pk[i] = *reinterpret_cast<uint32_t*>(&b);
             }
             l = l * factor + (sum0 + sum1);
-            if (j > 0) {
-                // the second product of the tile before reads the P buffer and writes O until pv_done completes
+            tmem_st32_nowait(tmem_base + st * FA_BN + lane_addr, pk);      // over the first half of this row's scores
+            if (j > 0 && __any_sync(0xffffffffu, raise)) {     // tensor-memory loads and stores take the whole warp
+                // the second product of the tile before adds to O until pv_done completes
                 ok = mbar_wait(pv_done, (uint32_t)((j - 1) & 1), abort_flag);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 tc_fence_after();
-                if (__any_sync(0xffffffffu, raise)) {          // tensor-memory loads and stores take the whole warp
 #pragma unroll
-                    for (int h = 0; h < HD / 64; ++h) {
-                        float ov[64];
-                        tmem_ld32x2(tmem_o + h * 64 + lane_addr, ov);
+                for (int h = 0; h < HD / 64; ++h) {
+                    float ov[64];
+                    tmem_ld32x2(tmem_o + h * 64 + lane_addr, ov);
 #pragma unroll
-                        for (int i = 0; i < 64; ++i) ov[i] *= factor;
-                        tmem_st32x2(tmem_o + h * 64 + lane_addr, ov);
-                    }
+                    for (int i = 0; i < 64; ++i) ov[i] *= factor;
+                    tmem_st32x2(tmem_o + h * 64 + lane_addr, ov);
                 }
             }
-            uint8_t* prow = sP + r * 128;                      // this thread's 128-byte row
-#pragma unroll
-            for (int c8 = 0; c8 < 8; ++c8)
-                *reinterpret_cast<uint4*>(prow + ((c8 ^ (r & 7)) << 4)) =
-                    make_uint4(pk[c8 * 4], pk[c8 * 4 + 1], pk[c8 * 4 + 2], pk[c8 * 4 + 3]);
+            tmem_st_wait();
             tc_fence_before();
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            mbar_arrive(p_ready);
+            mbar_arrive(&p_ready[st]);
         }
         if (ok && n_tiles > 0) {
             ok = mbar_wait(pv_done, (uint32_t)((n_tiles - 1) & 1), abort_flag);
