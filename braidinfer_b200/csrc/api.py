@@ -131,7 +131,9 @@ class Kernels:
         if any(flags):
             self._error_flag.zero_()
             names = ["cache write outside the sequence's pages", "tensor-core GEMM wait ran out",
-                     "NaN among the logits", "tcgen05 attention wait ran out"]
+                     "NaN among the logits",
+                     "tcgen05 attention gave up (a wait ran out, a visible position had no page, or its shared "
+                     "memory was not 1024-byte aligned)"]
             raise KernelError("device error: " + "; ".join(n for n, f in zip(names, flags) if f))
 
     # ------------------------------------------------------------------ row-wise kernels

@@ -228,6 +228,44 @@ def test_tcgen05_attention_kernel(K, hd, nqh, nkh, seqs, window):
     assert worst < 2e-2
 
 
+@pytest.mark.parametrize("hd, nqh, nkh, seqs, window, scale_q", [
+    (128, 32, 8, [(0, 1500)], None, 1.0),              # 376 CTAs: more than the GPU holds at once
+    (128, 32, 8, [(0, 1100), (900, 700)], 600, 4.0),   # the same with a window and a running maximum that moves
+    (64, 32, 8, [(0, 2048)], None, 1.0),
+])
+def test_tcgen05_attention_in_more_ctas_than_run_at_once(K, hd, nqh, nkh, seqs, window, scale_q):
+    """CTAs that start when others end meet a CTA in mid-flight on their SM; a barrier that the softmax
+    warps could run two phases ahead of showed only then.  Compared with the mma.sync kernel, which the
+    tests above hold against the float64 reference."""
+    torch.manual_seed(0)
+    lens = [b + n for b, n in seqs]
+    cache, table = make_cache(len(seqs), lens, nkh, hd, torch.bfloat16, shuffle_seed=5)
+    cache.copy_(torch.randn(cache.shape, device=DEV).to(torch.bfloat16))
+    rows = sum(n for _, n in seqs)
+    qkv = torch.randn(rows, (nqh + 2 * nkh) * hd, device=DEV)
+    qkv[:, :nqh * hd] *= scale_q
+    qkv = qkv.to(torch.bfloat16)
+    t = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    q_start, seq, r = [], [], 0
+    for i, (b, n) in enumerate(seqs):
+        q_start.append(r)
+        seq += [i] * n
+        r += n
+    args = (t(q_start), t([n for _, n in seqs]), t([b for b, _ in seqs]))
+    ref = torch.zeros(rows, nqh * hd, device=DEV, dtype=torch.bfloat16)
+    out = torch.zeros_like(ref)
+    for _ in range(3):                                   # the interleaving differs from launch to launch
+        K.attn_mma(qkv, ref, cache, table, *args, t(seq), len(seqs), max(n for _, n in seqs), nqh, nkh, hd, window,
+                   1 / math.sqrt(hd))
+        out.zero_()
+        K.attn_tc(qkv, out, cache, table, *args, len(seqs), max(n for _, n in seqs), nqh, nkh, hd, window,
+                  1 / math.sqrt(hd))
+        torch.cuda.synchronize()
+        K.check_device_errors()
+        # both are rounded to bfloat16: one unit in the last place is 2^-8 of the value
+        assert ((out.float() - ref.float()).abs() / (1.0 + ref.float().abs())).max().item() < 1.5e-2
+
+
 @pytest.mark.parametrize("hd, nqh, nkh, seqs, window, splits", [
     (128, 32, 8, [(2047, 1), (100, 1), (0, 1), (63, 1), (64, 1)], None, 8),
     (128, 32, 8, [(700, 1), (100, 1)], 128, 4),
