@@ -40,6 +40,7 @@
 #define TC_BLOCK_K 64
 #define TC_UMMA_K 16
 #define TC_THREADS 192
+#define TC_GROUP_N 8            // token tiles that share their stay in L2 (see TcWalk)
 
 struct GemmTcArgs {
     void* out;                 // mode 0: [n, ldo] bf16/f32; 1: f32; 2: bf16/f32 [n, ldo]; 3: f32 [slot][n_rows][128]
@@ -71,7 +72,8 @@ struct TcCfg {
 //
 // Modes 0-2: units u = blockIdx.x, blockIdx.x + gridDim.x, ...; a unit is one whole
 // [128 x BLOCK_N] output tile.  Token tiles vary fastest so that CTAs running side by
-// side share weight tiles in L2.
+// side share weight tiles in L2; with more than TC_GROUP_N token tiles they go in groups of
+// that many, each group against all the weights, or the tokens would not stay in L2.
 //
 // Mode 3 ("stream-k", for a few tokens, where the product only streams weights): the
 // k blocks of all tiles form one line of m_tiles * n_tiles * total_kb blocks, cut into
@@ -117,8 +119,20 @@ struct TcWalk {
             t.slot = 0;
             u += gridDim.x;
         }
-        const int nt = tile % a.n_tiles;
-        t.m0 = (tile / a.n_tiles) * TC_BLOCK_M;
+        int mt, nt;
+        if (MODE == 3 || a.n_tiles <= TC_GROUP_N) {
+            nt = tile % a.n_tiles;
+            mt = tile / a.n_tiles;
+        } else {
+            // many token tiles: groups of TC_GROUP_N of them, each group against all weight tiles
+            // before the next, so that a group's tokens stay in L2 while the weights stream past
+            const int per_group = TC_GROUP_N * a.m_tiles;
+            const int grp = tile / per_group, r = tile - grp * per_group;
+            const int width = min(TC_GROUP_N, a.n_tiles - grp * TC_GROUP_N);
+            mt = r / width;
+            nt = grp * TC_GROUP_N + (r - mt * width);
+        }
+        t.m0 = mt * TC_BLOCK_M;
         t.n0 = nt * BLOCK_N;
         return true;
     }
