@@ -85,17 +85,9 @@ __device__ __forceinline__ void tmem_ld32x2(uint32_t taddr, float* v) {
 #pragma unroll
     for (int i = 0; i < 64; ++i) v[i] = __uint_as_float(r[i]);
 }
-// tcgen05.mma with the A operand in tensor memory (rows in lanes, K packed two bfloat16 a column).
-__device__ __forceinline__ void umma_bf16_ta(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
-}
-// The same two instructions with the descriptors given as (low word, high word): the issuing thread
-// shares its scheduler with softmax warps, so every instruction it does not run counts.  A
-// descriptor's start address lives in its low word; the high word is the same for all tiles of a kind.
+// tcgen05.mma with both operands in shared memory, and with the A operand in tensor memory (rows in
+// lanes, K packed two bfloat16 a column).  Descriptors are given as (low word, high word): a
+// descriptor's start address lives in its low word, the high word is the same for all tiles of a kind.
 __device__ __forceinline__ void umma_ss_lohi(uint32_t tmem_d, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi,
                                              uint32_t idesc, uint32_t accumulate) {
     asm volatile(
