@@ -283,6 +283,58 @@ def run_other_size(args):
     return 0
 
 
+def run_sweep(args):
+    """Decode at batch 1, 8, 64 over contexts of 512 to 32,768 tokens and prefill of 512 to 16,384
+    tokens, on the default sizes: one JSON line with time, achieved bandwidth or FLOP rate, and the
+    fraction of the peak, for every point.  For profiles/; not the contract's line."""
+    import torch
+    from braidinfer_b200.config import preset
+    from braidinfer_b200.engine import Engine
+    pk = peaks()
+    cfg_dict = preset("mistral_7b_v03")
+    if args.layers:
+        cfg_dict["num_hidden_layers"] = args.layers
+    n_layers = cfg_dict["num_hidden_layers"]
+    engine = Engine.from_random(cfg_dict, seed=0, dtype="bfloat16", on_device=True, max_tokens=64 * 8192 + 4096,
+                                max_slots=64, verbose=True)
+    cfg = engine.config
+    g = torch.Generator().manual_seed(0)
+    _, weight_bytes, kv_per_tok = model_numbers(cfg, n_layers)
+    decode, prefill = [], []
+    for T in (512, 2048, 8192, 16384):
+        p = torch.randint(0, cfg.vocab_size, (T,), generator=g).tolist()
+        times = []
+        for i in range(5):
+            s = engine.open()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            engine.step([(s, p)], want="last")
+            e1.record()
+            torch.cuda.synchronize()
+            engine.close(s)
+            if i >= 2:
+                times.append(e0.elapsed_time(e1))
+        ms = statistics.median(times)
+        fl = prefill_flops(cfg, n_layers, T)
+        prefill.append({"tokens": T, "ms": round(ms, 3), "tokens_per_s": round(T / ms * 1e3),
+                        "tflops": round(fl / ms / 1e9, 1), "frac": round(fl / (ms / 1e3) / (pk["bf16_tflops"] * 1e12), 3)})
+    for ctx in (512, 2048, 8192, 32768):
+        for b in (1, 8, 64):
+            if b * (ctx + 64) > engine.max_tokens:
+                continue
+            prompts = [torch.randint(0, cfg.vocab_size, (ctx,), generator=g).tolist() for _ in range(b)]
+            steps = 32
+            secs, ctx0, _ = device_timed_decode(engine, engine.kernels, prompts, steps, 3)
+            step_bytes = weight_bytes + b * (ctx0 + steps / 2) * kv_per_tok
+            gbs = step_bytes / (secs / steps) / 1e9
+            decode.append({"batch": b, "context": ctx, "ms_per_step": round(secs / steps * 1e3, 3),
+                           "tokens_per_s": round(b * steps / secs, 1), "gb_per_s": round(gbs),
+                           "frac": round(gbs / pk["hbm_gbs"], 3)})
+    print(json.dumps({"metric": "sweep over batch, context and prompt length, Mistral-7B-v0.3 sizes, bf16", "impl": "ours",
+                      "layers": n_layers, "peaks": pk, "prefill": prefill, "decode": decode}))
+    return 0
+
+
 def run_reference(args):
     print(json.dumps({"impl": "reference", "unavailable":
                       "mcelrath/braidinfer is Rust + HIP for AMD RDNA3: pip finds neither setup.py nor pyproject.toml, "
@@ -305,12 +357,16 @@ def main() -> int:
     ap.add_argument("--preset", default="mistral_7b_v03",
                     choices=["mistral_7b_v03", "mistral_7b_v01", "mistral_nemo_12b"],
                     help="the default is the contract's run; the other two print their own line (see run_other_size)")
+    ap.add_argument("--sweep", action="store_true",
+                    help="decode over batch and context, prefill over prompt length; prints its own line (see run_sweep)")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
     if args.gpus != 1:
         print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
+    if args.sweep:
+        return run_sweep(args)
     if args.preset != "mistral_7b_v03":
         return run_other_size(args)
     return run_ours(args)

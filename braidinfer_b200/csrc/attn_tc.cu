@@ -16,9 +16,10 @@
 //               rounded to bfloat16, back into tensor memory over the first half of the
 //               row's scores: the second product takes P from there as its A operand.
 //
-// Products issued by one thread run in the order issued, so S of tile j + 2 overwrites the
-// buffer of tile j only after the second product of tile j has read P from it; the softmax
-// warps therefore never wait for a product except to rescale O (below) and at the end.
+// S of tile j + 2 overwrites the buffer of tile j; the MMA warp issues it only when the second
+// product of tile j, which reads P from there, has completed (issued a tile earlier, so it has).
+// The softmax warps look at the completion of every second product, one tile late, which costs
+// nothing and keeps their view of that barrier within one phase (see the loop).
 //
 // The running maximum m is only raised when a tile's maximum exceeds it by more than 8
 // (in the exponent of two), and then the thread scales its row of O in tensor memory by
@@ -293,10 +294,12 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             int kst = 0, vst = 0;                  // ring stages of key tile j and of value tile j - 1
             for (int j = 0; j < n_tiles && ok; ++j) {
                 ok = mbar_wait(&k_full[kst], (uint32_t)((j / FA_KST) & 1), abort_flag);
+                // S of tile j goes where S and P of tile j - 2 were: the second product of tile j - 2,
+                // which reads that P, has to be complete (it was issued a tile ago, so this wait is short;
+                // issue order alone does not keep a product's writes behind its predecessor's reads)
+                if (ok && j >= 2) ok = mbar_wait(pv_done, (uint32_t)(j & 1), abort_flag);
                 if (!ok) break;
                 tc_fence_after();
-                // S of tile j goes where S and P of tile j - 2 were: the second product of tile j - 2
-                // was issued before this one, and products run in the order issued
                 const uint32_t ks_lo = k_lo + (uint32_t)((kst * FA_KV_BYTES) >> 4);
                 const uint32_t ts = tmem_base + (j & 1) * FA_BN;
 #pragma unroll
@@ -376,19 +379,24 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             }
             l = l * factor + (sum0 + sum1);
             tmem_st32_nowait(tmem_base + st * FA_BN + lane_addr, pk);      // over the first half of this row's scores
-            if (j > 0 && __any_sync(0xffffffffu, raise)) {     // tensor-memory loads and stores take the whole warp
-                // the second product of the tile before adds to O until pv_done completes
+            if (j > 0) {
+                // Every tile, the second product of the tile before is waited for (it was issued a whole
+                // softmax ago, so this costs nothing): a parity wait only tells apart a barrier that is
+                // at most one phase off, and a thread that looked at pv_done only now and then, or
+                // only at the end, could find it two phases behind and take that for done.
                 ok = mbar_wait(pv_done, (uint32_t)((j - 1) & 1), abort_flag);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
-                tc_fence_after();
+                if (__any_sync(0xffffffffu, raise)) {          // tensor-memory loads and stores take the whole warp
+                    tc_fence_after();
 #pragma unroll
-                for (int h = 0; h < HD / 64; ++h) {
-                    float ov[64];
-                    tmem_ld32x2(tmem_o + h * 64 + lane_addr, ov);
+                    for (int h = 0; h < HD / 64; ++h) {
+                        float ov[64];
+                        tmem_ld32x2(tmem_o + h * 64 + lane_addr, ov);
 #pragma unroll
-                    for (int i = 0; i < 64; ++i) ov[i] *= factor;
-                    tmem_st32x2(tmem_o + h * 64 + lane_addr, ov);
+                        for (int i = 0; i < 64; ++i) ov[i] *= factor;
+                        tmem_st32x2(tmem_o + h * 64 + lane_addr, ov);
+                    }
                 }
             }
             tmem_st_wait();

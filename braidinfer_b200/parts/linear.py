@@ -13,9 +13,24 @@ import torch
 
 from .spec import TensorSpec
 
-# Up to this many tokens a product only streams its weights: it is spread evenly over
-# all SMs along k as well as along the output ("stream-k").
-_STREAM_K_MAX_ROWS = 64
+_SMS = None
+
+
+def stream_k_pays(rows: int, w_rows: int) -> bool:
+    """Whether the product of `rows` tokens with a [w_rows, k] weight should be spread evenly over
+    all SMs along k as well ("stream-k" partial sums plus a kernel that adds them up) rather than
+    cut into whole [128 x token tile] output tiles: it pays when whole tiles would leave SMs idle.
+    Measured on the 7B layer sizes at 1 to 512 tokens: a last round of tiles less than 70 % full
+    (80 % for up to 32 tokens, 60 % above 256) loses more than the adding-up costs."""
+    global _SMS
+    if _SMS is None:
+        _SMS = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+    if rows > 512:
+        return False
+    block_n = 16 if rows <= 16 else 32 if rows <= 32 else 64 if rows <= 64 else 128 if rows <= 128 else 256
+    tiles = -(-w_rows // 128) * -(-rows // block_n)
+    fill = tiles / (-(-tiles // _SMS) * _SMS)
+    return fill < (0.8 if rows <= 32 else 0.7 if rows <= 256 else 0.6)
 
 
 class Linear:
@@ -82,13 +97,14 @@ class Linear:
             K.cast(y, y2)
             return y2
         use_tc = (self.rt.gemm_backend == "auto" and x.dtype == torch.bfloat16 and K.gemm_tc_eligible(x, w))
-        can_defer = (defer_to is not None and use_tc and rows <= _STREAM_K_MAX_ROWS and not swiglu
+        sk = use_tc and stream_k_pays(rows, w_rows)
+        can_defer = (defer_to is not None and sk and not swiglu
                      and self.rt.fuse_reduce and K.pending_partial is None)
         if residual is not None:
             if can_defer:
                 defer_to.defer(residual, K.gemm_tc_partial(x, w), "residual")
             elif use_tc:
-                K.gemm_tc(x, w, residual, residual=residual, stream_k=rows <= _STREAM_K_MAX_ROWS)
+                K.gemm_tc(x, w, residual, residual=residual, stream_k=sk)
             else:
                 K.gemm_simt(x, w, residual, residual=residual)
             return residual
@@ -99,7 +115,7 @@ class Linear:
                 if not use_tc:
                     raise RuntimeError("interleaved gate/up weights need the tensor-core product; its input rows "
                                        "must be 16-byte aligned bfloat16")
-                K.gemm_tc(x, w, out, swiglu=True, stream_k=rows <= _STREAM_K_MAX_ROWS)
+                K.gemm_tc(x, w, out, swiglu=True, stream_k=sk)
             else:
                 gu = torch.empty((rows, w_rows), dtype=x.dtype, device=x.device)
                 K.gemm_simt(x, w, gu)
@@ -109,7 +125,7 @@ class Linear:
         if can_defer:
             defer_to.defer(out, K.gemm_tc_partial(x, w), "store")
         elif use_tc:
-            K.gemm_tc(x, w, out, stream_k=rows <= _STREAM_K_MAX_ROWS)
+            K.gemm_tc(x, w, out, stream_k=sk)
         else:
             K.gemm_simt(x, w, out)
         return out

@@ -35,6 +35,13 @@ def run(eng, prompts, n_decode, forced):
     ("7b_window", mistral(num_hidden_layers=2, hidden_size=4096, num_attention_heads=32, num_key_value_heads=8,
                           head_dim=128, intermediate_size=14336, vocab_size=32000, rope_theta=10000.0,
                           sliding_window=160), [500, 37, 260], 40),
+    # 390 and 210 rows a step: the products whose whole tiles would leave SMs idle go as partial sums
+    ("7b_390_rows", mistral(num_hidden_layers=2, hidden_size=4096, num_attention_heads=32, num_key_value_heads=8,
+                            head_dim=128, intermediate_size=14336, vocab_size=32000, rope_theta=1e6,
+                            sliding_window=None), [300, 90], 6),
+    ("7b_210_rows", mistral(num_hidden_layers=2, hidden_size=4096, num_attention_heads=32, num_key_value_heads=8,
+                            head_dim=128, intermediate_size=14336, vocab_size=32000, rope_theta=1e6,
+                            sliding_window=None), [120, 60, 30], 6),
     ("nemo", mistral(num_hidden_layers=1, hidden_size=5120, num_attention_heads=32, num_key_value_heads=8,
                      head_dim=128, intermediate_size=14336, vocab_size=131072, rope_theta=1e6,
                      sliding_window=None), [700, 33, 128, 65], 12),
@@ -55,7 +62,9 @@ def test_tensor_core_engine_equals_plain_engine_at_model_sizes(name, cfg, lens, 
         torch.cuda.empty_cache()
     fast, plain = results
     scale = plain.abs().max().item()
-    assert (fast - plain).abs().max().item() < 2e-2 * scale
+    per_row = (fast - plain).abs().max(dim=1).values          # rows: the prompts' last tokens, then a row a sequence and step
+    bad = [(i, round(v, 4)) for i, v in enumerate(per_row.tolist()) if v >= 2e-2 * scale]
+    assert not bad, f"rows (index, difference) beyond {2e-2 * scale:.4f}: {bad[:16]} of {len(per_row)} rows, {len(lens)} sequences"
     # the choice of token agrees wherever the plain logits have a clear winner
     top2 = plain.topk(2, dim=-1).values
     clear = (top2[:, 0] - top2[:, 1]) > 4e-2 * scale
