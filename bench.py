@@ -295,7 +295,7 @@ def run_sweep(args):
     if args.layers:
         cfg_dict["num_hidden_layers"] = args.layers
     n_layers = cfg_dict["num_hidden_layers"]
-    engine = Engine.from_random(cfg_dict, seed=0, dtype="bfloat16", on_device=True, max_tokens=64 * 8192 + 4096,
+    engine = Engine.from_random(cfg_dict, seed=0, dtype="bfloat16", on_device=True, max_tokens=64 * (8192 + 128),
                                 max_slots=64, verbose=True)
     cfg = engine.config
     g = torch.Generator().manual_seed(0)
@@ -320,11 +320,11 @@ def run_sweep(args):
                         "tflops": round(fl / ms / 1e9, 1), "frac": round(fl / (ms / 1e3) / (pk["bf16_tflops"] * 1e12), 3)})
     for ctx in (512, 2048, 8192, 32768):
         for b in (1, 8, 64):
-            if b * (ctx + 64) > engine.max_tokens:
+            if b * (ctx + 128) > engine.max_tokens:
                 continue
             prompts = [torch.randint(0, cfg.vocab_size, (ctx,), generator=g).tolist() for _ in range(b)]
-            steps = 32
-            secs, ctx0, _ = device_timed_decode(engine, engine.kernels, prompts, steps, 3)
+            steps = 48
+            secs, ctx0, _ = device_timed_decode(engine, engine.kernels, prompts, steps, 24)    # clocks settle after the prompts
             step_bytes = weight_bytes + b * (ctx0 + steps / 2) * kv_per_tok
             gbs = step_bytes / (secs / steps) / 1e9
             decode.append({"batch": b, "context": ctx, "ms_per_step": round(secs / steps * 1e3, 3),
