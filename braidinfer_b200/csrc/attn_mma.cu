@@ -88,9 +88,12 @@ attn_mma_kernel(AttnMmaArgs a) {
     const int hpc = g < C::BM ? g : C::BM;                 // heads per CTA
     const int tpc = C::BM / hpc;                           // tokens per CTA
     const int hchunks = (g + hpc - 1) / hpc;
-    const int seq = blockIdx.z;
-    const int kvh = blockIdx.y / hchunks, hchunk = blockIdx.y - kvh * hchunks;
-    const int tile = blockIdx.x / a.n_splits, split = blockIdx.x - tile * a.n_splits;
+    // CTAs start in the order x, y, z: every kv head and sequence of the last token tile first, then of
+    // the tile before: late tokens see the most keys, so the longest CTAs start first
+    const int seq = blockIdx.y;
+    const int kvh = blockIdx.x / hchunks, hchunk = blockIdx.x - kvh * hchunks;
+    const int unit = gridDim.z - 1 - blockIdx.z;
+    const int tile = unit / a.n_splits, split = unit - tile * a.n_splits;
     const int q_len = a.q_len[seq];
     const int tok0 = tile * tpc;
     if (tok0 >= q_len) return;
@@ -335,9 +338,9 @@ static int launch_attn(const AttnMmaArgs& a, int n_seqs, int max_q_len, cudaStre
     const int tpc = C::BM / hpc;
     const int hchunks = (g + hpc - 1) / hpc;
     const long long gx = (long long)((max_q_len + tpc - 1) / tpc) * a.n_splits;
-    if (gx > 0x7fffffffLL || (long long)a.nkh * hchunks > 65535 || n_seqs > 65535)
+    if (gx > 65535 || (long long)a.nkh * hchunks > 0x7fffffffLL || n_seqs > 65535)
         BRAID_REFUSE("attn_mma: the step exceeds the grid limits (%lld tiles, %d heads, %d sequences)", gx, a.nkh * hchunks, n_seqs);
-    dim3 grid((unsigned)gx, a.nkh * hchunks, n_seqs);
+    dim3 grid(a.nkh * hchunks, n_seqs, (unsigned)gx);
     braid_launch(attn_mma_kernel<BRAID_HD, NW, BN, ST>, dim3(grid), dim3(NW * 32), C::SMEM, s, a);
     BRAID_LAUNCH_CHECK();
 }

@@ -193,9 +193,12 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     const int hpc = g < FA_BM ? g : FA_BM;
     const int tpc = FA_BM / hpc;
     const int hchunks = (g + hpc - 1) / hpc;
-    const int seq = blockIdx.z;
-    const int kvh = blockIdx.y / hchunks, hchunk = blockIdx.y - kvh * hchunks;
-    const int tile = gridDim.x - 1 - blockIdx.x;       // late tokens see the most keys: start them first
+    // CTAs start in the order x, y, z: all kv heads and sequences of the last token tile first, then
+    // the tile before, ...: late tokens see the most keys, so the longest CTAs start first and the
+    // short ones fill the gaps at the end
+    const int seq = blockIdx.y;
+    const int kvh = blockIdx.x / hchunks, hchunk = blockIdx.x - kvh * hchunks;
+    const int tile = gridDim.z - 1 - blockIdx.z;
 
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
@@ -503,12 +506,12 @@ extern "C" int braid_attn_tc(const void* q, void* out, const void* cache, long l
         configured = true;
     }
     const long long gx = (max_q_len + tpc - 1) / tpc;
-    if (gx > 0x7fffffffLL || (long long)nkh * hchunks > 65535 || n_seqs > 65535)
-        BRAID_REFUSE("attn_tc: the step exceeds the grid limits");
+    if (gx > 65535 || (long long)nkh * hchunks > 0x7fffffffLL || n_seqs > 65535)
+        BRAID_REFUSE("attn_tc: the step exceeds the grid limits (%lld token tiles, %d sequences)", gx, n_seqs);
     const long long num_pages = cache_rows / (2LL * nkh * FA_PAGE);
     AttnTcArgs a{(__nv_bfloat16*)out, page_table, q_start, q_len, kv_before, out_row_stride, nqh, nkh, table_cols, window,
                  scale * 1.4426950408889634f, (int)num_pages, error_flag};
-    braid_launch(attn_tc_kernel, dim3((unsigned)gx, nkh * hchunks, n_seqs), dim3(FA_THREADS), FA_SMEM,
+    braid_launch(attn_tc_kernel, dim3(nkh * hchunks, n_seqs, (unsigned)gx), dim3(FA_THREADS), FA_SMEM,
                  (cudaStream_t)stream, mq, mkv, a);
     BRAID_LAUNCH_CHECK();
 }
