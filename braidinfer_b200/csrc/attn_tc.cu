@@ -443,22 +443,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
 }
 
 // ------------------------------------------------------------------ host side
-typedef CUresult (*FaEncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static FaEncodeTiledFn fa_encode_fn() {
-    static FaEncodeTiledFn fn = nullptr;
-    if (!fn) {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = (FaEncodeTiledFn)p;
-    }
-    return fn;
-}
-
 extern "C" int braid_attn_tc_supported(void) { return 1; }
 
 // Prompt attention on tcgen05.  Arguments as braid_attn_mma (attn_mma.cu); no slicing of
@@ -474,7 +458,7 @@ extern "C" int braid_attn_tc(const void* q, void* out, const void* cache, long l
     if ((q_row_stride % 8) || ((uintptr_t)q & 15) || ((uintptr_t)cache & 15)) BRAID_REFUSE("attn_tc: queries and cache must be 16-byte aligned");
     if ((out_row_stride % 8) || ((uintptr_t)out & 15)) BRAID_REFUSE("attn_tc: out rows must be 16-byte aligned");
     if (!error_flag) BRAID_REFUSE("attn_tc: error_flag is required");
-    FaEncodeTiledFn fn = fa_encode_fn();
+    TcEncodeTiledFn fn = tc_encode_tiled_fn();
     if (!fn) BRAID_REFUSE("attn_tc: the driver does not export cuTensorMapEncodeTiled");
     const int g = nqh / nkh;
     const int hpc = g < FA_BM ? g : FA_BM, tpc = FA_BM / hpc, hchunks = (g + hpc - 1) / hpc;

@@ -380,25 +380,9 @@ __global__ void streamk_reduce_kernel(StreamK k, void* __restrict__ out, const f
 }
 
 // ------------------------------------------------------------------ host side
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn get_encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    if (!fn) {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = (EncodeTiledFn)p;
-    }
-    return fn;
-}
-
 // rows x k bfloat16 matrix with row stride ld (elements); box = box_rows x 64, 128-byte swizzle.
 static int make_map(CUtensorMap* map, const void* base, long long rows, long long k, long long ld, int box_rows) {
-    EncodeTiledFn fn = get_encode_fn();
+    TcEncodeTiledFn fn = tc_encode_tiled_fn();
     if (!fn) BRAID_REFUSE("gemm_tc: the driver does not export cuTensorMapEncodeTiled");
     cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
     cuuint64_t strides[1] = {(cuuint64_t)ld * 2};

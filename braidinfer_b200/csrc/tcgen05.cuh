@@ -113,3 +113,21 @@ __device__ __forceinline__ uint64_t umma_desc_sw128_mn(uint32_t saddr, uint32_t 
 __host__ __device__ constexpr uint32_t umma_idesc_bf16_b_mn(int m, int n) {
     return (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
+
+// ------------------------------------------------------------------ host side
+// cuTensorMapEncodeTiled through the runtime's driver entry point lookup (no link against libcuda).
+typedef CUresult (*TcEncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static inline TcEncodeTiledFn tc_encode_tiled_fn() {
+    static TcEncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (TcEncodeTiledFn)p;
+    }
+    return fn;
+}
