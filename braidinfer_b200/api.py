@@ -53,6 +53,27 @@ class Model:
         """Greedy generation after one prompt (generate.rs:314-439)."""
         return self.generate(list(prompt_ids), SamplingParams.greedy(), None, max_tokens)
 
+    # -- the step function itself, for callers that schedule their own batches
+    def open(self) -> int:
+        """Take a slot for a new sequence."""
+        return self.engine.open()
+
+    def step(self, entries, want="last"):
+        """One step of `entries` = [(slot, tokens), ...] (see `Engine.step`): sequences that start
+        together bring their prompts, then one token each; returns float32 logits at the wanted places."""
+        return self.engine.step(entries, want=want)
+
+    def close(self, slot: int) -> None:
+        """Give a sequence's slot and pages back."""
+        self.engine.close(slot)
+
+    def replay(self, lines, out_dir: str) -> int:
+        """Feed given token ids step by step and write logits, as `bin/trace_run` does
+        (`lines`: JSON step objects, as text lines or dicts)."""
+        import json
+        from .engine.trace import replay
+        return replay(self.engine, (l if isinstance(l, str) else json.dumps(l) for l in lines), out_dir)
+
     # -- the step API of the reference, for one sequence at a time
     def prefill(self, tokens: Sequence[int]):
         """Start a sequence with its prompt; returns (slot, float32 logits of the last token)."""
