@@ -335,6 +335,57 @@ def run_sweep(args):
     return 0
 
 
+def run_timeline(args):
+    """Where a decode step's time goes: one CUDA-graph step of the default sizes under the torch
+    profiler (device activity only), printed as one JSON line: for the kernels of one layer in the
+    middle of the step, the time from the end of the kernel before to the end of this one (kernels
+    overlap their predecessors' tails through programmatic dependent launch, so durations would
+    count time twice).  For profiles/; not the contract's line."""
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+    from braidinfer_b200.config import preset
+    from braidinfer_b200.engine import Engine
+    cfg_dict = preset("mistral_7b_v03")
+    if args.layers:
+        cfg_dict["num_hidden_layers"] = args.layers
+    B = args.batch
+    engine = Engine.from_random(cfg_dict, seed=0, dtype="bfloat16", on_device=True, max_tokens=B * 4096, max_slots=B,
+                                verbose=True)
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, engine.config.vocab_size, (2048,), generator=g).tolist() for _ in range(B)]
+    slots = [engine.open() for _ in prompts]
+    engine.step(list(zip(slots, prompts)))
+    for _ in range(8):
+        engine.step([(s, [5]) for s in slots])
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        for _ in range(2):
+            engine.step([(s, [5]) for s in slots])
+        torch.cuda.synchronize()
+    with tempfile.TemporaryDirectory() as d:
+        path = os.path.join(d, "trace.json")
+        prof.export_chrome_trace(path)
+        with open(path) as f:
+            ev = [e for e in json.load(f)["traceEvents"] if e.get("cat") == "kernel"]
+    ev.sort(key=lambda e: e["ts"])
+    first = [i for i, e in enumerate(ev) if "embed" in e["name"]][-1]
+    step = ev[first:]
+    span = step[-1]["ts"] + step[-1]["dur"] - step[0]["ts"]
+    # a layer = from one attention kernel to the next
+    att = [i for i, e in enumerate(step) if "attn_" in e["name"] and "combine" not in e["name"]]
+    mid = len(att) // 2
+    start, per_layer = att[mid], att[mid + 1] - att[mid]
+    rows, prev_end = [], step[start - 1]["ts"] + step[start - 1]["dur"]
+    for e in step[start:start + per_layer]:
+        end = e["ts"] + e["dur"]
+        rows.append({"kernel": e["name"].split("(")[0][:48], "until_its_end_us": round(end - prev_end, 2)})
+        prev_end = end
+    print(json.dumps({"metric": "one decode step under the profiler, Mistral-7B-v0.3 sizes, bf16", "impl": "ours",
+                      "batch": B, "kernels_in_step": len(step), "step_us": round(span, 1), "kernels_a_layer": per_layer,
+                      "layer_us": round(sum(r["until_its_end_us"] for r in rows), 1), "one_layer": rows}))
+    return 0
+
+
 def run_reference(args):
     print(json.dumps({"impl": "reference", "unavailable":
                       "mcelrath/braidinfer is Rust + HIP for AMD RDNA3: pip finds neither setup.py nor pyproject.toml, "
@@ -359,6 +410,8 @@ def main() -> int:
                     help="the default is the contract's run; the other two print their own line (see run_other_size)")
     ap.add_argument("--sweep", action="store_true",
                     help="decode over batch and context, prefill over prompt length; prints its own line (see run_sweep)")
+    ap.add_argument("--timeline", action="store_true",
+                    help="one decode step under the torch profiler: a layer's kernels with their share (see run_timeline)")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
@@ -367,6 +420,8 @@ def main() -> int:
         return 2
     if args.sweep:
         return run_sweep(args)
+    if args.timeline:
+        return run_timeline(args)
     if args.preset != "mistral_7b_v03":
         return run_other_size(args)
     return run_ours(args)
