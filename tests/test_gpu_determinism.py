@@ -59,3 +59,32 @@ def test_the_same_batch_gives_the_same_bits(name, cfg, lens, n_decode, repeats):
             differ = (got != first).any(dim=1).nonzero().flatten().tolist()
             assert not differ, f"run {it}: rows {differ[:12]} of {got.shape[0]} differ from run 0 ({len(lens)} sequences a step)"
     eng.check()
+
+
+def test_results_do_not_depend_on_what_lay_in_memory_before():
+    """Device memory handed out by `torch.empty` holds whatever was there.  Here it holds NaN: a few
+    GB are filled with NaN and given back to the allocator before the engines are built, so a kernel
+    that reads a buffer (workspace, padding row, cache page) before anything wrote it shows as NaN or
+    as a difference from the plain kernels."""
+    blocks = [torch.full((1 << 28,), float("nan"), device="cuda", dtype=torch.float32) for _ in range(4)]
+    del blocks
+    name, cfg, lens, n_decode, _ = CASES[0]
+    g = torch.Generator().manual_seed(1)
+    prompts = [torch.randint(0, cfg["vocab_size"], (n,), generator=g).tolist() for n in lens]
+    forced = [torch.randint(0, cfg["vocab_size"], (n_decode,), generator=g).tolist() for _ in lens]
+    results = []
+    for backends in (dict(gemm_backend="auto", attention_backend="auto"),
+                     dict(gemm_backend="plain", attention_backend="plain")):
+        eng = Engine.from_random(cfg, seed=1, dtype="bfloat16", on_device=True, max_tokens=64 * 40, max_slots=4,
+                                 verbose=False, **backends)
+        slots = [eng.open() for _ in prompts]
+        outs = [eng.step(list(zip(slots, prompts)), want="last")]
+        for t in range(n_decode):
+            outs.append(eng.step([(s, [forced[i][t]]) for i, s in enumerate(slots)], want="last"))
+        eng.check()
+        results.append(torch.cat(outs).float().cpu())
+        del eng
+        torch.cuda.empty_cache()
+    fast, plain = results
+    assert not torch.isnan(fast).any() and not torch.isnan(plain).any()
+    assert (fast - plain).abs().max().item() < 2e-2 * plain.abs().max().item()
