@@ -157,3 +157,17 @@ def test_pipelined_loop_makes_the_same_decisions():
     GenerationLoop(DeviceTokenEngine(), smp2).generate([[1]], params=SamplingParams(temperature=0.0, repetition_penalty=1.2),
                                                        max_new_tokens=3)
     assert getattr(smp2, "async_calls", 0) == 0
+
+
+def test_where_a_product_is_spread_along_k():
+    """`stream_k_pays` at the points it was measured on (148 SMs, 7B layer sizes): partial sums
+    wherever whole tiles would leave SMs idle, whole tiles where they fill them."""
+    from braidinfer_b200.parts.linear import stream_k_pays
+    qkv, o, gate_up, down, head = 6144, 4096, 2 * 14336, 4096, 32768
+    for rows in (1, 8, 32, 64, 128, 256):
+        assert stream_k_pays(rows, qkv, 148) and stream_k_pays(rows, o, 148) and stream_k_pays(rows, down, 148)
+    assert stream_k_pays(8, gate_up, 148) and stream_k_pays(32, gate_up, 148)        # 224 tiles: 76 % full
+    assert not stream_k_pays(64, gate_up, 148) and not stream_k_pays(128, gate_up, 148)
+    assert not any(stream_k_pays(r, head, 148) for r in (1, 8, 64, 512))             # 256 tiles: 86 % full
+    assert not stream_k_pays(384, qkv, 148) and stream_k_pays(384, down, 148) and stream_k_pays(512, o, 148)
+    assert not stream_k_pays(513, o, 148) and not stream_k_pays(2048, down, 148)
