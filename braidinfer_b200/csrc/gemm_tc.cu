@@ -475,7 +475,11 @@ extern "C" int braid_gemm_tc(const void* x, const void* w, void* out, const floa
     if (out_dtype != BRAID_F32 && out_dtype != BRAID_BF16) BRAID_REFUSE("gemm_tc: unknown out dtype code %d", out_dtype);
     if (!error_flag) BRAID_REFUSE("gemm_tc: error_flag is required");
     const int w_rows = (mode == 2) ? 2 * ((m_out + 15) / 16) * 16 : m_out;
-    if (block_n == 0) block_n = stream_k ? pick_block_n(n_rows) : pick_block_n(n_rows);
+    // the workspace of the stream-k form is sized for the token tile that pick_block_n gives
+    // (braid_gemm_tc_workspace_bytes): another tile would write past it
+    if (stream_k && block_n != 0 && block_n != pick_block_n(n_rows))
+        BRAID_REFUSE("gemm_tc: the stream-k form picks its own token tile (%d for %d rows), not %d", pick_block_n(n_rows), n_rows, block_n);
+    if (block_n == 0) block_n = pick_block_n(n_rows);
     if (stream_k && !workspace) BRAID_REFUSE("gemm_tc: the stream-k form needs a workspace");
     cudaStream_t s = (cudaStream_t)stream;
 

@@ -391,6 +391,16 @@ def test_tensor_core_swiglu_epilogue(K, n, inter, k, sk):
     assert ((out.double() - want).abs() <= want.abs() / 100 + 1e-3).all()
 
 
+def test_stream_k_refuses_a_token_tile_its_workspace_is_not_sized_for(K):
+    from braidinfer_b200.csrc.api import KernelError
+    x, w = rnd(300, 256, dtype=torch.bfloat16), rnd(512, 256, dtype=torch.bfloat16, seed=1)
+    out = torch.empty(300, 512, device=DEV, dtype=torch.bfloat16)
+    with pytest.raises(KernelError, match="picks its own token tile"):
+        K.gemm_tc(x, w, out, block_n=128, stream_k=True)          # refused on the host: nothing is launched
+    K.gemm_tc(x, w, out, block_n=256, stream_k=True)              # the tile it would pick itself is fine
+    K.check_device_errors()
+
+
 def test_tensor_core_product_refuses_what_tma_cannot_address(K):
     x, w = rnd(4, 100, dtype=torch.bfloat16), rnd(128, 100, dtype=torch.bfloat16)     # row stride 100 is no multiple of 8
     assert not K.gemm_tc_eligible(x, w)
