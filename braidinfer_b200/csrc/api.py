@@ -294,7 +294,7 @@ class Kernels:
                 swiglu: bool = False, block_n: int = 0, stream_k: bool = False) -> None:
         """bfloat16 x [n, k] times w [m, k]^T on the tensor cores.  With `swiglu`, w holds
         gate and up rows interleaved in blocks of 16 (`interleave_gate_up`) and out is [n, I].  `stream_k` spreads the weight stream
-        evenly over all SMs whatever the shape (for a few tokens) and adds a reduce kernel."""
+        evenly over all SMs whatever the shape (for up to a few hundred tokens) and adds a reduce kernel."""
         n, k = x.shape
         w_rows = w.shape[0]
         m = out.shape[1] if swiglu else w_rows

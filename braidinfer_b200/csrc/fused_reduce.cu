@@ -1,5 +1,5 @@
 // Kernels that add up the partial products of a stream-k GEMM and go straight on with
-// what follows the product, for steps of a few tokens where every launch counts:
+// what follows the product, for steps of few tokens (up to a few hundred) where every launch counts:
 //
 //   braid_streamk_reduce_norm     h = h + sum (the residual sum, float32, written back),
 //                                 then RMSNorm of the new h: out = h * rsqrt(mean(h^2) + eps) * w.

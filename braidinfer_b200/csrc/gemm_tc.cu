@@ -75,7 +75,8 @@ struct TcCfg {
 // side share weight tiles in L2; with more than TC_GROUP_N token tiles they go in groups of
 // that many, each group against all the weights, or the tokens would not stay in L2.
 //
-// Mode 3 ("stream-k", for a few tokens, where the product only streams weights): the
+// Mode 3 ("stream-k", for steps whose whole tiles would leave SMs idle: a few tokens, or a
+// few hundred with few weight tiles): the
 // k blocks of all tiles form one line of m_tiles * n_tiles * total_kb blocks, cut into
 // gridDim.x equal ranges.  A CTA's range is a run of segments (tile, first k block,
 // count); it writes the float32 partial product of its j-th segment to slot
@@ -458,7 +459,7 @@ extern "C" long long braid_gemm_tc_workspace_bytes(int n_rows, int w_rows, int k
 // w_rows = m_out; for the SwiGLU epilogue w_rows = 2 * ceil(m_out / 16) * 16 and the rows are
 // interleaved in blocks of 16: block t holds gate rows [16t, 16t+16) then up rows [16t, 16t+16)
 // (rows past m_out are zero).  stream_k != 0 balances the
-// weight stream over all SMs for any shape (meant for a few tokens) and needs
+// weight stream over all SMs for any shape (meant for up to a few hundred tokens) and needs
 // `workspace`.  block_n = 0 picks the token tile.  With stream_k and plan_out != null only
 // the partial products are computed; plan_out receives {grid, max_segs, total_kb,
 // n_tiles, block_n, w} for the kernel that adds them up (fused_reduce.cu).
