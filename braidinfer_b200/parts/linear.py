@@ -20,19 +20,20 @@ def stream_k_pays(rows: int, w_rows: int, sms: Optional[int] = None) -> bool:
     """Whether the product of `rows` tokens with a [w_rows, k] weight should be spread evenly over
     all SMs along k as well ("stream-k" partial sums plus a kernel that adds them up) rather than
     cut into whole [128 x token tile] output tiles: it pays when whole tiles would leave SMs idle.
-    Measured on the 7B layer sizes at 1 to 512 tokens: a last round of tiles less than 70 % full
-    (80 % for up to 32 tokens, 60 % above 256) loses more than the adding-up costs."""
+    Measured on the 7B layer sizes at 1 to 2,048 tokens: up to 768 tokens a last round of tiles less
+    than 70 % full (80 % for up to 32 tokens, 60 % between 257 and 512) loses more than the adding-up
+    costs; beyond that the partial sums themselves cost too much."""
     global _SMS
     if sms is None:
         if _SMS is None:
             _SMS = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
         sms = _SMS
-    if rows > 512:
+    if rows > 768:
         return False
     block_n = 16 if rows <= 16 else 32 if rows <= 32 else 64 if rows <= 64 else 128 if rows <= 128 else 256
     tiles = -(-w_rows // 128) * -(-rows // block_n)
     fill = tiles / (-(-tiles // sms) * sms)
-    return fill < (0.8 if rows <= 32 else 0.7 if rows <= 256 else 0.6)
+    return fill < (0.8 if rows <= 32 else 0.7 if rows <= 256 else 0.6 if rows <= 512 else 0.7)
 
 
 class Linear:

@@ -170,4 +170,5 @@ def test_where_a_product_is_spread_along_k():
     assert not stream_k_pays(64, gate_up, 148) and not stream_k_pays(128, gate_up, 148)
     assert not any(stream_k_pays(r, head, 148) for r in (1, 8, 64, 512))             # 256 tiles: 86 % full
     assert not stream_k_pays(384, qkv, 148) and stream_k_pays(384, down, 148) and stream_k_pays(512, o, 148)
-    assert not stream_k_pays(513, o, 148) and not stream_k_pays(2048, down, 148)
+    assert stream_k_pays(640, o, 148) and stream_k_pays(768, down, 148) and not stream_k_pays(768, qkv, 148)
+    assert not stream_k_pays(769, o, 148) and not stream_k_pays(2048, down, 148)

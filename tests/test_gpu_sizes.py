@@ -42,6 +42,9 @@ def run(eng, prompts, n_decode, forced):
     ("7b_210_rows", mistral(num_hidden_layers=2, hidden_size=4096, num_attention_heads=32, num_key_value_heads=8,
                             head_dim=128, intermediate_size=14336, vocab_size=32000, rope_theta=1e6,
                             sliding_window=None), [120, 60, 30], 6),
+    ("7b_700_rows", mistral(num_hidden_layers=2, hidden_size=4096, num_attention_heads=32, num_key_value_heads=8,
+                            head_dim=128, intermediate_size=14336, vocab_size=32000, rope_theta=1e6,
+                            sliding_window=None), [640, 60], 4),
     ("nemo", mistral(num_hidden_layers=1, hidden_size=5120, num_attention_heads=32, num_key_value_heads=8,
                      head_dim=128, intermediate_size=14336, vocab_size=131072, rope_theta=1e6,
                      sliding_window=None), [700, 33, 128, 65], 12),
