@@ -10,15 +10,20 @@ names and meanings and widens them from one sequence to batches.
 """
 from __future__ import annotations
 
+import math
 import os
 from typing import List, Optional, Sequence, Union
 
+from .cache import PAGE_SIZE
 from .config import preset, read_config_json
 from .engine.engine import Engine
+from .models import architecture_for
+from .weights import tensor_specs_of
 from .engine.generate import Completion, GenerationLoop, GenerationStats
 from .sampling import Sampler, SamplingParams
 
 DEFAULT_MAX_SEQ_LEN_CAP = 8192      # the reference's default cap on context (model_load.rs:49, 113-116)
+RANDOM_ON_DEVICE_BYTES = 64 << 20   # random models above this many bytes of weights are drawn on the GPU
 
 
 class Model:
@@ -26,7 +31,8 @@ class Model:
 
     def __init__(self, engine: Engine, max_batch: int) -> None:
         self.engine = engine
-        self.config = engine.config
+        self.config = engine.config           # the architecture's typed configuration, or None for a hand-made ModelSpec
+        self.spec = engine.spec
         self.sampler = Sampler(engine.kernels, engine.device)
         self.max_batch = max_batch
         self.last_stats: Optional[GenerationStats] = None
@@ -43,7 +49,7 @@ class Model:
         single = len(prompts) > 0 and isinstance(prompts[0], int)
         plist = [list(prompts)] if single else [list(p) for p in prompts]
         if stop_tokens is None:
-            stop_tokens = self.config.eos_token_id or ()
+            stop_tokens = self.spec.eos_token_ids
         loop = GenerationLoop(self.engine, self.sampler, max_batch=self.max_batch)
         out = loop.generate(plist, params, max_new_tokens, stop_tokens)
         self.last_stats = loop.stats
@@ -102,14 +108,17 @@ def load(model: str, dtype: str = "bfloat16", max_seq_len: Optional[int] = None,
             raise FileNotFoundError(f"MODEL={model!r} is not a folder (use a model folder or random:<preset>)")
         cfg_dict = read_config_json(model)
         source = model
+    arch = architecture_for(cfg_dict)
+    spec = arch.build_spec(arch.config_from_dict(cfg_dict))
     if max_seq_len is None:
-        max_seq_len = min(int(cfg_dict.get("max_position_embeddings", 2048)), DEFAULT_MAX_SEQ_LEN_CAP)
-    per_seq = -(-max_seq_len // 64) * 64
+        max_seq_len = min(spec.max_position or 2048, DEFAULT_MAX_SEQ_LEN_CAP)
+    per_seq = -(-max_seq_len // PAGE_SIZE) * PAGE_SIZE
     opts = dict(dtype=dtype, max_tokens=per_seq * max_batch, max_slots=max_batch, device=device, verbose=verbose)
     opts.update(engine_options)
     if source is None:
-        big = cfg_dict["hidden_size"] * cfg_dict["num_hidden_layers"] > 1 << 14
-        engine = Engine.from_random(cfg_dict, seed, on_device=big, **opts)
+        # a large model is drawn on the device: the CPU draw of gigabytes takes minutes
+        n_bytes = sum(2 * math.prod(ts.shape) for ts in tensor_specs_of(spec).values())
+        engine = Engine.from_random(cfg_dict, seed, on_device=n_bytes > RANDOM_ON_DEVICE_BYTES, **opts)
     else:
         engine = Engine.from_folder(source, **opts)
     return Model(engine, max_batch)

@@ -17,9 +17,10 @@ import numpy as np
 import torch
 
 from ..parts.spec import CacheRequest
+from ..csrc.build import page_size as _page_size
 from .pages import CacheError, GroupPages, SlotTable
 
-PAGE_SIZE = 64
+PAGE_SIZE = _page_size()      # csrc/page.h holds the number
 
 
 @dataclass
@@ -81,6 +82,7 @@ class CacheManager:
             if cache_of is not None:
                 if owners[cache_of] is None:
                     raise CacheError(f"schedule entry {e} reads the cache of entry {cache_of}, which keeps none")
+                self._check_reader(e, req, cache_of, plan[cache_of][0])
                 self.entry_group.append(owners[cache_of])
                 self.entry_read_only.append(True)
             else:
@@ -91,6 +93,25 @@ class CacheManager:
         for (_req, _co, sb) in plan:
             self.state.append(torch.zeros((max_slots, sb), dtype=torch.uint8, device=device) if sb > 0 else None)
         self.max_blocks_per_seq = max_blocks_per_seq or self.num_pages
+
+    @staticmethod
+    def _check_reader(e: int, reader: Optional[CacheRequest], owner_entry: int, owner: CacheRequest) -> None:
+        """A run that reads another run's cache must find there what its mixer expects: the
+        same heads and head size (the layout's strides), and every key its own window still
+        sees (a windowed owner gives pages back once its own window has passed them)."""
+        if reader is None:
+            return                            # a mixer that keeps nothing ignores the view it is handed
+        if (reader.num_kv_heads, reader.head_dim) != (owner.num_kv_heads, owner.head_dim):
+            raise CacheError(
+                f"schedule entry {e} reads the cache of entry {owner_entry}, but its mixer expects "
+                f"{reader.num_kv_heads} kv heads of {reader.head_dim} and that cache holds "
+                f"{owner.num_kv_heads} of {owner.head_dim}")
+        if owner.kind == "window":
+            if reader.kind != "window" or reader.window is None or reader.window > owner.window:
+                raise CacheError(
+                    f"schedule entry {e} reads the cache of entry {owner_entry}, which keeps a window of "
+                    f"{owner.window} positions only; the reader "
+                    + ("sees every earlier position" if reader.kind != "window" else f"has a window of {reader.window}"))
 
     # ------------------------------------------------------------------ slots
     def alloc_slot(self) -> int:

@@ -34,6 +34,16 @@ def _ptr(t: Optional[torch.Tensor]):
     return None if t is None else t.data_ptr()
 
 
+def token_tile(rows: int) -> int:
+    """The token tile (UMMA N) of the tensor-core product for a step of `rows` tokens: the
+    smallest of 16, 32, 64, 128, 256 that holds them, 256 beyond.  The one place the ladder
+    is written: the kernel is told the tile, and whoever sizes work by it asks here."""
+    for t in (16, 32, 64, 128):
+        if rows <= t:
+            return t
+    return 256
+
+
 def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     """The weight layout of the SwiGLU epilogue: blocks of 32 rows, each the gate rows
     [16t, 16t+16) followed by the up rows [16t, 16t+16); rows past the true size are zero."""
@@ -68,7 +78,7 @@ class Kernels:
         self.path = str(path)
         self.launches = 0          # kernels launched through this object (for measurements)
         self._declare()
-        self._error_flag = torch.zeros(4, dtype=torch.int32, device="cuda")
+        self._error_flag = torch.zeros(8, dtype=torch.int32, device="cuda")
         self._tc_workspace: Optional[torch.Tensor] = None
         self._attn_libs = {}
         self.pending_partial = None     # the open PartialProduct, if any (it owns the GEMM workspace)
@@ -92,10 +102,10 @@ class Kernels:
         L.braid_gather_i32.restype = c_int
         L.braid_attn_simple.argtypes = [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                                         c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                                        c_float, c_void_p]
+                                        c_float, c_void_p, c_void_p]
         L.braid_gemm_simt.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                                       c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_void_p]
-        L.braid_gemm_tc.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+        L.braid_gemm_tc.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int,
                                     c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_int, c_int,
                                     c_void_p, c_void_p, c_void_p]
         L.braid_streamk_reduce.argtypes = [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_longlong,
@@ -103,7 +113,7 @@ class Kernels:
         L.braid_streamk_reduce_norm.argtypes = [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int,
                                                 c_void_p, c_int, c_int, c_float, c_void_p]
         L.braid_streamk_reduce_rope_kv.argtypes = [c_void_p] * 8 + [c_int] * 9 + [c_void_p, c_void_p]
-        L.braid_gemm_tc_workspace_bytes.argtypes = [c_int, c_int, c_int]
+        L.braid_gemm_tc_workspace_bytes.argtypes = [c_int, c_int, c_int, c_int]
         L.braid_gemm_tc_workspace_bytes.restype = c_longlong
         L.braid_argmax.argtypes = [c_void_p, c_longlong, c_void_p, c_int, c_int, c_void_p, c_void_p]
         L.braid_sample.argtypes = [c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_int] + [c_void_p] * 12 + \
@@ -133,7 +143,9 @@ class Kernels:
             names = ["cache write outside the sequence's pages", "tensor-core GEMM wait ran out",
                      "NaN among the logits",
                      "tcgen05 attention gave up (a wait ran out, a visible position had no page, or its shared "
-                     "memory was not 1024-byte aligned)"]
+                     "memory was not 1024-byte aligned)",
+                     "attention met a visible position whose page is absent or outside the cache (it read page 0 "
+                     "instead; the result is wrong)"]
             raise KernelError("device error: " + "; ".join(n for n, f in zip(names, flags) if f))
 
     # ------------------------------------------------------------------ row-wise kernels
@@ -195,7 +207,8 @@ class Kernels:
         self._check(self.lib.braid_attn_simple(
             q.data_ptr(), out.data_ptr(), dtype_code(out.dtype), cache.data_ptr(), page_table.data_ptr(),
             positions.data_ptr(), token_seq.data_ptr(), q.stride(0), out.stride(0), rows, nqh, nkh, hd,
-            page_size, page_table.shape[1], cache.shape[0], int(window or 0), float(scale), self._stream()),
+            page_size, page_table.shape[1], cache.shape[0], int(window or 0), float(scale),
+            self._error_flag.data_ptr() + 16, self._stream()),
             "attn_simple")
 
     @staticmethod
@@ -211,7 +224,7 @@ class Kernels:
             lib = ctypes.CDLL(str(build.attention_library(head_dim, verbose=self._verbose)))
             lib.braid_last_error.restype = c_char_p
             lib.braid_attn_mma.restype = c_int
-            lib.braid_attn_mma.argtypes = [c_void_p] * 9 + [c_int] * 12 + [c_float, c_void_p]
+            lib.braid_attn_mma.argtypes = [c_void_p] * 9 + [c_int] * 13 + [c_float, c_void_p, c_void_p]
             lib.braid_attn_mma_partial_floats.restype = c_longlong
             lib.braid_attn_mma_partial_floats.argtypes = [c_int, c_int, c_int]
             lib.braid_attn_tc_supported.restype = c_int
@@ -227,6 +240,13 @@ class Kernels:
         return lib
 
     @staticmethod
+    def _check_pages(cache: torch.Tensor) -> None:
+        """The tensor-core attention kernels tile pages at compile time (csrc/page.h)."""
+        if cache.dim() != 5 or cache.shape[3] != build.page_size():
+            raise KernelError(f"the tensor-core attention reads a cache [pages, 2, kv_heads, {build.page_size()}, "
+                              f"head_dim]; got {tuple(cache.shape)}")
+
+    @staticmethod
     def attn_tc_supports(head_dim: int) -> bool:
         return head_dim in (64, 128)
 
@@ -235,6 +255,7 @@ class Kernels:
                 nqh: int, nkh: int, hd: int, window: Optional[int], scale: float) -> None:
         """bfloat16 attention of prompts over the cache on tcgen05 (head sizes 64 and 128)."""
         lib = self.attn_mma_library(hd)
+        self._check_pages(cache)
         if not lib.has_tc:
             raise KernelError(f"the tcgen05 attention is built for head sizes 64 and 128, not {hd}")
         self.launches += 1
@@ -256,6 +277,7 @@ class Kernels:
         """bfloat16 attention over the cache on the tensor cores; `n_splits` > 1 slices the
         context (for steps of few tokens) and merges the slices in a second kernel."""
         lib = self.attn_mma_library(hd)
+        self._check_pages(cache)
         rows = out.shape[0]
         partial = None
         if n_splits > 1:
@@ -269,8 +291,8 @@ class Kernels:
         rc = lib.braid_attn_mma(q.data_ptr(), out.data_ptr(), _ptr(partial), cache.data_ptr(), page_table.data_ptr(),
                                 q_start.data_ptr(), q_len.data_ptr(), kv_before.data_ptr(), token_seq.data_ptr(),
                                 q.stride(0), out.stride(0), rows, n_seqs, max_q_len, nqh, nkh, hd,
-                                page_table.shape[1], int(window or 0), n_splits, 1 if few_tokens else 0,
-                                float(scale), self._stream())
+                                page_table.shape[1], cache.shape[0], int(window or 0), n_splits,
+                                1 if few_tokens else 0, float(scale), self._error_flag.data_ptr() + 16, self._stream())
         if rc != 0:
             raise KernelError(f"attn_mma: {lib.braid_last_error().decode(errors='replace')} (code {rc})")
 
@@ -278,6 +300,12 @@ class Kernels:
     def gemm_simt(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, residual: Optional[torch.Tensor] = None) -> None:
         n, k = x.shape
         m = w.shape[0]
+        if x.dtype != w.dtype:
+            # the kernel reads both operands as one element type: a mixed call would read the
+            # narrower operand past its end
+            raise KernelError(f"gemm_simt: x is {x.dtype} and w is {w.dtype}; both operands must have one element type")
+        if w.shape[1] != k or tuple(out.shape) != (n, m):
+            raise KernelError(f"gemm_simt: shapes x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} do not fit")
         mode = 1 if residual is not None else 0
         self.launches += 1
         self._check(self.lib.braid_gemm_simt(x.data_ptr(), w.data_ptr(), out.data_ptr(), _ptr(residual),
@@ -289,6 +317,12 @@ class Kernels:
             self._tc_workspace = torch.empty(max((nbytes + 3) // 4, 1 << 22), dtype=torch.float32, device="cuda")
             self.workspace_generation += 1
         return self._tc_workspace
+
+    def _stream_k_workspace(self, n: int, w_rows: int, k: int, block_n: int) -> torch.Tensor:
+        need = self.lib.braid_gemm_tc_workspace_bytes(n, w_rows, k, block_n)
+        if need < 0:
+            raise KernelError(f"gemm_tc: no stream-k plan for {n} rows x {w_rows} x {k} with token tile {block_n}")
+        return self.tc_workspace(need)
 
     def gemm_tc(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, residual: Optional[torch.Tensor] = None,
                 swiglu: bool = False, block_n: int = 0, stream_k: bool = False) -> None:
@@ -302,15 +336,17 @@ class Kernels:
             raise KernelError(f"the SwiGLU epilogue wants {2 * (-(-m // 16) * 16)} interleaved weight rows for "
                               f"{m} outputs, got {w_rows} (see interleave_gate_up)")
         mode = 2 if swiglu else (1 if residual is not None else 0)
+        block_n = block_n or token_tile(n)
         ws = None
         if stream_k:
             if self.pending_partial is not None:
                 raise KernelError("a deferred sum still lives in the GEMM workspace; resolve it before the next "
                                   "stream-k product")
-            ws = self.tc_workspace(self.lib.braid_gemm_tc_workspace_bytes(n, w_rows, k))
+            ws = self._stream_k_workspace(n, w_rows, k, block_n)
             self.launches += 1
         self.launches += 1
         self._check(self.lib.braid_gemm_tc(x.data_ptr(), w.data_ptr(), out.data_ptr(), _ptr(residual), _ptr(ws),
+                                           ws.numel() * 4 if ws is not None else 0,
                                            dtype_code(out.dtype), mode, n, m, k, x.stride(0), w.stride(0),
                                            out.stride(0), block_n, int(stream_k), None,
                                            self._error_flag.data_ptr() + 4, self._stream()), "gemm_tc")
@@ -323,11 +359,12 @@ class Kernels:
             raise KernelError("a deferred sum still lives in the GEMM workspace; resolve it first")
         n, k = x.shape
         w_rows = w.shape[0]
-        ws = self.tc_workspace(self.lib.braid_gemm_tc_workspace_bytes(n, w_rows, k))
+        block_n = token_tile(n)
+        ws = self._stream_k_workspace(n, w_rows, k, block_n)
         plan = (c_int * 6)()
         self.launches += 1
-        self._check(self.lib.braid_gemm_tc(x.data_ptr(), w.data_ptr(), None, None, ws.data_ptr(), F32, 0, n, w_rows, k,
-                                           x.stride(0), w.stride(0), 0, 0, 1, plan,
+        self._check(self.lib.braid_gemm_tc(x.data_ptr(), w.data_ptr(), None, None, ws.data_ptr(), ws.numel() * 4,
+                                           F32, 0, n, w_rows, k, x.stride(0), w.stride(0), 0, block_n, 1, plan,
                                            self._error_flag.data_ptr() + 4, self._stream()), "gemm_tc_partial")
         p = PartialProduct(ws, plan, n, w_rows)
         self.pending_partial = p

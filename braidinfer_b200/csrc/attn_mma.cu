@@ -23,7 +23,8 @@
 #endif
 static_assert(BRAID_HD % 16 == 0 && BRAID_HD >= 16 && BRAID_HD <= 256, "head_dim must be a multiple of 16 in [16, 256]");
 
-#define PAGE 64
+#include "page.h"
+#define PAGE BRAID_PAGE_SIZE
 
 struct AttnMmaArgs {
     const __nv_bfloat16* q;      // [rows, q_row_stride]; head h at column h * HD
@@ -37,6 +38,8 @@ struct AttnMmaArgs {
     int q_row_stride, out_row_stride;
     int nqh, nkh, table_cols, window, n_splits;
     float scale_log2;            // softmax scale * log2(e)
+    int num_pages;               // pages of the cache: a table entry outside [0, num_pages) is never followed
+    int* error_flag;             // raised when a tile of visible keys has no page or one outside the cache
 };
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
@@ -65,6 +68,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 
 template <int HD, int NW, int BN, int ST>
 struct AttnCfg {
+    static_assert(PAGE % BN == 0, "a key tile must not straddle a page");
     static constexpr int BM = 16 * NW;
     static constexpr int ROW = HD * 2 + 16;               // bytes per padded shared-memory row
     static constexpr int Q_BYTES = BM * ROW;
@@ -115,8 +119,13 @@ attn_mma_kernel(AttnMmaArgs a) {
     constexpr int CH = HD / 8;                             // 16-byte chunks per row
     auto load_tile = [&](int t, int stage) {
         const int key0 = t * BN;
-        const int page = table[key0 / PAGE];
-        const int off = key0 - (key0 / PAGE) * PAGE;
+        const int block = key0 / PAGE;
+        int page = (block < a.table_cols) ? table[block] : -1;
+        if (page < 0 || page >= a.num_pages) {             // flag it and read page 0 instead: no address is made from it
+            if (tid == 0) atomicExch(a.error_flag, 1);
+            page = 0;
+        }
+        const int off = key0 - block * PAGE;
         const __nv_bfloat16* kbase = a.cache + (((size_t)page * 2) * a.nkh + kvh) * PAGE * HD + (size_t)off * HD;
         const __nv_bfloat16* vbase = kbase + (size_t)a.nkh * PAGE * HD;
         uint8_t* dk = sKV + stage * 2 * C::TILE_BYTES;
@@ -370,9 +379,11 @@ extern "C" int braid_attn_mma_decode_slots(int kind) {
 extern "C" int braid_attn_mma(const void* q, void* out, void* partial, const void* cache, const int* page_table,
                               const int* q_start, const int* q_len, const int* kv_before, const int* token_seq,
                               int q_row_stride, int out_row_stride, int rows, int n_seqs, int max_q_len,
-                              int nqh, int nkh, int hd, int table_cols, int window, int n_splits, int kind,
-                              float scale, void* stream) {
+                              int nqh, int nkh, int hd, int table_cols, int num_pages, int window, int n_splits, int kind,
+                              float scale, int* error_flag, void* stream) {
     if (rows <= 0 || n_seqs <= 0) return BRAID_OK;
+    if (!error_flag) BRAID_REFUSE("attn_mma: error_flag is required");
+    if (num_pages <= 0 || table_cols <= 0) BRAID_REFUSE("attn_mma: the cache has no pages (pages=%d, table columns=%d)", num_pages, table_cols);
     if (hd != BRAID_HD) BRAID_REFUSE("attn_mma: this library was compiled for head_dim=%d, not %d", BRAID_HD, hd);
     if (nqh <= 0 || nkh <= 0 || nqh % nkh) BRAID_REFUSE("attn_mma: %d query heads do not divide into %d kv heads", nqh, nkh);
     if ((q_row_stride % 8) || ((uintptr_t)q & 15)) BRAID_REFUSE("attn_mma: queries must be 16-byte aligned rows");
@@ -381,7 +392,7 @@ extern "C" int braid_attn_mma(const void* q, void* out, void* partial, const voi
     if (n_splits > 1 && !partial) BRAID_REFUSE("attn_mma: n_splits > 1 needs the partial buffer");
     AttnMmaArgs a{(const __nv_bfloat16*)q, (__nv_bfloat16*)out, (float*)partial, (const __nv_bfloat16*)cache, page_table,
                   q_start, q_len, kv_before, q_row_stride, out_row_stride, nqh, nkh, table_cols, window, n_splits,
-                  scale * 1.4426950408889634f};
+                  scale * 1.4426950408889634f, num_pages, error_flag};
     cudaStream_t s = (cudaStream_t)stream;
     int rc;
     if (kind == 0) rc = launch_attn<4, 64, 2>(a, n_seqs, max_q_len, s);
@@ -411,8 +422,8 @@ extern "C" long long braid_attn_noalloc_capacity_floats(void) { return BRAID_ATT
 extern "C" int braid_attn_mma_noalloc(const void* q, void* out, const void* cache, const int* page_table,
                                       const int* q_start, const int* q_len, const int* kv_before, const int* token_seq,
                                       int q_row_stride, int out_row_stride, int rows, int n_seqs, int max_q_len,
-                                      int nqh, int nkh, int hd, int table_cols, int window, int n_splits, int kind,
-                                      float scale, void* stream) {
+                                      int nqh, int nkh, int hd, int table_cols, int num_pages, int window, int n_splits,
+                                      int kind, float scale, int* error_flag, void* stream) {
     if (rows <= 0 || n_seqs <= 0) return BRAID_OK;
     if (n_splits < 1) n_splits = 1;
     const long long need = braid_attn_mma_partial_floats(rows, nqh, n_splits);
@@ -436,5 +447,5 @@ extern "C" int braid_attn_mma_noalloc(const void* q, void* out, const void* cach
     }
     return braid_attn_mma(q, out, n_splits > 1 ? g_noalloc_ptr[dev] : nullptr, cache, page_table, q_start, q_len,
                           kv_before, token_seq, q_row_stride, out_row_stride, rows, n_seqs, max_q_len, nqh, nkh, hd,
-                          table_cols, window, n_splits, kind, scale, stream);
+                          table_cols, num_pages, window, n_splits, kind, scale, error_flag, stream);
 }

@@ -25,8 +25,18 @@
 //     (cudaGetSymbolAddress, with that device current).  That lookup is set-up work:
 //     make the first call on a device before any stream capture begins.
 //
+//   * Consistent arguments.  "Every slot that is read was written first" holds only when the
+//     host scalars describe the device tables: max_q_len must be at least the largest
+//     q_len[s], rows the number of rows the tables speak of, n_seqs their sequences.  With a
+//     max_q_len that is too small the attention grid leaves the slots of the rows beyond
+//     it unwritten and the merge reads what an earlier call left there (with a buffer of
+//     the caller's own the same mistake would read the caller's own stale data).  The
+//     entry point cannot see the device tables, so it cannot check this.
+//
 // It calls no cudaMalloc, cudaFree or other allocating routine.  Arguments are those of
-// braid_attn_mma() without `partial`; see attn_mma.cu for their meaning.
+// braid_attn_mma() without `partial` (see attn_mma.cu for their meaning); `error_flag` is
+// one int of device memory that the caller owns, set to 1 if a page-table entry of a
+// visible key lies outside [0, num_pages).
 #pragma once
 
 #define BRAID_ATTN_NOALLOC_MAX_FLOATS (2 * 1024 * 1024)
@@ -38,8 +48,8 @@ extern "C" {
 int braid_attn_mma_noalloc(const void* q, void* out, const void* cache, const int* page_table,
                            const int* q_start, const int* q_len, const int* kv_before, const int* token_seq,
                            int q_row_stride, int out_row_stride, int rows, int n_seqs, int max_q_len,
-                           int nqh, int nkh, int hd, int table_cols, int window, int n_splits, int kind,
-                           float scale, void* stream);
+                           int nqh, int nkh, int hd, int table_cols, int num_pages, int window, int n_splits,
+                           int kind, float scale, int* error_flag, void* stream);
 
 // The capacity of the built-in scratch, in floats (for callers that size their steps by it).
 long long braid_attn_noalloc_capacity_floats(void);

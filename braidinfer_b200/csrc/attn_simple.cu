@@ -22,6 +22,7 @@ struct AttnSimpleArgs {
     int q_row_stride, out_row_stride;
     int rows, nqh, nkh, hd, page_size, table_cols, num_pages, window;
     float scale;
+    int* error_flag;          // raised when a visible position has no page, or one outside the cache
 };
 
 #define ATTN_SIMPLE_WARPS 4
@@ -65,7 +66,11 @@ attn_simple_kernel(AttnSimpleArgs a) {
         const T* vrow = nullptr;
         if (j <= pos) {
             const int block = j / a.page_size, off = j - block * a.page_size;
-            const int page = table[block];
+            int page = (block < a.table_cols) ? table[block] : -1;
+            if (page < 0 || page >= a.num_pages) {      // never followed: flag it and read page 0 instead
+                atomicExch(a.error_flag, 1);
+                page = 0;
+            }
             const T* kbase = (const T*)a.cache + ((size_t)page * 2 * a.nkh + kvh) * head_stride + (size_t)off * a.hd;
             vrow = kbase + (size_t)a.nkh * head_stride;
             float dot = 0.f;
@@ -106,12 +111,14 @@ extern "C" int braid_attn_simple(const void* q, void* out, int dtype, const void
                                  const int* page_table, const int* positions, const int* token_seq,
                                  int q_row_stride, int out_row_stride, int rows, int nqh, int nkh, int hd,
                                  int page_size, int table_cols, int num_pages, int window, float scale,
-                                 void* stream) {
+                                 int* error_flag, void* stream) {
     if (rows <= 0) return BRAID_OK;
+    if (!error_flag) BRAID_REFUSE("attn_simple: error_flag is required");
+    if (num_pages <= 0 || table_cols <= 0 || page_size <= 0) BRAID_REFUSE("attn_simple: the cache has no pages (pages=%d, table columns=%d, page size=%d)", num_pages, table_cols, page_size);
     if (nqh <= 0 || nkh <= 0 || nqh % nkh != 0) BRAID_REFUSE("attn_simple: %d query heads do not divide into %d kv heads", nqh, nkh);
     if (hd <= 0 || hd > ATTN_SIMPLE_MAX_HD) BRAID_REFUSE("attn_simple: head_dim=%d outside (0, %d]", hd, ATTN_SIMPLE_MAX_HD);
     AttnSimpleArgs a{q, out, cache, page_table, positions, token_seq, q_row_stride, out_row_stride,
-                     rows, nqh, nkh, hd, page_size, table_cols, num_pages, window, scale};
+                     rows, nqh, nkh, hd, page_size, table_cols, num_pages, window, scale, error_flag};
     const long long items = (long long)rows * nqh;
     const long long blocks = (items + ATTN_SIMPLE_WARPS - 1) / ATTN_SIMPLE_WARPS;
     if (blocks > 0x7fffffffLL) BRAID_REFUSE("attn_simple: %lld (token, head) pairs exceed one launch", items);

@@ -47,7 +47,9 @@
 
 #define FA_BM 128
 #define FA_BN 64                                 // keys per tile: one page
-#define FA_PAGE 64
+#include "page.h"
+#define FA_PAGE BRAID_PAGE_SIZE
+static_assert(FA_PAGE == 64, "a key tile of this kernel is one page of 64 positions");
 #define FA_THREADS 192                           // TMA warp, MMA warp, 4 softmax warps
 #define FA_HB (BRAID_HD / 64)                    // 64-element blocks of the head dimension
 #define FA_QBLOCK_BYTES (128 * 128)              // [128 rows][64 elements] bf16, 128-byte rows
@@ -240,6 +242,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             // key and value tiles go out independently, each as soon as its stage is free
             int jk = 0, jv = 0;
             uint32_t idle = 0;
+            uint64_t idle_since = 0;
             while (jk < n_tiles || jv < n_tiles) {
                 bool moved = false;
                 const bool k_turn = jk < n_tiles && mbar_try_wait(&k_empty[jk % FA_KST], (uint32_t)((jk / FA_KST) & 1) ^ 1u);
@@ -261,9 +264,14 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                     if (k_turn) ++jk; else ++jv;
                     moved = true;
                 }
-                if (moved) { idle = 0; continue; }
+                if (moved) { idle = 0; idle_since = 0; continue; }
                 if (++idle >= TC_SPIN_LIMIT) { *abort_flag = 1; break; }
-                if ((idle & 1023u) == 1023u && *abort_flag) break;
+                if ((idle & 1023u) == 1023u) {              // the same bound as mbar_wait: time on the device's clock
+                    if (*abort_flag) break;
+                    const uint64_t now = global_timer_ns();
+                    if (idle_since == 0) idle_since = now;
+                    else if (now - idle_since > TC_WAIT_LIMIT_NS) { *abort_flag = 1; break; }
+                }
             }
         }
     } else if (warp == 1) {

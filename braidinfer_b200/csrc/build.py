@@ -29,11 +29,20 @@ COMMON_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "--expt
 # Sources that do not depend on a model size.
 CORE_SOURCES = ["errors.cu", "elementwise.cu", "attn_simple.cu", "gemm_simt.cu", "gemm_tc.cu",
                 "fused_reduce.cu", "sampling.cu"]
-HEADERS = ["common.cuh", "streamk.cuh", "tcgen05.cuh", "attn_noalloc.h"]
+HEADERS = ["common.cuh", "streamk.cuh", "tcgen05.cuh", "attn_noalloc.h", "page.h"]
 
 
 class BuildError(RuntimeError):
     pass
+
+
+def page_size() -> int:
+    """Positions per cache page: read from page.h, the one place the number is written."""
+    import re
+    m = re.search(r"^#define\s+BRAID_PAGE_SIZE\s+(\d+)\s*$", (CSRC / "page.h").read_text(), re.M)
+    if not m:
+        raise BuildError("page.h does not define BRAID_PAGE_SIZE")
+    return int(m.group(1))
 
 
 def find_nvcc() -> str:

@@ -446,13 +446,13 @@ static StreamKPlan plan_stream_k(int n_rows, int w_rows, int k_in, int block_n) 
     return p;
 }
 
-static int pick_block_n(int n_rows) {
-    return n_rows <= 16 ? 16 : n_rows <= 32 ? 32 : n_rows <= 64 ? 64 : n_rows <= 128 ? 128 : 256;
-}
+static bool valid_block_n(int b) { return b == 16 || b == 32 || b == 64 || b == 128 || b == 256; }
 
-// Bytes of float32 scratch that the stream-k form needs for this shape.
-extern "C" long long braid_gemm_tc_workspace_bytes(int n_rows, int w_rows, int k_in) {
-    return plan_stream_k(n_rows, w_rows, k_in, pick_block_n(n_rows)).bytes;
+// Bytes of float32 scratch that the stream-k form needs for this shape and token tile
+// (-1: not a token tile this kernel has).
+extern "C" long long braid_gemm_tc_workspace_bytes(int n_rows, int w_rows, int k_in, int block_n) {
+    if (!valid_block_n(block_n) || n_rows <= 0 || w_rows <= 0 || k_in <= 0) return -1;
+    return plan_stream_k(n_rows, w_rows, k_in, block_n).bytes;
 }
 
 // x: [n_rows, k_in] bf16 (row stride ldx); w: [w_rows, k_in] bf16 (row stride ldw), where
@@ -460,11 +460,13 @@ extern "C" long long braid_gemm_tc_workspace_bytes(int n_rows, int w_rows, int k
 // interleaved in blocks of 16: block t holds gate rows [16t, 16t+16) then up rows [16t, 16t+16)
 // (rows past m_out are zero).  stream_k != 0 balances the
 // weight stream over all SMs for any shape (meant for up to a few hundred tokens) and needs
-// `workspace`.  block_n = 0 picks the token tile.  With stream_k and plan_out != null only
+// `workspace` of at least braid_gemm_tc_workspace_bytes() bytes for the same shape and tile
+// (`workspace_bytes` says how many it has; too few is refused, never written past).
+// block_n names the token tile: 16, 32, 64, 128 or 256.  With stream_k and plan_out != null only
 // the partial products are computed; plan_out receives {grid, max_segs, total_kb,
 // n_tiles, block_n, w} for the kernel that adds them up (fused_reduce.cu).
 extern "C" int braid_gemm_tc(const void* x, const void* w, void* out, const float* res, void* workspace,
-                             int out_dtype, int mode, int n_rows, int m_out, int k_in,
+                             long long workspace_bytes, int out_dtype, int mode, int n_rows, int m_out, int k_in,
                              long long ldx, long long ldw, long long ldo, int block_n, int stream_k,
                              int* plan_out, int* error_flag, void* stream) {
     if (n_rows <= 0 || m_out <= 0) return BRAID_OK;
@@ -476,12 +478,16 @@ extern "C" int braid_gemm_tc(const void* x, const void* w, void* out, const floa
     if (out_dtype != BRAID_F32 && out_dtype != BRAID_BF16) BRAID_REFUSE("gemm_tc: unknown out dtype code %d", out_dtype);
     if (!error_flag) BRAID_REFUSE("gemm_tc: error_flag is required");
     const int w_rows = (mode == 2) ? 2 * ((m_out + 15) / 16) * 16 : m_out;
-    // the workspace of the stream-k form is sized for the token tile that pick_block_n gives
-    // (braid_gemm_tc_workspace_bytes): another tile would write past it
-    if (stream_k && block_n != 0 && block_n != pick_block_n(n_rows))
-        BRAID_REFUSE("gemm_tc: the stream-k form picks its own token tile (%d for %d rows), not %d", pick_block_n(n_rows), n_rows, block_n);
-    if (block_n == 0) block_n = pick_block_n(n_rows);
+    if (!valid_block_n(block_n)) BRAID_REFUSE("gemm_tc: token tile %d is not one of 16, 32, 64, 128, 256", block_n);
     if (stream_k && !workspace) BRAID_REFUSE("gemm_tc: the stream-k form needs a workspace");
+    if (stream_k) {
+        // the partial sums of every CTA's segments must fit: checked here, on the host, for the very
+        // plan the kernel will walk
+        const long long need = plan_stream_k(n_rows, w_rows, k_in, block_n).bytes;
+        if (need > workspace_bytes)
+            BRAID_REFUSE("gemm_tc: the stream-k form of %d rows x %d x %d with token tile %d needs %lld bytes of workspace, "
+                         "it was given %lld", n_rows, w_rows, k_in, block_n, need, workspace_bytes);
+    }
     cudaStream_t s = (cudaStream_t)stream;
 
     CUtensorMap mw, mx;

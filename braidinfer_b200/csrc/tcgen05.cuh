@@ -5,7 +5,12 @@
 #include "common.cuh"
 #include <cuda.h>
 
-#define TC_SPIN_LIMIT (1u << 24)
+// A wait gives up after this much time on the device's clock (%globaltimer, nanoseconds),
+// looked at every 1024 polls, and in any case after TC_SPIN_LIMIT polls.  Time, not a count
+// of polls, is the bound: under programmatic dependent launch a consumer warp may poll for
+// as long as the kernel before this one runs, which a poll count cannot know.
+#define TC_WAIT_LIMIT_NS 2000000000ull
+#define TC_SPIN_LIMIT (1u << 27)
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -25,10 +30,21 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     return ok != 0;
 }
 // Bounded wait.  Returns false when it gave up or another warp already had.
+__device__ __forceinline__ uint64_t global_timer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+    uint64_t t0 = 0;
     for (uint32_t i = 0; i < TC_SPIN_LIMIT; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
-        if ((i & 1023u) == 1023u && *abort_flag) return false;
+        if ((i & 1023u) == 1023u) {
+            if (*abort_flag) return false;
+            const uint64_t now = global_timer_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > TC_WAIT_LIMIT_NS) break;
+        }
     }
     *abort_flag = 1;
     return false;

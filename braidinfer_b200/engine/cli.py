@@ -124,9 +124,9 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     m = load(model, dtype=dtype, max_seq_len=max_seq_len, max_batch=max(1, min(len(prompts_text), 64)),
              seed=_env_int("WEIGHT_SEED", 0))
     print(f"LOAD PROFILE: load = {(time.perf_counter() - t_load) * 1000:.0f} ms", file=sys.stderr)
-    cfg = m.config
-    codec = TextCodec(None if model.startswith("random:") else model, cfg.vocab_size, cfg.bos_token_id)
-    stop = list(cfg.eos_token_id or ())
+    spec = m.spec
+    codec = TextCodec(None if model.startswith("random:") else model, spec.vocab_size, spec.bos_token_id)
+    stop = list(spec.eos_token_ids)
     print(f"max_seq_len: {m.engine.max_tokens // m.max_batch}", file=sys.stderr)
     print(f"stop tokens: {stop}", file=sys.stderr)
     prompts = [codec.encode(p) for p in prompts_text]

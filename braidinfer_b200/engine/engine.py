@@ -58,7 +58,11 @@ class Engine:
         if isinstance(tensors_or_folder, (str, os.PathLike)):
             tensors = load_tensors(str(tensors_or_folder), specs, self.dtype, self.device)
         else:
-            tensors = tensors_or_folder
+            # tensors handed over directly get the loader's rule for element types: a float32 run
+            # widens every floating tensor (exactly), a bfloat16 run keeps what it is given
+            tensors = {n: (t.to(self.device).float() if self.dtype == torch.float32 and t.is_floating_point()
+                           and t.dtype != torch.float32 else t.to(self.device))
+                       for n, t in tensors_or_folder.items()}
         self.weight_bytes = sum(t.numel() * t.element_size() for t in tensors.values())
         self.model.load(tensors)
         del tensors
@@ -188,10 +192,17 @@ class Engine:
         ctx.kernels = self.kernels
         if device_tokens is not None:
             self.kernels.gather_i32(device_tokens[0], self.packer.token_source_view, ctx.token_ids)
-        if graphable:
-            logits = self._graph_step(ctx)
-        else:
-            logits = self.model.forward(ctx, self.cache)
+        try:
+            if graphable:
+                logits = self._graph_step(ctx)
+            else:
+                logits = self.model.forward(ctx, self.cache)
+        except BaseException:
+            # a part gave up in mid-step: a sum it left deferred must not outlive the step, or
+            # every later stream-k product would find the workspace taken
+            ctx.drop_deferred()
+            self.kernels.pending_partial = None
+            raise
         self.cache.end_step(slots, n_new)
         self.steps_run += 1
         return logits

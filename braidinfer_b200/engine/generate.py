@@ -23,7 +23,7 @@ import torch
 from ..sampling.params import SamplingParams
 from ..sampling.rng import entropy_seed
 
-PAGE = 64     # a sequence's tokens are counted in units of the cache's page
+from ..cache import PAGE_SIZE as PAGE     # a sequence's tokens are counted in units of the cache's page
 
 
 @dataclass

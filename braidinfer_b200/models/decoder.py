@@ -78,7 +78,7 @@ class DecoderModel:
         if ctx.n_want == 0:
             ctx.drop_deferred()
             return None
-        if not getattr(self.final_norm, "accepts_deferred", False):
+        if not self.final_norm.accepts_deferred:
             ctx.resolve(h)
         x = self.final_norm.forward(h, ctx, row_index=ctx.want_rows, rows=ctx.n_want)
         return self.head.forward(x)

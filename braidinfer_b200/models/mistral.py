@@ -18,7 +18,7 @@ def build_mistral_spec(cfg: MistralConfig) -> ModelSpec:
     layers = []
     for i in range(cfg.num_hidden_layers):
         rope = PartSpec("rope", {"head_dim": cfg.head_dim, "theta": cfg.rope_theta,
-                                 "rope_dim": cfg.head_dim, "pairing": cfg.rope_pairing})
+                                 "rope_dim": cfg.rope_dim, "pairing": cfg.rope_pairing})
         mixer = PartSpec("gqa_attention", {
             "hidden_size": cfg.hidden_size, "num_heads": cfg.num_attention_heads,
             "num_kv_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim,
@@ -41,7 +41,8 @@ def build_mistral_spec(cfg: MistralConfig) -> ModelSpec:
                                         "name": "model.norm.weight"}),
         head=PartSpec("linear_head", {"vocab_size": cfg.vocab_size, "hidden_size": cfg.hidden_size,
                                       "name": "lm_head.weight", "tied": cfg.tie_word_embeddings}),
-        max_position=cfg.max_position_embeddings)
+        max_position=cfg.max_position_embeddings,
+        eos_token_ids=tuple(cfg.eos_token_id or ()), bos_token_id=cfg.bos_token_id)
 
 
 MISTRAL = register_architecture(Architecture(

@@ -10,8 +10,11 @@ from ..parts.spec import ModelSpec
 
 @dataclass(frozen=True)
 class Architecture:
-    """`config_from_dict` reads config.json's keys into a typed configuration;
-    `build_spec` turns that configuration into a description of parts."""
+    """`config_from_dict` reads config.json's keys into a typed configuration (any object:
+    only `build_spec` looks inside it); `build_spec` turns that configuration into a
+    `ModelSpec`, the description of parts that everything else works from: loader, cache,
+    step, generation, command line and replay read sizes, stop tokens and the longest
+    sequence from the `ModelSpec` alone."""
     name: str
     config_from_dict: Callable[[Mapping[str, Any]], Any]
     build_spec: Callable[[Any], ModelSpec]

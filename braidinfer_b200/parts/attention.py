@@ -63,7 +63,7 @@ class GQAAttention(Mixer):
         if cache is None:
             raise RuntimeError("gqa_attention needs a cache view")
         rt = self.rt
-        fused = getattr(self.pe, "accepts_deferred", False)
+        fused = self.pe.accepts_deferred
         qkv = self.qkv.forward(x, defer_to=ctx if fused else None)
         self.pe.encode_and_store(qkv, self.nqh, self.nkh, ctx, cache)
         rows = x.shape[0]

@@ -23,6 +23,10 @@ class Part:
     # step kernel by kernel.
     graph_safe = True
 
+    # A part that can finish a deferred sum inside its own kernel (see StepContext.deferred)
+    # says so here; every other part is handed tensors that are already complete.
+    accepts_deferred = False
+
     def __init__(self, params: dict, prefix: str, runtime) -> None:
         self.params = dict(params)
         self.prefix = prefix
@@ -37,16 +41,28 @@ class Part:
 
 
 class Norm(Part):
-    def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
-        """x: residual stream [rows, width] float32 -> normalised rows in the run dtype."""
+    def forward(self, x: torch.Tensor, ctx, row_index: Optional[torch.Tensor] = None,
+                rows: Optional[int] = None) -> torch.Tensor:
+        """x: residual stream [rows, width] float32 -> normalised rows in the run dtype.
+
+        As a layer's norm it is called with (x, ctx) and returns every row.  As the model's
+        final norm it is called with `row_index` (int32 on the device) and `rows`: it then
+        returns the `rows` rows x[row_index[i]] only, normalised, and leaves x as it is."""
         raise NotImplementedError
 
 
 class PositionEncoding(Part):
-    """Holds the constants of a position encoding; mixers ask it to encode
-    queries and keys in place given each token's position."""
+    """Holds the constants of a position encoding.  A mixer that keeps keys and values hands
+    it the step's stacked q, k, v rows; it encodes queries and keys and stores keys and
+    values, so that a cached key is encoded exactly once."""
 
-    def encode(self, q, k, positions, ctx) -> None:
+    def encode_and_store(self, qkv: torch.Tensor, nqh: int, nkh: int, ctx, cache) -> None:
+        """qkv: [rows, (nqh + 2 nkh) * head_dim] in the run dtype, query heads first, then key
+        heads, then value heads.  Encode the query and key heads in place using
+        `ctx.positions`, then write each row's keys and values into `cache` (a LayerCache)
+        at its position; `cache` None or read-only: no write.  Rows with ctx.token_seq < 0
+        are padding.  `ctx.take_deferred(qkv)` tells whether qkv still waits for a deferred
+        sum; only a part with `accepts_deferred` is ever handed such a tensor."""
         raise NotImplementedError
 
 
@@ -81,8 +97,26 @@ class FeedForward(Part):
         raise NotImplementedError
 
 
+class Embedding(Part):
+    def forward(self, token_ids: torch.Tensor, rows: int) -> torch.Tensor:
+        """token_ids [rows] int32 on the device -> the residual stream [rows, width], float32."""
+        raise NotImplementedError
+
+
+class Head(Part):
+    """The output head.  If it has an attribute `tied` that is true after `load`, the model
+    calls `tie(embedding.weight)` so that it can use the embedding table."""
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        """x [wanted rows, width] (the final norm's output) -> logits [wanted rows, vocab], float32."""
+        raise NotImplementedError
+
+
 class Block:
-    """The arrangement of a layer's parts."""
+    """The arrangement of a layer's parts.  `forward(h, ctx, cache, state) -> h` runs them on
+    the float32 residual stream; `cache` and `state` are the mixer's (see Mixer.forward).
+    h may arrive with a deferred sum pending (`ctx.deferred`): hand it only to a part with
+    `accepts_deferred`, else call `ctx.resolve(h)` first."""
 
     def __init__(self, mixer: Mixer, mixer_norm: Norm, feed_forward: Optional[FeedForward],
                  feed_forward_norm: Optional[Norm]) -> None:

@@ -15,12 +15,12 @@ class PreNormResidualBlock(Block):
     def forward(self, h, ctx, cache, state):
         # h may still wait for a deferred sum (see StepContext.deferred); a norm that
         # accepts that adds it up in its own kernel, any other part gets h completed first
-        if not getattr(self.mixer_norm, "accepts_deferred", False):
+        if not self.mixer_norm.accepts_deferred:
             ctx.resolve(h)
         x = self.mixer_norm.forward(h, ctx)
         h = self.mixer.forward(x, h, ctx, cache, state)
         if self.feed_forward is not None:
-            if not getattr(self.feed_forward_norm, "accepts_deferred", False):
+            if not self.feed_forward_norm.accepts_deferred:
                 ctx.resolve(h)
             x = self.feed_forward_norm.forward(h, ctx)
             h = self.feed_forward.forward(x, h, ctx)

@@ -11,13 +11,13 @@ from typing import Dict, Optional
 
 import torch
 
-from .base import EMBEDDINGS, HEADS, Part
+from .base import EMBEDDINGS, HEADS, Embedding, Head
 from .linear import Linear
 from .spec import TensorSpec
 
 
 @EMBEDDINGS.register("token_embedding")
-class TokenEmbedding(Part):
+class TokenEmbedding(Embedding):
     """params: vocab_size, hidden_size, name."""
 
     def __init__(self, params, prefix, runtime) -> None:
@@ -40,7 +40,7 @@ class TokenEmbedding(Part):
 
 
 @HEADS.register("linear_head")
-class LinearHead(Part):
+class LinearHead(Head):
     """params: vocab_size, hidden_size, name, tied (use the embedding table)."""
 
     def __init__(self, params, prefix, runtime) -> None:

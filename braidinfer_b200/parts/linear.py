@@ -23,6 +23,7 @@ def stream_k_pays(rows: int, w_rows: int, sms: Optional[int] = None) -> bool:
     Measured on the 7B layer sizes at 1 to 2,048 tokens: up to 768 tokens a last round of tiles less
     than 70 % full (80 % for up to 32 tokens, 60 % between 257 and 512) loses more than the adding-up
     costs; beyond that the partial sums themselves cost too much."""
+    from ..csrc.api import token_tile
     global _SMS
     if sms is None:
         if _SMS is None:
@@ -30,8 +31,7 @@ def stream_k_pays(rows: int, w_rows: int, sms: Optional[int] = None) -> bool:
         sms = _SMS
     if rows > 768:
         return False
-    block_n = 16 if rows <= 16 else 32 if rows <= 32 else 64 if rows <= 64 else 128 if rows <= 128 else 256
-    tiles = -(-w_rows // 128) * -(-rows // block_n)
+    tiles = -(-w_rows // 128) * -(-rows // token_tile(rows))
     fill = tiles / (-(-tiles // sms) * sms)
     return fill < (0.8 if rows <= 32 else 0.7 if rows <= 256 else 0.6 if rows <= 512 else 0.7)
 

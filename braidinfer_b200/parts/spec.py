@@ -47,7 +47,9 @@ class ModelSpec:
     schedule: Tuple[ScheduleEntry, ...]
     final_norm: PartSpec
     head: PartSpec
-    max_position: int = 0
+    max_position: int = 0                      # longest sequence the model is meant for (0: not stated)
+    eos_token_ids: Tuple[int, ...] = ()        # tokens that end a sequence unless the caller names others
+    bos_token_id: Optional[int] = None         # put before a text prompt by the command line
 
     def validate(self) -> None:
         for i, e in enumerate(self.schedule):

@@ -2,16 +2,23 @@
 
 What is asked for comes from the parts (`DecoderModel.tensor_specs`); what is there
 comes from the folder.  The two are compared before anything is copied, and every
-difference is reported in one error: missing tensors, unexpected tensors, wrong
-shapes (the reference reports them one at a time and panics on a size mismatch,
-crates/braidinfer-runtime/src/weights.rs:229-236, :301-307).
+difference that stops the load is reported in one error: missing tensors, wrong
+shapes, wrong kinds of element (the reference reports them one at a time and panics
+on a size mismatch, crates/braidinfer-runtime/src/weights.rs:229-236, :301-307).
+Tensors that the folder holds and no part asks for (older exports store
+``...rotary_emb.inv_freq``, for one) do not stop it: they are listed in one
+`UnexpectedTensorsWarning` and in the error, if there is one; `strict=True` makes
+them an error of their own.
 
 Element types: floating tensors stored in 16 bits are kept in bfloat16, a tensor
 stored in 32 bits stays float32, integer tables become int32.  A float32 run widens
-everything floating to float32 (exactly; bfloat16 -> float32 loses nothing).
+everything floating to float32 (exactly; bfloat16 -> float32 loses nothing).  A
+float16 tensor in a bfloat16 run is rounded to bfloat16 (8 mantissa bits for its
+11), which one `RoundedWeightsWarning` per load says.
 """
 from __future__ import annotations
 
+import warnings
 from typing import Dict, List, Mapping, Optional, Tuple
 
 import torch
@@ -44,6 +51,14 @@ class WeightsError(ValueError):
         super().__init__("\n".join(lines))
 
 
+class UnexpectedTensorsWarning(UserWarning):
+    """The folder holds tensors that no part of the model asks for; they were not loaded."""
+
+
+class RoundedWeightsWarning(UserWarning):
+    """Tensors stored in float16 were rounded to bfloat16 for a bfloat16 run."""
+
+
 def target_dtype(stored: torch.dtype, spec: TensorSpec, run_dtype: torch.dtype) -> torch.dtype:
     if spec.integer or not stored.is_floating_point:
         return torch.int32
@@ -55,8 +70,9 @@ def target_dtype(stored: torch.dtype, spec: TensorSpec, run_dtype: torch.dtype) 
 
 
 def load_tensors(folder: str, specs: Mapping[str, TensorSpec], run_dtype: torch.dtype,
-                 device) -> Dict[str, torch.Tensor]:
-    """Check the folder against `specs`, then copy every asked-for tensor to `device`."""
+                 device, strict: bool = False) -> Dict[str, torch.Tensor]:
+    """Check the folder against `specs`, then copy every asked-for tensor to `device`.
+    `strict`: tensors nobody asks for are an error instead of a warning."""
     found = open_model_folder(folder)
     missing = [n for n, s in specs.items() if n not in found and not s.optional]
     unexpected = [n for n in found if n not in specs]
@@ -70,8 +86,12 @@ def load_tensors(folder: str, specs: Mapping[str, TensorSpec], run_dtype: torch.
             wrong_shape.append((n, tuple(shape), tuple(s.shape)))
         if s.integer == dt.is_floating_point:
             wrong_dtype.append((n, str(dt)))
-    if missing or unexpected or wrong_shape or wrong_dtype:
+    if missing or wrong_shape or wrong_dtype or (strict and unexpected):
         raise WeightsError(folder, missing, unexpected, wrong_shape, wrong_dtype)
+    if unexpected:
+        warnings.warn(f"{folder}: {len(unexpected)} stored tensors are asked for by no part of the model and were "
+                      f"not loaded: " + ", ".join(unexpected), UnexpectedTensorsWarning, stacklevel=2)
+    rounded: List[str] = []
     out: Dict[str, torch.Tensor] = {}
     for n, s in specs.items():
         if n not in found:
@@ -83,5 +103,11 @@ def load_tensors(folder: str, specs: Mapping[str, TensorSpec], run_dtype: torch.
             out[n] = t.to(device, copy=True)
         else:
             # convert on the device: the host copy stays a view of the mapped file
+            if t.dtype == torch.float16 and want == torch.bfloat16:
+                rounded.append(n)
             out[n] = t.to(device).to(want)
+    if rounded:
+        warnings.warn(f"{folder}: {len(rounded)} tensors stored in float16 were rounded to bfloat16 "
+                      f"(first: {rounded[0]}); run with dtype float32 to keep every stored bit",
+                      RoundedWeightsWarning, stacklevel=2)
     return out

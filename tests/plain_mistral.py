@@ -10,14 +10,67 @@ tensors only, and no import from the package under test.
 Two things are this library's own and have no reference line: the sliding
 window mask (the reference never reads ``sliding_window``,
 crates/braidinfer-runtime/src/config.rs:416) and the half-split rotary
-pairing (the reference rotates adjacent pairs only).
+pairing (the reference rotates adjacent pairs only).  Both are pinned by
+hand-worked numbers in tests/test_plain.py.
+
+The configuration is read here too (`PlainConfig`), from config.json's keys
+with the defaults of crates/braidinfer-runtime/src/config.rs:227-268, so that a
+wrong default or a wrong per-layer window in the package shows as a difference
+instead of being wrong on both sides.
 """
 from __future__ import annotations
 
+import json
 import math
+import os
 from typing import Dict, List, Optional, Sequence
 
 import torch
+
+
+# --------------------------------------------------------------------------- configuration
+class PlainConfig:
+    """The sizes and constants the formulas below need, read from config.json's keys.
+
+    Defaults: kv heads = heads (config.rs:236-246), head_dim = hidden / heads (:247),
+    eps 1e-5 (:249-252), theta 10000 (:253-260), rotated part = head_dim *
+    partial_rotary_factor with factor 1 (:261-268).  ``sliding_window``,
+    ``layer_types`` and ``rope_pairing`` are this library's own keys.
+    """
+
+    def __init__(self, d: Dict) -> None:
+        self.num_hidden_layers = int(d["num_hidden_layers"])
+        self.hidden_size = int(d["hidden_size"])
+        self.num_attention_heads = int(d["num_attention_heads"])
+        kv = d.get("num_key_value_heads")
+        self.num_key_value_heads = int(kv) if kv is not None else self.num_attention_heads
+        hd = d.get("head_dim")
+        self.head_dim = int(hd) if hd is not None else self.hidden_size // self.num_attention_heads
+        self.intermediate_size = int(d["intermediate_size"])
+        self.vocab_size = int(d["vocab_size"])
+        eps = d.get("rms_norm_eps")
+        self.rms_norm_eps = float(eps) if eps is not None else 1e-5
+        theta = d.get("rope_theta")
+        self.rope_theta = float(theta) if theta is not None else 10000.0
+        factor = d.get("partial_rotary_factor")
+        self.rope_dim = int(self.head_dim * (float(factor) if factor is not None else 1.0))
+        self.rope_pairing = d.get("rope_pairing") or "half"
+        self.sliding_window = d.get("sliding_window")
+        self.layer_types = d.get("layer_types")
+
+    @classmethod
+    def from_folder(cls, folder: str) -> "PlainConfig":
+        with open(os.path.join(folder, "config.json")) as f:
+            return cls(json.load(f))
+
+    def layer_window(self, layer: int) -> Optional[int]:
+        """None: the layer sees every earlier key.  With ``layer_types``, only layers named
+        "sliding_attention" are windowed; without it every layer is, when a window is set."""
+        if self.sliding_window is None:
+            return None
+        if self.layer_types is not None and self.layer_types[layer] != "sliding_attention":
+            return None
+        return int(self.sliding_window)
 
 
 # --------------------------------------------------------------------------- parts
@@ -52,26 +105,30 @@ def inv_freq(rope_dim: int, theta: float, dtype=torch.float32) -> torch.Tensor:
     return (1.0 / (float(theta) ** (2.0 * p / rope_dim))).to(dtype)
 
 
-def rope(x: torch.Tensor, positions: torch.Tensor, theta: float, pairing: str = "half") -> torch.Tensor:
-    """Rotate each head of x[T, heads, hd] by angle pos*inv_freq[p].
+def rope(x: torch.Tensor, positions: torch.Tensor, theta: float, pairing: str = "half",
+         rope_dim: Optional[int] = None) -> torch.Tensor:
+    """Rotate the first `rope_dim` elements (default: all) of each head of x[T, heads, hd] by
+    angle pos*inv_freq[p]; elements from rope_dim on pass through.
 
-    (a, b) <- (a cos - b sin, a sin + b cos); kernels/megakernel_ops.hip:2019-2030,
+    (a, b) <- (a cos - b sin, a sin + b cos); kernels/megakernel_ops.hip:2019-2030
+    (its loop runs over rope_dim / 2 pairs and leaves the rest of the head alone),
     oracle crates/braidinfer-runtime/tests/mrope_test.rs:25-59, where the pair is
-    (x[2p], x[2p+1]) ("adjacent").  "half" pairs (x[p], x[p+hd/2]) instead.
+    (x[2p], x[2p+1]) ("adjacent").  "half" pairs (x[p], x[p+rd/2]) instead.
     """
     T, H, hd = x.shape
-    f = inv_freq(hd, theta, dtype=x.dtype)
-    ang = positions.to(x.dtype)[:, None] * f[None, :]          # [T, hd/2]
+    rd = hd if rope_dim is None else int(rope_dim)
+    f = inv_freq(rd, theta, dtype=x.dtype)
+    ang = positions.to(x.dtype)[:, None] * f[None, :]          # [T, rd/2]
     c, s = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
-    out = torch.empty_like(x)
+    out = x.clone()
     if pairing == "adjacent":
-        a, b = x[..., 0::2], x[..., 1::2]
-        out[..., 0::2] = a * c - b * s
-        out[..., 1::2] = a * s + b * c
+        a, b = x[..., 0:rd:2], x[..., 1:rd:2]
+        out[..., 0:rd:2] = a * c - b * s
+        out[..., 1:rd:2] = a * s + b * c
     elif pairing == "half":
-        a, b = x[..., : hd // 2], x[..., hd // 2:]
-        out[..., : hd // 2] = a * c - b * s
-        out[..., hd // 2:] = a * s + b * c
+        a, b = x[..., : rd // 2], x[..., rd // 2:rd]
+        out[..., : rd // 2] = a * c - b * s
+        out[..., rd // 2:rd] = a * s + b * c
     else:
         raise ValueError(pairing)
     return out
@@ -125,11 +182,12 @@ def attention_block(h, weights: Dict[str, torch.Tensor], prefix: str, cfg, layer
     nqh, nkh, hd = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
     n = rmsnorm(h, weights[prefix + "input_layernorm.weight"], cfg.rms_norm_eps)
     q = linear(n, weights[prefix + "self_attn.q_proj.weight"]).view(T, nqh, hd)
-    q = rope(q, positions, cfg.rope_theta, cfg.rope_pairing)
+    rd = getattr(cfg, "rope_dim", None)
+    q = rope(q, positions, cfg.rope_theta, cfg.rope_pairing, rd)
     if kv_override is None:
         k = linear(n, weights[prefix + "self_attn.k_proj.weight"]).view(T, nkh, hd)
         v = linear(n, weights[prefix + "self_attn.v_proj.weight"]).view(T, nkh, hd)
-        k = rope(k, positions, cfg.rope_theta, cfg.rope_pairing)
+        k = rope(k, positions, cfg.rope_theta, cfg.rope_pairing, rd)
     else:
         k, v = kv_override
     a = attention(q, k, v, cfg.layer_window(layer)).reshape(T, nqh * hd)

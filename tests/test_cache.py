@@ -99,6 +99,25 @@ def test_groups_by_request_and_shared_entries():
     assert s2 == s and int(m.state_view(1)[s2].sum()) == 0              # state is zero when a slot is taken
 
 
+def test_a_run_that_reads_another_runs_cache_must_fit_it():
+    """Heads and head size must be the owner's, and the reader must not look further back than
+    a windowed owner keeps pages for."""
+    full, win5, win9 = CacheRequest("full", 2, 8, None), CacheRequest("window", 2, 8, 5), CacheRequest("window", 2, 8, 9)
+    ok = [[(full, None, 0), (full, 0, 0)], [(full, None, 0), (win5, 0, 0)], [(win9, None, 0), (win5, 0, 0)],
+          [(win5, None, 0), (win5, 0, 0)], [(win5, None, 0), (None, 0, 0)]]
+    for plan in ok:
+        CacheManager(plan, max_tokens=128, max_slots=2, dtype=torch.float32, device="cpu")
+    bad = [([(win5, None, 0), (full, 0, 0)], "every earlier position"),
+           ([(win5, None, 0), (win9, 0, 0)], "window of 9"),
+           ([(full, None, 0), (CacheRequest("full", 4, 8, None), 0, 0)], "kv heads"),
+           ([(full, None, 0), (CacheRequest("full", 2, 16, None), 0, 0)], "kv heads"),
+           ([(None, None, 0), (full, 0, 0)], "keeps none")]
+    for plan, word in bad:
+        with pytest.raises(CacheError) as e:
+            CacheManager(plan, max_tokens=128, max_slots=2, dtype=torch.float32, device="cpu")
+        assert word in str(e.value), str(e.value)
+
+
 def test_random_traffic_loses_nothing():
     rng = random.Random(0)
     m = CacheManager(plan(window=100), max_tokens=PAGE_SIZE * 12, max_slots=5, dtype=torch.float32, device="cpu")

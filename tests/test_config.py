@@ -52,6 +52,65 @@ def test_refuses_bad_values(change, word):
     assert word in str(e.value)
 
 
+def test_alias_keys_of_the_reference_parser():
+    # crates/braidinfer-runtime/src/config.rs:208-277: the same value under its other spellings
+    d = {"architectures": ["MistralForCausalLM"], "n_embd": 48, "n_head": 4, "num_kv_heads": 2, "n_layer": 5,
+         "n_vocab": 77, "intermediate_size": 100, "norm_eps": 3e-4, "rope_freq_constant": 777.0,
+         "max_context_length": 321, "share_input_output_layers": True}
+    c = MistralConfig.from_dict(d)
+    assert (c.hidden_size, c.num_attention_heads, c.num_key_value_heads, c.num_hidden_layers, c.vocab_size) == \
+           (48, 4, 2, 5, 77)
+    assert c.rms_norm_eps == 3e-4 and c.rope_theta == 777.0 and c.max_position_embeddings == 321
+    assert c.tie_word_embeddings is True
+    d2 = dict(d)
+    del d2["norm_eps"]
+    d2["layer_norm_epsilon"] = 2e-3
+    assert MistralConfig.from_dict(d2).rms_norm_eps == 2e-3
+    # the primary spelling wins over an alias
+    assert MistralConfig.from_dict(dict(d, num_hidden_layers=2)).num_hidden_layers == 2
+
+
+def test_partial_rotary_factor_sets_the_rotated_part():
+    c = MistralConfig.from_dict(dict(TINY_B, partial_rotary_factor=0.5))
+    assert c.rope_dim == 16 and c.head_dim == 32
+    assert MistralConfig.from_dict(dict(TINY_B, rope_parameters={"partial_rotary_factor": 0.25})).rope_dim == 8
+    assert MistralConfig.from_dict(TINY_B).rope_dim == 32
+    arch = architecture_for(TINY_B)
+    spec = arch.build_spec(c)
+    assert spec.layers[1].mixer.params["position_encoding"].params["rope_dim"] == 16
+    assert MistralConfig.from_dict(c.to_dict()) == c
+    with pytest.raises(ConfigError) as e:
+        MistralConfig.from_dict(dict(TINY_B, partial_rotary_factor=0.3))      # 9 elements: odd
+    assert "partial_rotary_factor" in str(e.value)
+
+
+@pytest.mark.parametrize("change, words", [
+    ({"hidden_act": "gelu"}, ("hidden_act", "gelu")),
+    ({"hidden_act": "gelu_pytorch_tanh"}, ("hidden_act", "gelu_pytorch_tanh")),
+    ({"rope_scaling": {"type": "yarn", "factor": 4.0}}, ("rope_scaling", "yarn")),
+    ({"rope_scaling": {"rope_type": "linear", "factor": 2.0}}, ("rope_scaling", "linear")),
+    ({"rope_parameters": {"rope_type": "llama3", "rope_theta": 1e4}}, ("rope_type", "llama3")),
+    ({"attention_bias": True}, ("attention_bias", "True")),
+    ({"mlp_bias": True}, ("mlp_bias", "True")),
+    ({"partial_rotary_factor": 1.5}, ("partial_rotary_factor", "1.5")),
+])
+def test_refuses_what_it_does_not_compute(change, words):
+    """A key that asks for other arithmetic is an error that names key and value, never a silent run."""
+    with pytest.raises(ConfigError) as e:
+        MistralConfig.from_dict(dict(TINY_A, **change))
+    for w in words:
+        assert w in str(e.value)
+
+
+@pytest.mark.parametrize("change", [
+    {"hidden_act": "silu"}, {"rope_scaling": None}, {"rope_scaling": {"rope_type": "default"}},
+    {"rope_parameters": {"rope_type": "default", "rope_theta": 5e4}}, {"attention_bias": False}, {"mlp_bias": False},
+    {"attention_dropout": 0.0}, {"use_cache": True}, {"initializer_range": 0.02}, {"transformers_version": "4.40"},
+])
+def test_accepts_what_changes_no_arithmetic(change):
+    MistralConfig.from_dict(dict(TINY_A, **change))
+
+
 def test_layer_windows():
     c = MistralConfig.from_dict(TINY_C)
     assert [c.layer_window(i) for i in range(4)] == [None, 70, 70, None]

@@ -132,9 +132,10 @@ def attention_reference(q, k_all, v_all, pos, window):
     return out
 
 
-def attention_case(K, which, dtype, hd, nqh, nkh, seqs, window, n_splits=1, few=False, plant=None):
+def attention_case(K, which, dtype, hd, nqh, nkh, seqs, window, n_splits=1, few=False, plant=None, spoil=None):
     """seqs: (cache length before, new tokens).  `plant` = (seq, query offset, key position):
-    that key is made to dominate that query's scores, its value made distinctive."""
+    that key is made to dominate that query's scores, its value made distinctive.
+    `spoil` = (seq, block, value): that entry of the page table is overwritten before the launch."""
     lens = [b + n for b, n in seqs]
     cache, table = make_cache(len(seqs), lens, nkh, hd, dtype, shuffle_seed=3)
     kv_ref = []
@@ -164,6 +165,8 @@ def attention_case(K, which, dtype, hd, nqh, nkh, seqs, window, n_splits=1, few=
             page = int(table[i, p_ // 64])
             cache[page, 0, :, p_ % 64] = k[p_]
             cache[page, 1, :, p_ % 64] = v[p_]
+    if spoil is not None:
+        table[spoil[0], spoil[1]] = spoil[2]
     pos = [p_ for b, n in seqs for p_ in range(b, b + n)] + [0]
     seq = [i for i, (b, n) in enumerate(seqs) for _ in range(n)] + [-1]
     t = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
@@ -337,6 +340,42 @@ def test_a_far_key_among_hundreds_and_the_windows_edge(K, which):
         assert worst < 3e-2 and abs(float(out[650].float().mean()) - 5.0) < 0.1
 
 
+@pytest.mark.parametrize("which, dtype", [("simple", torch.float32), ("simple", torch.bfloat16), ("mma", torch.bfloat16),
+                                          ("mma_sliced", torch.bfloat16), ("mma_prompt", torch.bfloat16),
+                                          ("tc", torch.bfloat16)])
+@pytest.mark.parametrize("bad", [-1, 10 ** 6])
+def test_a_broken_page_table_raises_the_error_flag_and_is_never_followed(K, which, dtype, bad):
+    """A table entry of a visible position that is absent (-1) or beyond the cache: every attention
+    kernel checks the entry before it makes an address from it, reads page 0 instead and raises
+    the device error flag, which the host turns into a KernelError."""
+    hd, nqh, nkh = 64, 4, 2
+    K.check_device_errors()
+    if which in ("mma_prompt", "tc"):
+        seqs, kw = [(0, 200)], {}
+    else:
+        seqs, kw = [(199, 1)], (dict(n_splits=3, few=True) if which == "mma_sliced" else {})
+    name = which if which in ("simple", "tc") else "mma"
+    attention_case(K, name, dtype, hd, nqh, nkh, seqs, None, **kw)          # the sound table: no flag
+    K.check_device_errors()
+    try:
+        attention_case(K, name, dtype, hd, nqh, nkh, seqs, None, spoil=(0, 1, bad), **kw)
+    except KernelError:
+        return                                               # the tcgen05 case checks its flag itself
+    with pytest.raises(KernelError, match="page"):
+        K.check_device_errors()
+    K.check_device_errors()                                  # the flag is cleared once it was reported
+
+
+def test_plain_product_refuses_operands_of_two_element_types(K):
+    """The plain product reads both operands as one element type; a float32 x with a bfloat16 w
+    would read w past its end, so the call is refused on the host."""
+    x, w = rnd(4, 64), rnd(32, 64, dtype=torch.bfloat16, seed=1)
+    with pytest.raises(KernelError, match="one element type"):
+        K.gemm_simt(x, w, torch.empty(4, 32, device=DEV))
+    with pytest.raises(KernelError, match="do not fit"):
+        K.gemm_simt(x, rnd(32, 48), torch.empty(4, 32, device=DEV))
+
+
 @pytest.mark.parametrize("n, m, k", [(5, 70, 33), (64, 64, 64), (130, 200, 96), (1, 331, 120)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_plain_matrix_product(K, dtype, n, m, k):
@@ -391,14 +430,30 @@ def test_tensor_core_swiglu_epilogue(K, n, inter, k, sk):
     assert ((out.double() - want).abs() <= want.abs() / 100 + 1e-3).all()
 
 
-def test_stream_k_refuses_a_token_tile_its_workspace_is_not_sized_for(K):
-    from braidinfer_b200.csrc.api import KernelError
+def test_stream_k_refuses_a_workspace_that_is_too_small_and_takes_any_token_tile(K):
+    """The partial sums of a stream-k product must fit the workspace it is given: the entry point
+    checks that on the host for the very plan the kernel walks, whatever token tile is named."""
+    from braidinfer_b200.csrc.api import KernelError, F32, BF16
     x, w = rnd(300, 256, dtype=torch.bfloat16), rnd(512, 256, dtype=torch.bfloat16, seed=1)
+    want = x.double() @ w.double().t()
+    for tile in (128, 256):                                         # 3 token tiles, or 2
+        out = torch.full((300, 512), float("nan"), device=DEV, dtype=torch.bfloat16)
+        K.gemm_tc(x, w, out, block_n=tile, stream_k=True)
+        K.check_device_errors()
+        assert (out.double() - want).abs().max().item() < 2e-2
+    need = K.lib.braid_gemm_tc_workspace_bytes(300, 512, 256, 128)
+    assert need > K.lib.braid_gemm_tc_workspace_bytes(300, 512, 256, 256) > 0
+    assert K.lib.braid_gemm_tc_workspace_bytes(300, 512, 256, 48) == -1
+    ws = torch.empty(need // 4, dtype=torch.float32, device=DEV)
     out = torch.empty(300, 512, device=DEV, dtype=torch.bfloat16)
-    with pytest.raises(KernelError, match="picks its own token tile"):
-        K.gemm_tc(x, w, out, block_n=128, stream_k=True)          # refused on the host: nothing is launched
-    K.gemm_tc(x, w, out, block_n=256, stream_k=True)              # the tile it would pick itself is fine
+    args = lambda nbytes, tile: (x.data_ptr(), w.data_ptr(), out.data_ptr(), None, ws.data_ptr(), nbytes, BF16, 0,
+                                 300, 512, 256, 256, 256, 512, tile, 1, None, K._error_flag.data_ptr() + 4, K._stream())
+    assert K.lib.braid_gemm_tc(*args(need - 4, 128)) != 0            # refused on the host: nothing is launched
+    assert b"bytes of workspace" in K.lib.braid_last_error()
+    assert K.lib.braid_gemm_tc(*args(need, 48)) != 0 and b"token tile" in K.lib.braid_last_error()
+    assert K.lib.braid_gemm_tc(*args(need, 128)) == 0
     K.check_device_errors()
+    assert (out.double() - want).abs().max().item() < 2e-2
 
 
 def test_tensor_core_product_refuses_what_tma_cannot_address(K):

@@ -170,7 +170,7 @@ def test_block_and_schedule_against_the_plain_model(tmp_path):
     folder = make_folder(tmp_path, "A")
     cfg = config_of(folder)
     arch = architecture_for(TINY_A)
-    base = arch.build_spec(cfg)
+    base = arch.build_spec(arch.config_from_dict(TINY_A))
     sched = (ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(0), ScheduleEntry(1, cache_of=1))
     spec = dataclasses.replace(base, schedule=sched)
     toks = random_prompts(cfg.vocab_size, [75], seed=1)[0]

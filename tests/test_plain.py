@@ -9,7 +9,7 @@ import plain_mistral as P
 from braidinfer_b200.config import MistralConfig
 from braidinfer_b200.weights import draw_tensors, tensor_specs_of
 from braidinfer_b200.models import architecture_for
-from tiny import TINY_A, TINY_B
+from tiny import TINY_A, TINY_B, TINY_C
 
 
 def test_rmsnorm_by_hand():
@@ -68,9 +68,38 @@ def test_swiglu_by_hand():
 
 
 def weights_for(d, seed):
+    """Random tensors under the model's tensor names (data only) and the plain reading of the configuration."""
     arch = architecture_for(d)
-    cfg = arch.config_from_dict(d)
-    return cfg, {n: t.double() for n, t in draw_tensors(tensor_specs_of(arch.build_spec(cfg)), seed).items()}
+    drawn = draw_tensors(tensor_specs_of(arch.build_spec(arch.config_from_dict(d))), seed)
+    return P.PlainConfig(d), {n: t.double() for n, t in drawn.items()}
+
+
+@pytest.mark.parametrize("d", [TINY_A, TINY_B, TINY_C,
+                               {"hidden_size": 48, "num_attention_heads": 4, "intermediate_size": 100,
+                                "num_hidden_layers": 2, "vocab_size": 50, "partial_rotary_factor": 0.5}])
+def test_the_package_reads_config_json_as_the_plain_reader_does(d):
+    """Two readings of the same keys, written apart: every size, constant and default, and each
+    layer's window, must agree (a wrong default would otherwise be wrong on both sides of every test)."""
+    mine, theirs = P.PlainConfig(d), MistralConfig.from_dict(dict(d, architectures=["MistralForCausalLM"]))
+    for key in ("num_hidden_layers", "hidden_size", "num_attention_heads", "num_key_value_heads", "head_dim",
+                "intermediate_size", "vocab_size", "rms_norm_eps", "rope_theta", "rope_dim", "rope_pairing"):
+        assert getattr(mine, key) == getattr(theirs, key), key
+    for i in range(mine.num_hidden_layers):
+        assert mine.layer_window(i) == theirs.layer_window(i), i
+
+
+def test_partial_rotation_by_hand():
+    # head of 6, 4 of them rotated: pairs (0, 2) and (1, 3) for "half", (0, 1) and (2, 3) for "adjacent";
+    # frequencies come from the rotated size (4), elements 4 and 5 pass through
+    x = torch.tensor([[[1.0, 2.0, 3.0, 4.0, 5.0, 6.0]]], dtype=torch.float64)
+    pos = torch.tensor([3])
+    c0, s0, c1, s1 = math.cos(3.0), math.sin(3.0), math.cos(0.3), math.sin(0.3)
+    half = P.rope(x, pos, 100.0, "half", rope_dim=4)[0, 0]
+    assert torch.allclose(half, torch.tensor([1 * c0 - 3 * s0, 2 * c1 - 4 * s1, 1 * s0 + 3 * c0, 2 * s1 + 4 * c1, 5.0, 6.0],
+                                             dtype=torch.float64))
+    adj = P.rope(x, pos, 100.0, "adjacent", rope_dim=4)[0, 0]
+    assert torch.allclose(adj, torch.tensor([1 * c0 - 2 * s0, 1 * s0 + 2 * c0, 3 * c1 - 4 * s1, 3 * s1 + 4 * c1, 5.0, 6.0],
+                                            dtype=torch.float64))
 
 
 def test_later_tokens_do_not_change_earlier_logits_and_window_forgets():

@@ -7,7 +7,7 @@ import pytest
 import torch
 
 from braidinfer_b200.models import architecture_for
-from braidinfer_b200.weights import (WeightsError, load_tensors, open_model_folder, save_file, tensor_specs_of,
+from braidinfer_b200.weights import (RoundedWeightsWarning, UnexpectedTensorsWarning, WeightsError, load_tensors, open_model_folder, save_file, tensor_specs_of,
                                      write_random_model, SafetensorsError)
 from tiny import TINY_A, TINY_B, TINY_C, make_folder, read_weights
 
@@ -75,7 +75,7 @@ def test_one_error_lists_missing_unexpected_and_wrong_shapes(tmp_path):
     save_file(tensors, os.path.join(folder, "model.safetensors"))
     with pytest.raises(WeightsError) as e:
         load_tensors(folder, specs_for(TINY_B), torch.bfloat16, "cpu")
-    err = e.value
+    err = e.value                                      # what stops the load and what does not, in one message
     assert sorted(err.missing) == ["model.layers.1.mlp.up_proj.weight", "model.norm.weight"]
     assert err.unexpected == ["model.layers.9.extra.weight"]
     assert err.wrong_shape == [("model.layers.0.self_attn.q_proj.weight", (10, 96), (192, 96))]
@@ -83,6 +83,43 @@ def test_one_error_lists_missing_unexpected_and_wrong_shapes(tmp_path):
     for word in ("missing", "unexpected", "wrong shape", "model.norm.weight", "model.layers.9.extra.weight",
                  "[10, 96]", "[192, 96]"):
         assert word in text
+
+
+def test_a_tensor_nobody_asks_for_is_a_warning_that_lists_it(tmp_path):
+    # older exports of this family store a table of rotary frequencies beside every attention layer
+    folder = make_folder(tmp_path, "A")
+    tensors = {n: f.tensor(k).clone() for n, (f, k) in open_model_folder(folder).items()}
+    extra = ["model.layers.0.self_attn.rotary_emb.inv_freq", "model.layers.1.self_attn.rotary_emb.inv_freq"]
+    for n in extra:
+        tensors[n] = torch.ones(8, dtype=torch.float32)
+    save_file(tensors, os.path.join(folder, "model.safetensors"))
+    with pytest.warns(UnexpectedTensorsWarning) as rec:
+        got = load_tensors(folder, specs_for(TINY_A), torch.bfloat16, "cpu")
+    mine = [r for r in rec if r.category is UnexpectedTensorsWarning]
+    assert len(mine) == 1 and all(n in str(mine[0].message) for n in extra)
+    assert set(got) == set(specs_for(TINY_A))
+    with pytest.raises(WeightsError) as e:
+        load_tensors(folder, specs_for(TINY_A), torch.bfloat16, "cpu", strict=True)
+    assert sorted(e.value.unexpected) == extra and not e.value.missing
+
+
+def test_float16_weights_are_rounded_with_a_word_and_kept_whole_in_float32(tmp_path):
+    import warnings
+    folder = make_folder(tmp_path, "A")
+    tensors = {n: f.tensor(k).clone() for n, (f, k) in open_model_folder(folder).items()}
+    name = "model.layers.0.mlp.up_proj.weight"
+    half = (tensors[name].float() * 1.001).to(torch.float16)          # values with more than 8 mantissa bits
+    tensors[name] = half
+    save_file(tensors, os.path.join(folder, "model.safetensors"))
+    with pytest.warns(RoundedWeightsWarning) as rec:
+        got = load_tensors(folder, specs_for(TINY_A), torch.bfloat16, "cpu")
+    mine = [r for r in rec if r.category is RoundedWeightsWarning]
+    assert len(mine) == 1 and name in str(mine[0].message)
+    assert got[name].dtype == torch.bfloat16 and torch.equal(got[name], half.to(torch.bfloat16))
+    with warnings.catch_warnings():
+        warnings.simplefilter("error", RoundedWeightsWarning)
+        got32 = load_tensors(folder, specs_for(TINY_A), torch.float32, "cpu")
+    assert torch.equal(got32[name], half.float())
 
 
 def test_tied_head_needs_no_head_tensor(tmp_path):

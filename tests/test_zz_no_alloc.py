@@ -45,30 +45,38 @@ def test_no_alloc_entry_point_matches_the_ordinary_one_twice_in_a_row():
     lib = K.attn_mma_library(hd)
     fn = lib.braid_attn_mma_noalloc                      # the exported C symbol
     fn.restype = ctypes.c_int
-    fn.argtypes = [ctypes.c_void_p] * 8 + [ctypes.c_int] * 12 + [ctypes.c_float, ctypes.c_void_p]
+    fn.argtypes = [ctypes.c_void_p] * 8 + [ctypes.c_int] * 13 + [ctypes.c_float, ctypes.c_void_p, ctypes.c_void_p]
     lib.braid_attn_noalloc_capacity_floats.restype = ctypes.c_longlong
     cap = lib.braid_attn_noalloc_capacity_floats()
     assert cap == 2 * 1024 * 1024
     stream = torch.cuda.current_stream().cuda_stream
-    for seed, lens, splits in [(1, [2047, 100, 0, 63, 700], 8), (2, [300, 1500, 64], 5)]:
+    flag = torch.zeros(1, dtype=torch.int32, device=dev)         # the caller's own int for the page guard
+
+    def call(c, out, window, splits):
+        return fn(c["qkv"].data_ptr(), out.data_ptr(), c["cache"].data_ptr(), c["table"].data_ptr(),
+                  c["q_start"].data_ptr(), c["q_len"].data_ptr(), c["kv_before"].data_ptr(), c["token_seq"].data_ptr(),
+                  c["qkv"].stride(0), out.stride(0), c["rows"], c["rows"], 1, nqh, nkh, hd, c["table"].shape[1],
+                  c["cache"].shape[0], window, splits, 1, 1 / math.sqrt(hd), flag.data_ptr(), stream)
+
+    # sliced contexts twice in a row (the second call finds the first one's leftovers), then a
+    # window, then a single slice, which uses no scratch at all
+    for seed, lens, splits, window in [(1, [2047, 100, 0, 63, 700], 8, 0), (2, [300, 1500, 64], 5, 0),
+                                       (4, [900, 2000, 130, 5], 6, 500), (5, [400, 77, 1000], 1, 0),
+                                       (6, [400, 77, 1000], 1, 128)]:
         c = make_case(seed, hd, nqh, nkh, lens, dev)
         want = torch.zeros(c["rows"], nqh * hd, device=dev, dtype=torch.bfloat16)
         K.attn_mma(c["qkv"], want, c["cache"], c["table"], c["q_start"], c["q_len"], c["kv_before"], c["token_seq"],
-                   c["rows"], 1, nqh, nkh, hd, None, 1 / math.sqrt(hd), n_splits=splits, few_tokens=True)
+                   c["rows"], 1, nqh, nkh, hd, window or None, 1 / math.sqrt(hd), n_splits=splits, few_tokens=True)
         got = torch.full_like(want, 9.0)
-        rc = fn(c["qkv"].data_ptr(), got.data_ptr(), c["cache"].data_ptr(), c["table"].data_ptr(),
-                c["q_start"].data_ptr(), c["q_len"].data_ptr(), c["kv_before"].data_ptr(), c["token_seq"].data_ptr(),
-                c["qkv"].stride(0), got.stride(0), c["rows"], c["rows"], 1, nqh, nkh, hd, c["table"].shape[1], 0,
-                splits, 1, 1 / math.sqrt(hd), stream)
+        rc = call(c, got, window, splits)
         assert rc == 0, lib.braid_last_error().decode()
         torch.cuda.synchronize()
-        # same kernels, same slices, same order of sums: within the bfloat16 tolerance of the kernel tests
-        assert (got.float() - want.float()).abs().max().item() < 2e-2
+        # the same kernels over the same slices in the same order of sums: bit for bit
+        assert torch.equal(got, want), (seed, (got.float() - want.float()).abs().max().item())
+        assert flag.item() == 0
+    K.check_device_errors()
     # a step beyond the array's size is refused with a clear message, not truncated
     c = make_case(3, hd, nqh, nkh, [10] * 64, dev)
     out = torch.empty(64, nqh * hd, device=dev, dtype=torch.bfloat16)
-    rc = fn(c["qkv"].data_ptr(), out.data_ptr(), c["cache"].data_ptr(), c["table"].data_ptr(),
-            c["q_start"].data_ptr(), c["q_len"].data_ptr(), c["kv_before"].data_ptr(), c["token_seq"].data_ptr(),
-            c["qkv"].stride(0), out.stride(0), 64, 64, 1, nqh, nkh, hd, c["table"].shape[1], 0, 64, 1,
-            1 / math.sqrt(hd), stream)
+    rc = call(c, out, 0, 64)
     assert rc != 0 and b"holds" in lib.braid_last_error()

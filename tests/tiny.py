@@ -76,9 +76,10 @@ def read_weights(folder: str) -> Dict[str, torch.Tensor]:
 
 
 def config_of(folder: str):
-    from braidinfer_b200.config import MistralConfig
-    with open(os.path.join(folder, "config.json")) as f:
-        return MistralConfig.from_dict(json.load(f))
+    """The folder's configuration as the plain implementation reads it (its own few lines,
+    nothing of the package under test)."""
+    from plain_mistral import PlainConfig
+    return PlainConfig.from_folder(folder)
 
 
 def random_prompts(vocab: int, lengths: List[int], seed: int) -> List[List[int]]:
