@@ -131,7 +131,11 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     print(f"stop tokens: {stop}", file=sys.stderr)
     prompts = [codec.encode(p) for p in prompts_text]
     start = time.perf_counter()
-    outs = m.generate(prompts, params, stop, max_tokens)
+    try:
+        outs = m.generate(prompts, params, stop, max_tokens)
+    except ValueError as e:                 # an empty prompt, or a request the cache has no room for
+        print(f"generate: {e}", file=sys.stderr)
+        return 2
     elapsed = time.perf_counter() - start
     n_tokens = 0
     for o in outs:

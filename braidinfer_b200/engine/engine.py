@@ -183,13 +183,19 @@ class Engine:
         before = [self.cache.length(s) for s in slots]
         n_new = [len(t) for t in tokens]
         tables = self.cache.begin_step(slots, n_new)
-        graphable = self.use_graphs and all(n == 1 for n in n_new)
-        if device_tokens is not None and not all(n == 1 for n in n_new):
+        one_each = all(n == 1 for n in n_new)
+        graphable = self.use_graphs and one_each
+        if device_tokens is not None and not one_each:
             raise ValueError("device_tokens needs a step of one token a sequence")
-        ctx = self.packer.pack(slots, tokens, before, want_l, tables,
-                               bucket_tables=graphable or device_tokens is not None,
+        ctx = self.packer.pack(slots, tokens, before, want_l, tables, bucket_tables=one_each,
                                token_source_rows=device_tokens[1] if device_tokens is not None else None)
         ctx.kernels = self.kernels
+        if one_each and ctx.page_tables:
+            # A one-token step shapes its launches (how the context is sliced) by the bound that
+            # the widened page tables give, not by the lengths themselves: a CUDA graph can
+            # depend on the step's shape only, and a step launched kernel by kernel takes the
+            # same shape so that it gives the same bits.
+            ctx.max_kv_len = max(t.shape[1] for t in ctx.page_tables) * PAGE_SIZE
         if device_tokens is not None:
             self.kernels.gather_i32(device_tokens[0], self.packer.token_source_view, ctx.token_ids)
         try:
@@ -210,15 +216,13 @@ class Engine:
     def _graph_step(self, ctx: StepContext) -> Optional[torch.Tensor]:
         """Run a one-token-per-sequence step through a CUDA graph.  The graph holds kernel
         launches only; the step's tables were copied to fixed device addresses before it.
-        Launch shapes may depend on the step's shape alone, so the context length that
-        shapes the attention launch is the bound the page tables' width gives.  The
-        graph writes its logits into its own memory; the caller gets a copy."""
+        Launch shapes depend on the step's shape alone (see `step`).  The graph writes its
+        logits into its own memory; the caller gets a copy."""
         generation = (self.packer.generation, self.kernels.workspace_generation)
         if generation != self._graph_generation:       # a buffer that graphs point into has moved
             self._graphs.clear()
             self._graph_seen.clear()
             self._graph_generation = generation
-        ctx.max_kv_len = max(t.shape[1] for t in ctx.page_tables) * PAGE_SIZE if ctx.page_tables else ctx.max_kv_len
         key = (ctx.rows, ctx.n_seqs, ctx.n_want, tuple(tuple(t.shape) for t in ctx.page_tables))
         entry = self._graphs.get(key)
         if entry is None:

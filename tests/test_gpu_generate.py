@@ -64,7 +64,6 @@ def test_temperature_sampling_is_seeded_and_matches_the_plain_chain(tmp_path):
     b = m.generate(prompts, sp, stop_tokens=(), max_new_tokens=6)
     c = m.generate(prompts, SamplingParams(temperature=0.8, seed=2), stop_tokens=(), max_new_tokens=6)
     assert [o.tokens for o in a] == [o.tokens for o in b] != [o.tokens for o in c]
-    alone = m.generate([prompts[1]], sp, stop_tokens=(), max_new_tokens=6)      # same draws outside the batch?
     for i, (p, o) in enumerate(zip(prompts, a)):
         toks = list(p)
         for step, t in enumerate(o.tokens):
@@ -74,8 +73,6 @@ def test_temperature_sampling_is_seeded_and_matches_the_plain_chain(tmp_path):
                 near = {P.sample(orc.logits(toks)[-1], temperature=0.8, top_k=50, u=u + d) for d in (-1e-4, 1e-4)}
                 assert t in near
             toks.append(t)
-    # a sequence's draws depend on its own index in the request list, not on the batch around it
-    assert alone[0].tokens != [] and len(alone[0].tokens) == 6
 
 
 def test_stop_tokens_and_batches_one_after_another(tmp_path):
@@ -124,3 +121,90 @@ def test_command_line(tmp_path):
     assert p.returncode == 0, p.stderr
     p = subprocess.run([sys.executable, os.path.join(root, "bin", "generate")], env=env, capture_output=True, text=True)
     assert p.returncode == 2 and "MODEL" in p.stderr
+
+
+def run_cli(args, **env):
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    e = dict(os.environ, RAW="1")
+    e.update({k: str(v) for k, v in env.items()})
+    return subprocess.run([sys.executable, os.path.join(root, "bin", "generate")] + list(args), env=e,
+                          capture_output=True, text=True, timeout=600)
+
+
+def test_command_line_sampling_options_are_seeded(tmp_path):
+    folder = make_folder(tmp_path, "A")
+    opts = dict(MODEL=folder, MAX_TOKENS=8, DTYPE="float32", TEMPERATURE="0.9", TOP_K="40", TOP_P="0.95", MIN_P="0.01")
+    a = run_cli(["7, 200, 31"], SEED=5, **opts)
+    b = run_cli(["7, 200, 31"], SEED=5, **opts)
+    c = run_cli(["7, 200, 31"], SEED=6, **opts)
+    assert a.returncode == b.returncode == c.returncode == 0, a.stderr + c.stderr
+    assert a.stdout == b.stdout != c.stdout and len(a.stdout.split()) <= 8
+    # the same options through the Python entry point choose the same tokens
+    m = lib.load(folder, dtype="float32", max_batch=1, verbose=False)
+    sp = SamplingParams(temperature=0.9, top_k=40, top_p=0.95, min_p=0.01, seed=5)
+    assert [int(x) for x in a.stdout.split()] == m.generate([7, 200, 31], sp, None, 8)
+    # a repetition penalty takes the loop that reads every token back; greedy with a penalty differs from plain greedy
+    g = run_cli(["7, 7, 7, 7"], MODEL=folder, MAX_TOKENS=6, DTYPE="float32")
+    r = run_cli(["7, 7, 7, 7"], MODEL=folder, MAX_TOKENS=6, DTYPE="float32", TEMPERATURE="0.0001", TOP_K="1",
+                REPETITION_PENALTY="50", SEED=1)
+    assert g.returncode == 0 and r.returncode == 0, g.stderr + r.stderr
+    rt = [int(x) for x in r.stdout.split()]
+    assert len(set(rt)) == len(rt)                            # a penalty of 50 never lets a token come twice
+    bad = run_cli(["7"], MODEL=folder, TEMPERATURE="warm")
+    assert bad.returncode != 0 and "TEMPERATURE" in bad.stderr
+
+
+def test_command_line_batch_file_and_max_seq_len(tmp_path):
+    folder = make_folder(tmp_path, "A")
+    orc = Oracle(folder)
+    lines = ["7, 200, 31", "5", "9, 9, 100, 3, 77, 12"]
+    bf = tmp_path / "prompts.txt"
+    bf.write_text("\n".join(lines) + "\n\n")
+    p = run_cli([], MODEL=folder, MAX_TOKENS=5, DTYPE="float32", BATCH_FILE=str(bf), MAX_SEQ_LEN=64)
+    assert p.returncode == 0, p.stderr
+    got = [[int(x) for x in l.split()] for l in p.stdout.strip("\n").split("\n")]
+    assert len(got) == 3
+    for line, g in zip(lines, got):
+        toks, want = [int(x) for x in line.replace(",", " ").split()], []
+        for _ in range(5):
+            t = P.argmax_lowest(orc.logits(toks)[-1])
+            if t == 2:
+                break
+            want.append(t)
+            toks.append(t)
+        assert g == want
+    assert "max_seq_len: 64" in p.stderr                      # the cache holds 64 positions a sequence
+    # a request that cannot fit the cache MAX_SEQ_LEN asked for is refused in words
+    p = run_cli([", ".join(["3"] * 60)], MODEL=folder, MAX_TOKENS=10, DTYPE="float32", MAX_SEQ_LEN=64)
+    assert p.returncode == 2 and "the cache holds 64" in p.stderr
+    p = run_cli([", ".join(["3"] * 60)], MODEL=folder, MAX_TOKENS=10, DTYPE="float32", MAX_SEQ_LEN=128)
+    assert p.returncode == 0 and "max_seq_len: 128" in p.stderr
+
+
+def test_command_line_with_a_tokenizer_prepends_bos(tmp_path):
+    pytest.importorskip("tokenizers")
+    import json
+    from tokenizers import Tokenizer
+    from tokenizers.models import WordLevel
+    from tokenizers.pre_tokenizers import Whitespace
+    folder = make_folder(tmp_path, "A")                      # bos_token_id 1, eos_token_id 2
+    vocab = {f"w{i}": i for i in range(256)}
+    t = Tokenizer(WordLevel(vocab, unk_token="w0"))
+    t.pre_tokenizer = Whitespace()
+    t.save(os.path.join(folder, "tokenizer.json"))
+    orc = Oracle(folder)
+    p = run_cli(["w7 w200 w31"], MODEL=folder, MAX_TOKENS=4, DTYPE="float32")
+    assert p.returncode == 0, p.stderr
+    toks, want = [1, 7, 200, 31], []                          # BOS first
+    for _ in range(4):
+        tok = P.argmax_lowest(orc.logits(toks)[-1])
+        if tok == 2:
+            break
+        want.append(tok)
+        toks.append(tok)
+    assert p.stdout.split() == [f"w{i}" for i in want]
+    with open(os.path.join(folder, "tokenizer_config.json"), "w") as f:
+        json.dump({"add_bos_token": False}, f)
+    q = run_cli(["w7 w200 w31"], MODEL=folder, MAX_TOKENS=4, DTYPE="float32")
+    first = P.argmax_lowest(orc.logits([7, 200, 31])[-1])
+    assert q.returncode == 0 and (q.stdout.split()[:1] == [f"w{first}"] or first == 2)

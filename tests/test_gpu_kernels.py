@@ -440,7 +440,7 @@ def test_stream_k_refuses_a_workspace_that_is_too_small_and_takes_any_token_tile
         out = torch.full((300, 512), float("nan"), device=DEV, dtype=torch.bfloat16)
         K.gemm_tc(x, w, out, block_n=tile, stream_k=True)
         K.check_device_errors()
-        assert (out.double() - want).abs().max().item() < 2e-2
+        assert (out.double() - want).abs().max().item() < want.abs().max().item() / 128      # bfloat16 output
     need = K.lib.braid_gemm_tc_workspace_bytes(300, 512, 256, 128)
     assert need > K.lib.braid_gemm_tc_workspace_bytes(300, 512, 256, 256) > 0
     assert K.lib.braid_gemm_tc_workspace_bytes(300, 512, 256, 48) == -1
@@ -453,7 +453,7 @@ def test_stream_k_refuses_a_workspace_that_is_too_small_and_takes_any_token_tile
     assert K.lib.braid_gemm_tc(*args(need, 48)) != 0 and b"token tile" in K.lib.braid_last_error()
     assert K.lib.braid_gemm_tc(*args(need, 128)) == 0
     K.check_device_errors()
-    assert (out.double() - want).abs().max().item() < 2e-2
+    assert (out.double() - want).abs().max().item() < want.abs().max().item() / 128
 
 
 def test_tensor_core_product_refuses_what_tma_cannot_address(K):
