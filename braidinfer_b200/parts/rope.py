@@ -28,7 +28,7 @@ class RotaryEncoding(PositionEncoding):
         self.pairing = params.get("pairing", "half")
         if self.pairing not in ("half", "adjacent"):
             raise ValueError(f"rope pairing must be 'half' or 'adjacent', got {self.pairing!r}")
-        if self.rope_dim % 2 or not (0 < self.rope_dim <= self.head_dim):
+        if self.rope_dim % 2 or not (0 <= self.rope_dim <= self.head_dim):
             raise ValueError(f"rope_dim={self.rope_dim} must be even and within head_dim={self.head_dim}")
         p = torch.arange(self.rope_dim // 2, dtype=torch.float64)
         inv = 1.0 / (self.theta ** (2.0 * p / self.rope_dim))
@@ -54,3 +54,13 @@ class RotaryEncoding(PositionEncoding):
             cache.page_table if writable else None, cache.storage if writable else None,
             nqh, nkh, self.head_dim, self.rope_dim, self.pairing == "adjacent",
             cache.page_size if cache is not None else 1)
+
+
+@POSITION_ENCODINGS.register("none")
+class NoPositionEncoding(RotaryEncoding):
+    """No position information in queries and keys: they pass through as the projections made
+    them, and keys and values are stored.  (The rotation of zero elements: the same kernels.)
+    params: head_dim."""
+
+    def __init__(self, params, prefix, runtime) -> None:
+        super().__init__({"head_dim": params["head_dim"], "theta": 1.0, "rope_dim": 0}, prefix, runtime)

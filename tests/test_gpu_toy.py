@@ -263,3 +263,166 @@ def test_toy_routed_feed_forward_and_toy_position_encoding():
     finally:
         FEED_FORWARDS.unregister("toy_top_one_experts")
         POSITION_ENCODINGS.unregister("toy_learned_offsets")
+
+
+# ---------------------------------------------------------------------------------------------
+# The parts nobody had swapped yet, each written to the interface that braidinfer_b200/parts/base.py
+# documents and registered from here: a norm with a mean and a bias (also as the model's final norm,
+# where it is handed the wanted rows only), a block that runs mixer and feed-forward side by side
+# from one norm, an embedding with a scale, a head that caps its logits, and attention without any
+# position encoding (the built-in "none").
+from braidinfer_b200.parts import BLOCKS, EMBEDDINGS, HEADS, NORMS, Block, Embedding, Head, Norm
+
+
+class ToyLayerNorm(Norm):
+    def __init__(self, params, prefix, runtime):
+        super().__init__(params, prefix, runtime)
+        self.width, self.eps = int(params["width"]), float(params["eps"])
+        self.wn, self.bn = prefix + params["name"] + ".weight", prefix + params["name"] + ".bias"
+
+    def tensor_specs(self):
+        return {self.wn: TensorSpec((self.width,), init="one_plus_normal"), self.bn: TensorSpec((self.width,))}
+
+    def load(self, tensors):
+        self.w, self.b = tensors[self.wn].float(), tensors[self.bn].float()
+
+    def forward(self, x, ctx, row_index=None, rows=None):
+        if row_index is not None:                       # the final norm: the wanted rows only
+            x = x[row_index[:rows].long()]
+        mu = x.mean(-1, keepdim=True)
+        var = ((x - mu) ** 2).mean(-1, keepdim=True)
+        return ((x - mu) * torch.rsqrt(var + self.eps) * self.w + self.b).to(self.rt.act_dtype)
+
+
+class SideBySideBlock(Block):
+    """h + mixer(norm(h)) + feed_forward(norm(h)): one norm feeds both."""
+
+    def forward(self, h, ctx, cache, state):
+        ctx.resolve(h)                                  # the norm here knows nothing of deferred sums
+        x = self.mixer_norm.forward(h, ctx)
+        h = self.mixer.forward(x, h, ctx, cache, state)
+        ctx.resolve(h)
+        return self.feed_forward.forward(x, h, ctx)
+
+
+class ScaledEmbedding(Embedding):
+    def __init__(self, params, prefix, runtime):
+        super().__init__(params, prefix, runtime)
+        self.vocab, self.width, self.scale = int(params["vocab_size"]), int(params["hidden_size"]), float(params["scale"])
+        self.name = prefix + "model.embed_tokens.weight"
+
+    def tensor_specs(self):
+        return {self.name: TensorSpec((self.vocab, self.width))}
+
+    def load(self, tensors):
+        self.weight = tensors[self.name]
+
+    def forward(self, token_ids, rows):
+        return self.weight[token_ids[:rows].long()].float() * self.scale
+
+
+class CappedHead(Head):
+    def __init__(self, params, prefix, runtime):
+        super().__init__(params, prefix, runtime)
+        self.vocab, self.width, self.cap = int(params["vocab_size"]), int(params["hidden_size"]), float(params["cap"])
+        self.name = prefix + "lm_head.weight"
+
+    def tensor_specs(self):
+        return {self.name: TensorSpec((self.vocab, self.width))}
+
+    def load(self, tensors):
+        self.w = tensors[self.name].float()
+
+    def forward(self, x):
+        return self.cap * torch.tanh(x.float() @ self.w.t() / self.cap)
+
+
+def plain_toy_model_3(weights, cfg, tokens, scale, cap, eps):
+    import plain_mistral as P
+    w = {k: v.double() for k, v in weights.items()}
+    T = len(tokens)
+    nqh, nkh, hd = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+
+    def layer_norm(x, name):
+        mu = x.mean(-1, keepdim=True)
+        var = ((x - mu) ** 2).mean(-1, keepdim=True)
+        return (x - mu) * torch.rsqrt(var + eps) * w[name + ".weight"] + w[name + ".bias"]
+
+    h = P.embedding(w["model.embed_tokens.weight"], tokens, torch.float64) * scale
+    for layer in range(cfg.num_hidden_layers):
+        pre = f"model.layers.{layer}."
+        n = layer_norm(h, pre + "toy_norm")
+        q = P.linear(n, w[pre + "self_attn.q_proj.weight"]).view(T, nqh, hd)          # no position encoding at all
+        k = P.linear(n, w[pre + "self_attn.k_proj.weight"]).view(T, nkh, hd)
+        v = P.linear(n, w[pre + "self_attn.v_proj.weight"]).view(T, nkh, hd)
+        a = P.linear(P.attention(q, k, v, cfg.layer_window(layer)).reshape(T, nqh * hd), w[pre + "self_attn.o_proj.weight"])
+        f = P.swiglu(n, w[pre + "mlp.gate_proj.weight"], w[pre + "mlp.up_proj.weight"], w[pre + "mlp.down_proj.weight"])
+        h = h + a + f
+    h = layer_norm(h, "toy_final")
+    return cap * torch.tanh(P.linear(h, w["lm_head.weight"]) / cap)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_norm_block_embedding_head_and_no_position_encoding(dtype):
+    from braidinfer_b200.engine import Engine
+    from braidinfer_b200.models import architecture_for
+    from tiny import TINY_B, random_prompts
+    NORMS.register("toy_layer_norm", ToyLayerNorm)
+    BLOCKS.register("toy_side_by_side", SideBySideBlock)
+    EMBEDDINGS.register("toy_scaled_embedding", ScaledEmbedding)
+    HEADS.register("toy_capped_head", CappedHead)
+    try:
+        arch = architecture_for(TINY_B)
+        cfg = arch.config_from_dict(TINY_B)
+        base = arch.build_spec(cfg)
+        eps, scale, cap = 1e-4, 3.0, 0.4
+        layers = []
+        for ls in base.layers:
+            mp = dict(ls.mixer.params)
+            mp["position_encoding"] = PartSpec("none", {"head_dim": cfg.head_dim})
+            layers.append(dataclasses.replace(
+                ls, block="toy_side_by_side", mixer=PartSpec("gqa_attention", mp),
+                mixer_norm=PartSpec("toy_layer_norm", {"width": cfg.hidden_size, "eps": eps, "name": "toy_norm"}),
+                feed_forward_norm=PartSpec("toy_layer_norm", {"width": cfg.hidden_size, "eps": eps, "name": "toy_norm"})))
+        spec = dataclasses.replace(
+            base, layers=tuple(layers),
+            embedding=PartSpec("toy_scaled_embedding", {"vocab_size": cfg.vocab_size, "hidden_size": cfg.hidden_size,
+                                                        "scale": scale}),
+            final_norm=PartSpec("toy_layer_norm", {"width": cfg.hidden_size, "eps": eps, "name": "toy_final"}),
+            head=PartSpec("toy_capped_head", {"vocab_size": cfg.vocab_size, "hidden_size": cfg.hidden_size, "cap": cap}))
+        eng = Engine.from_spec(spec, 13, dtype=dtype, max_tokens=512, max_slots=3, verbose=False,
+                               scale={"toy_norm.bias": 10.0, "toy_final.bias": 10.0, "lm_head.weight": 10.0})
+        names = set(eng.model.tensor_specs())
+        assert {"model.layers.2.toy_norm.bias", "toy_final.weight", "lm_head.weight"} <= names
+        assert not any("layernorm" in n or n == "model.norm.weight" for n in names)
+        assert eng.use_graphs                     # every part here can be replayed by a graph
+        w64 = {n_: t.double() for n_, t in eng.drawn.items()}
+        prompts = random_prompts(cfg.vocab_size, [70, 9, 21], seed=3)
+        want = [plain_toy_model_3(w64, cfg, p, scale, cap, eps) for p in prompts]
+        assert max(w_.abs().max().item() for w_ in want) > 0.9 * cap          # the cap does bite
+        tol = 2e-5 if dtype == "float32" else 1.5e-2
+        slots = [eng.open() for _ in prompts]
+        cut = [64, 3, 12]
+        got = eng.step([(s, p[:c]) for s, p, c in zip(slots, prompts, cut)], want=[[0, 63], [2], list(range(12))])
+        assert (got[0].double().cpu() - want[0][0]).abs().max() < tol         # wanted rows, gathered by the final norm
+        assert (got[1].double().cpu() - want[0][63]).abs().max() < tol
+        assert (got[2].double().cpu() - want[1][2]).abs().max() < tol
+        assert (got[3:].double().cpu() - want[2][:12]).abs().max() < tol
+        for t in range(6):                                                    # the later ones through a CUDA graph
+            out = eng.step([(slots[i], [prompts[i][cut[i] + t]]) for i in range(3)], want="last")
+            for i in range(3):
+                assert (out[i].double().cpu() - want[i][cut[i] + t]).abs().max() < tol
+        assert eng.graph_replays >= 4
+        eng.check()
+        # generation through the entry point works for a model that no configuration describes
+        import braidinfer_b200 as lib
+        m = lib.Model(eng, max_batch=3)
+        for s in slots:
+            eng.close(s)
+        outs = m.generate([p[:5] for p in prompts], None, None, 4)
+        assert [len(o.tokens) for o in outs] == [4, 4, 4] and m.config is None
+    finally:
+        NORMS.unregister("toy_layer_norm")
+        BLOCKS.unregister("toy_side_by_side")
+        EMBEDDINGS.unregister("toy_scaled_embedding")
+        HEADS.unregister("toy_capped_head")
