@@ -3,8 +3,8 @@
 //
 //   braid_streamk_reduce_norm     h = h + sum (the residual sum, float32, written back),
 //                                 then RMSNorm of the new h: out = h * rsqrt(mean(h^2) + eps) * w.
-//                                 A row is shared by a cluster of up to 8 CTAs that exchange
-//                                 their sums of squares through distributed shared memory.
+//                                 One CTA of up to 1024 threads a row, so that the row's sum of
+//                                 squares needs one block-wide sum and nothing between CTAs.
 //   braid_streamk_reduce_rope_kv  qkv = sum, rotary encoding of the query and key heads,
 //                                 keys and values into the paged cache (what elementwise.cu's
 //                                 rope_kv_kernel does after a plain product).
@@ -12,90 +12,99 @@
 // Formulas are those of the unfused kernels (elementwise.cu cites the reference lines).
 #include "common.cuh"
 #include "streamk.cuh"
-#include <cooperative_groups.h>
-namespace cg = cooperative_groups;
 
-#define RN_THREADS 128
+#define RN_MAX_THREADS 1024
 
-// grid (cluster_size, rows); cluster dims (cluster_size, 1, 1): the CTAs of a cluster share row blockIdx.y.
+// One CTA per output row, one thread per group of four columns (a thread takes further groups
+// in turn when the row is wider than four times the block).  The first group of a thread
+// stays in registers between the two passes, so a row of up to 4096 columns is read once.
 template <typename TW, typename TO>
-__global__ void __launch_bounds__(RN_THREADS)
+__global__ void __launch_bounds__(RN_MAX_THREADS)
 streamk_reduce_norm_kernel(StreamK k, float* h, const TW* __restrict__ w, TO* __restrict__ out,
                            const int* __restrict__ row_index, int width, float eps) {
     pdl_trigger();
     __shared__ float red[32];
-    __shared__ float my_ss;
-    cg::cluster_group cluster = cg::this_cluster();
-    const int rank = (int)cluster.block_rank(), csize = (int)cluster.num_blocks();
-    const int r = blockIdx.y;
-    const int src = row_index ? row_index[r] : r;
+    const int r = blockIdx.x;
+    const int src = row_index ? row_index[r] : r;       // the step's tables are on the device before its first kernel
     const bool write_back = (row_index == nullptr);      // gathered rows may repeat: leave h alone
     const int groups = (width + 3) / 4;                  // groups of four columns
-    const int per = (groups + csize - 1) / csize;
-    const int g0 = rank * per, g1 = min(groups, g0 + per);
+    const bool vec = (width & 3) == 0;                   // rows of h start on 16 bytes
     TO* o = out + (size_t)r * width;
     float ss = 0.f;
-    // where this thread's first group of partial sums lies is worked out before the wait
-    const int g_first = g0 + threadIdx.x;
+    // where this thread's first group of partial sums lies, and the norm's weights of that group
+    // (no kernel writes them), are worked out before the wait
+    const int g_first = threadIdx.x;
     StreamKSpan sp_first = {};
-    float w_first[4] = {0.f, 0.f, 0.f, 0.f};              // the norm's weights of that group: no kernel writes them
-    if (src >= 0 && g_first < g1) {
+    float w_first[4] = {0.f, 0.f, 0.f, 0.f};
+    if (src >= 0 && g_first < groups) {
         sp_first = streamk_span(k, src, g_first * 4);
 #pragma unroll
         for (int e = 0; e < 4; ++e)
             if (g_first * 4 + e < width) w_first[e] = to_f32(w[g_first * 4 + e]);
     }
     pdl_wait();
-    float v_first[4] = {0.f, 0.f, 0.f, 0.f};              // the new h of this thread's first group stays in registers
+    float v_first[4] = {0.f, 0.f, 0.f, 0.f};              // the new h of this thread's first group
     if (src >= 0) {
         float* hr = h + (size_t)src * width;
-        for (int g = g0 + threadIdx.x; g < g1; g += RN_THREADS) {
+        for (int g = g_first; g < groups; g += blockDim.x) {
             const int c = g * 4;
-            const float4 s4 = streamk_sum4(k, g == g_first ? sp_first : streamk_span(k, src, c), src, c);
-            const float s[4] = {s4.x, s4.y, s4.z, s4.w};
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                if (c + e >= width) break;
-                const float v = hr[c + e] + s[e];
-                if (write_back) hr[c + e] = v;
-                if (g == g_first) v_first[e] = v;
-                ss = fmaf(v, v, ss);
-            }
-        }
-    }
-    ss = block_sum(ss, red);
-    if (threadIdx.x == 0) my_ss = ss;
-    cluster.sync();
-    float total = 0.f;
-    for (int b = 0; b < csize; ++b) total += *cluster.map_shared_rank(&my_ss, b);
-    if (src < 0) {
-        for (int g = g0 + threadIdx.x; g < g1; g += RN_THREADS)
-            for (int e = 0; e < 4 && g * 4 + e < width; ++e) o[g * 4 + e] = from_f32<TO>(0.f);
-    } else {
-        const float scale = rsqrtf(total / (float)width + eps);
-        const float* hr = h + (size_t)src * width;
-        for (int g = g0 + threadIdx.x; g < g1; g += RN_THREADS) {
-            const int c = g * 4;
-            if (g == g_first) {
+            // the row's old values are asked for before the partial sums are added up: one trip for all
+            float old[4] = {0.f, 0.f, 0.f, 0.f};
+            if (vec) {
+                const float4 o4 = *reinterpret_cast<const float4*>(hr + c);
+                old[0] = o4.x; old[1] = o4.y; old[2] = o4.z; old[3] = o4.w;
+            } else {
 #pragma unroll
                 for (int e = 0; e < 4; ++e)
-                    if (c + e < width) o[c + e] = from_f32<TO>(v_first[e] * scale * w_first[e]);
-                continue;
+                    if (c + e < width) old[e] = hr[c + e];
             }
-            float s[4] = {0.f, 0.f, 0.f, 0.f};
-            if (!write_back) {
-                const float4 s4 = streamk_sum4(k, streamk_span(k, src, c), src, c);
-                s[0] = s4.x; s[1] = s4.y; s[2] = s4.z; s[3] = s4.w;
-            }
+            const float4 s4 = streamk_sum4(k, g == g_first ? sp_first : streamk_span(k, src, c), src, c);
+            const float s[4] = {s4.x, s4.y, s4.z, s4.w};
+            float v[4];
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                if (c + e >= width) break;
-                const float v = hr[c + e] + s[e];             // written back above by this very thread, or recomputed
-                o[c + e] = from_f32<TO>(v * scale * to_f32(w[c + e]));
+                v[e] = (c + e < width) ? old[e] + s[e] : 0.f;
+                ss = fmaf(v[e], v[e], ss);
             }
+            if (write_back) {
+                if (vec) *reinterpret_cast<float4*>(hr + c) = make_float4(v[0], v[1], v[2], v[3]);
+                else {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e)
+                        if (c + e < width) hr[c + e] = v[e];
+                }
+            }
+            if (g == g_first) { v_first[0] = v[0]; v_first[1] = v[1]; v_first[2] = v[2]; v_first[3] = v[3]; }
         }
     }
-    cluster.sync();                                       // nobody leaves while its sum may still be read
+    const float total = block_sum(ss, red);
+    if (src < 0) {
+        for (int g = g_first; g < groups; g += blockDim.x)
+            for (int e = 0; e < 4 && g * 4 + e < width; ++e) o[g * 4 + e] = from_f32<TO>(0.f);
+        return;
+    }
+    const float scale = rsqrtf(total / (float)width + eps);
+    const float* hr = h + (size_t)src * width;
+    for (int g = g_first; g < groups; g += blockDim.x) {
+        const int c = g * 4;
+        if (g == g_first) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+                if (c + e < width) o[c + e] = from_f32<TO>(v_first[e] * scale * w_first[e]);
+            continue;
+        }
+        float s[4] = {0.f, 0.f, 0.f, 0.f};
+        if (!write_back) {
+            const float4 s4 = streamk_sum4(k, streamk_span(k, src, c), src, c);
+            s[0] = s4.x; s[1] = s4.y; s[2] = s4.z; s[3] = s4.w;
+        }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            if (c + e >= width) break;
+            const float v = hr[c + e] + s[e];             // written back above by this very thread, or recomputed
+            o[c + e] = from_f32<TO>(v * scale * to_f32(w[c + e]));
+        }
+    }
 }
 
 extern "C" int braid_streamk_reduce_norm(const float* partial, const int* plan, int n_rows, float* h, const void* w,
@@ -104,20 +113,11 @@ extern "C" int braid_streamk_reduce_norm(const float* partial, const int* plan, 
     if (rows_out <= 0) return BRAID_OK;
     if (width <= 0) BRAID_REFUSE("reduce_norm: width=%d must be positive", width);
     StreamK k{partial, plan[0], plan[1], plan[2], plan[3], n_rows, plan[4], (long long)plan[5]};
-    int csize = 1;
-    while (csize < 8 && width / (csize * 2) >= 256) csize *= 2;      // at least 256 columns a CTA
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(csize, rows_out);
-    cfg.blockDim = dim3(RN_THREADS);
-    cfg.stream = (cudaStream_t)stream;
-    cudaLaunchAttribute attr[2];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = csize; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
-    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[1].val.programmaticStreamSerializationAllowed = braid_pdl_enabled();
-    cfg.attrs = attr;
-    cfg.numAttrs = 2;
-#define RN_LAUNCH(TW, TO) cudaLaunchKernelEx(&cfg, streamk_reduce_norm_kernel<TW, TO>, k, h, (const TW*)w, (TO*)out, row_index, width, eps)
+    const int groups = (width + 3) / 4;
+    int threads = ((groups + 31) / 32) * 32;
+    if (threads > RN_MAX_THREADS) threads = RN_MAX_THREADS;
+    cudaStream_t s = (cudaStream_t)stream;
+#define RN_LAUNCH(TW, TO) braid_launch(streamk_reduce_norm_kernel<TW, TO>, dim3(rows_out), dim3(threads), 0, s, k, h, (const TW*)w, (TO*)out, row_index, width, eps)
     if (w_dtype == BRAID_F32 && out_dtype == BRAID_F32) RN_LAUNCH(float, float);
     else if (w_dtype == BRAID_F32 && out_dtype == BRAID_BF16) RN_LAUNCH(float, __nv_bfloat16);
     else if (w_dtype == BRAID_BF16 && out_dtype == BRAID_F32) RN_LAUNCH(__nv_bfloat16, float);
@@ -190,8 +190,10 @@ __global__ void streamk_reduce_rope_kv_kernel(ReduceRopeArgs a) {
                 s1 = streamk_span(a.k, row, col0 + i1);
             }
             // the product is rounded to bfloat16 before it is rotated, as after a plain product
-            const float x0 = __bfloat162float(__float2bfloat16_rn(streamk_sum(a.k, s0, row, col0 + i0)));
-            const float x1 = __bfloat162float(__float2bfloat16_rn(streamk_sum(a.k, s1, row, col0 + i1)));
+            float f0, f1;
+            streamk_sum_pair(a.k, s0, s1, row, col0 + i0, col0 + i1, f0, f1);
+            const float x0 = __bfloat162float(__float2bfloat16_rn(f0));
+            const float x1 = __bfloat162float(__float2bfloat16_rn(f1));
             const __nv_bfloat16 y0 = __float2bfloat16_rn(x0 * cs - x1 * sn);
             const __nv_bfloat16 y1 = __float2bfloat16_rn(x0 * sn + x1 * cs);
             dst_row[i0] = y0;
@@ -208,11 +210,20 @@ __global__ void streamk_reduce_rope_kv_kernel(ReduceRopeArgs a) {
         StreamKSpan sp0 = {};
         if (i_first < a.hd) sp0 = streamk_span(a.k, row, col0 + i_first);
         pdl_wait();
-        for (int i = threadIdx.x; i < a.hd; i += blockDim.x) {
+        for (int i = threadIdx.x; i < a.hd; i += 2 * blockDim.x) {
             const StreamKSpan s0 = (i == i_first) ? sp0 : streamk_span(a.k, row, col0 + i);
-            const __nv_bfloat16 y = __float2bfloat16_rn(streamk_sum(a.k, s0, row, col0 + i));
-            dst_row[i] = y;
-            if (dst) dst[i] = y;
+            const int i2 = i + blockDim.x;                  // a thread's elements go two at a time
+            if (i2 < a.hd) {
+                float f0, f1;
+                streamk_sum_pair(a.k, s0, streamk_span(a.k, row, col0 + i2), row, col0 + i, col0 + i2, f0, f1);
+                const __nv_bfloat16 y0 = __float2bfloat16_rn(f0), y1 = __float2bfloat16_rn(f1);
+                dst_row[i] = y0; dst_row[i2] = y1;
+                if (dst) { dst[i] = y0; dst[i2] = y1; }
+            } else {
+                const __nv_bfloat16 y = __float2bfloat16_rn(streamk_sum(a.k, s0, row, col0 + i));
+                dst_row[i] = y;
+                if (dst) dst[i] = y;
+            }
         }
     }
 }
