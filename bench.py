@@ -6,8 +6,8 @@ random weights and random token ids.
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
 
 Prints ONE JSON line.  A step is one decode step of the whole batch.  `value` times K
-steps with CUDA events on the launching stream (engine step + token choice, tokens fed
-back without a host read); `e2e` is the same number through the Python entry point
+steps with CUDA events on the launching stream (engine step + token choice; the chosen
+tokens stay on the device and feed the next step); `e2e` is the same number through the Python entry point
 (`Model.generate`): host token ids in, host token ids out, every step copying its
 inputs from pinned host memory and reading its chosen tokens back.  Weights (14.5 GB)
 exceed the 126 MB L2, so no L2 flush is needed between steps.
@@ -127,15 +127,15 @@ def device_timed_decode(engine, sampler_kernels, prompts, steps, warmup):
     for _ in range(warmup):
         logits = engine.step([(s, [t]) for s, t in zip(slots, toks)], want="last")
         sampler_kernels.argmax(logits, out)
-    toks = out.tolist()
     ctx0 = engine.length(slots[0])
-    entries = [(s, [t]) for s, t in zip(slots, toks)]
+    entries = [(s, [0]) for s in slots]                  # placeholders: each step takes its tokens from `out`
+    rows = list(range(len(slots)))
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     launches0 = engine.kernels.launches
     e0.record()
     for _ in range(steps):
-        logits = engine.step(entries, want="last")
+        logits = engine.step(entries, want="last", device_tokens=(out, rows))
         sampler_kernels.argmax(logits, out)
     e1.record()
     torch.cuda.synchronize()
@@ -144,6 +144,44 @@ def device_timed_decode(engine, sampler_kernels, prompts, steps, warmup):
     for s in slots:
         engine.close(s)
     return e0.elapsed_time(e1) / 1e3, ctx0, launches
+
+
+def sm_clock_reader():
+    """A function that reads the SM clock in MHz (a query only), or None without NVML."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        h = pynvml.nvmlDeviceGetHandleByIndex(0)
+        return lambda: int(pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM))
+    except Exception:
+        return None
+
+
+def steps_after_a_prefill(engine, prompts, n=40):
+    """The first `n` decode steps right after a batch's prefill, one by one: the time of each
+    (host clock around a synchronised step) and the SM clock read after it.  Shows how long the
+    clocks take to come back after the prefill's power draw, which is the difference between the
+    device-timed number (taken after warm-up steps) and the one through the entry point."""
+    import torch
+    read_mhz = sm_clock_reader()
+    slots = [engine.open() for _ in prompts]
+    logits = engine.step(list(zip(slots, prompts)), want="last")
+    out = torch.empty(len(prompts), dtype=torch.int32, device=engine.device)
+    engine.kernels.argmax(logits, out)
+    torch.cuda.synchronize()
+    ms, mhz = [], []
+    entries, rows = [(s, [0]) for s in slots], list(range(len(slots)))
+    for _ in range(n):
+        t0 = time.perf_counter()
+        logits = engine.step(entries, want="last", device_tokens=(out, rows))
+        engine.kernels.argmax(logits, out)
+        torch.cuda.synchronize()
+        ms.append(round((time.perf_counter() - t0) * 1e3, 3))
+        mhz.append(read_mhz() if read_mhz else None)
+    for s in slots:
+        engine.close(s)
+    prod = [round(a * b / 1e3, 2) for a, b in zip(ms, mhz)] if read_mhz else None      # ms x GHz: clock-free work
+    return {"step_ms": ms, "sm_mhz": mhz, "ms_times_ghz": prod}
 
 
 def run_ours(args):
@@ -217,12 +255,19 @@ def run_ours(args):
                "h2d_bytes_per_step": engine.packer.h2d_bytes_last, "d2h_bytes_per_step": B * 4,
                "prefill_tokens_per_s": st.prompt_tokens / st.prefill_seconds if st.prefill_seconds > 0 else 0.0}
 
-    # ---- other batch sizes
+    # ---- other batch sizes, temperature sampling, and the steps right after a prefill
     points = {}
+    after_prefill = None
     for b in (() if args.quick else (1, 64)):
         k = min(steps, 64)
         s2, _, _ = device_timed_decode(engine, engine.kernels, prompts_for(b), k, warmup)
         points[f"decode_b{b}"] = b * k / s2
+    if not args.quick:
+        model.generate(prompts_for(B), SamplingParams(temperature=0.8, seed=1), stop_tokens=(),
+                       max_new_tokens=min(steps, gen_len) + 1)
+        st = model.last_stats
+        points["decode_b8_temperature"] = st.decode_tokens / st.decode_seconds if st.decode_seconds > 0 else 0.0
+        after_prefill = steps_after_a_prefill(engine, prompts_for(B))
 
     line = {
         "metric": "decode tokens/s at batch 8, Mistral-7B-v0.3 sizes, bf16 (also batch 1, 64; prefill of 2,048 tokens)",
@@ -238,55 +283,102 @@ def run_ours(args):
                    "cache_tokens": cache_seqs * ctx_len, "parallelism": "single GPU",
                    "l2": "inputs (14.5 GB of weights) exceed L2; no flush"},
         "e2e": e2e, "gpu_launches": launches, "clocks": clocks, "prefill": prefill, "roofline": roofline,
-        "points": points, "setup_seconds": time.time() - t0,
+        "points": points, "after_prefill": after_prefill, "setup_seconds": time.time() - t0,
     }
     print(json.dumps(line))
     return 0
 
 
 def run_other_size(args):
-    """The other sizes the measurements are quoted on, through the Python entry point:
+    """The other sizes the measurements are quoted on:
     `mistral_7b_v01`: sliding window 4096, context 8192, batch 8, prompts of 6,000-8,000 tokens;
     `mistral_nemo_12b`: head_dim 128 with hidden 5120, vocabulary 131072, context 16384, batch 16, prompts of
-    512-8,192 tokens.  Prints one JSON line with prompt and decode tokens a second."""
+    512-8,192 tokens.  One JSON line with the same keys as the default run: `value` is decode tokens a second
+    timed on the device, `prefill` the batch's prompt step, `roofline` the bytes a decode step has to read
+    (every weight once, and the keys and values that each sequence's window still sees) over its time,
+    `e2e` the same batch through `Model.generate`."""
     import random
     import torch
     from braidinfer_b200.api import Model
     from braidinfer_b200.config import preset
     from braidinfer_b200.engine import Engine
     from braidinfer_b200.sampling import SamplingParams
+    pk = peaks()
     rng = random.Random(0)
     g = torch.Generator().manual_seed(0)
     if args.preset == "mistral_7b_v01":
         B, ctx, lens = 8, 8192, [rng.randint(6000, 8000) for _ in range(8)]
     else:
         B, ctx, lens = 16, 16384, [rng.randint(512, 8192) for _ in range(16)]
-    cfg = preset(args.preset)
+    cfg_dict = preset(args.preset)
+    full_layers = cfg_dict["num_hidden_layers"]
     if args.layers:
-        cfg["num_hidden_layers"] = args.layers
-    engine = Engine.from_random(cfg, seed=0, dtype="bfloat16", on_device=True, max_tokens=B * ctx, max_slots=B)
+        cfg_dict["num_hidden_layers"] = args.layers
+    n_layers = cfg_dict["num_hidden_layers"]
+    t0 = time.time()
+    engine = Engine.from_random(cfg_dict, seed=0, dtype="bfloat16", on_device=True, max_tokens=B * ctx, max_slots=B)
+    cfg = engine.config
     model = Model(engine, max_batch=B)
-    prompts = [torch.randint(0, cfg["vocab_size"], (n,), generator=g).tolist() for n in lens]
-    new = min(args.steps, 256)
-    for _ in range(2):                       # the second run has every kernel and graph warm
-        model.generate(prompts, SamplingParams.greedy(), stop_tokens=(), max_new_tokens=new)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in lens]
+    steps, warmup = min(args.steps, 128), max(3, args.warmup)
+    _, weight_bytes, kv_per_tok = model_numbers(cfg, n_layers)
+
+    # the batch's prompts in one step (unequal lengths), timed on the device after one warm-up run
+    pre_ms = None
+    for i in range(2):
+        slots = [engine.open() for _ in prompts]
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        engine.step(list(zip(slots, prompts)), want="last")
+        e1.record()
+        torch.cuda.synchronize()
+        pre_ms = e0.elapsed_time(e1)
+        for sl in slots:
+            engine.close(sl)
+    window = cfg.sliding_window
+    lin = 2 * ((cfg.num_attention_heads + 2 * cfg.num_key_value_heads) * cfg.head_dim * cfg.hidden_size
+               + cfg.hidden_size * cfg.num_attention_heads * cfg.head_dim + 3 * cfg.intermediate_size * cfg.hidden_size)
+    att = sum(sum(min(p + 1, window) if window else p + 1 for p in range(n)) for n in lens) * 4 * cfg.num_attention_heads * cfg.head_dim
+    pre_flops = n_layers * (lin * sum(lens) + att) + 2 * cfg.vocab_size * cfg.hidden_size * B
+    prefill = {"value": sum(lens) / (pre_ms / 1e3), "tokens": sum(lens), "ms": pre_ms, "unit": "tokens/s",
+               "frac": pre_flops / (pre_ms / 1e3) / (pk["bf16_tflops"] * 1e12),
+               "peak": f"{pk['bf16_tflops']} TFLOP/s bf16, {pk['source']}"}
+
+    with ClockSampler() as cs:
+        secs, _, launches = device_timed_decode(engine, engine.kernels, prompts, steps, warmup)
+    clocks = cs.summary()
+    seen = [min(n + warmup + steps / 2, window) if window else n + warmup + steps / 2 for n in lens]
+    step_bytes = weight_bytes + sum(seen) * kv_per_tok + B * cfg.hidden_size * 2
+    achieved = step_bytes / (secs / steps) / 1e9
+    outs = model.generate(prompts, SamplingParams.greedy(), stop_tokens=(), max_new_tokens=steps + 1)
     st = model.last_stats
     engine.check()
     print(json.dumps({
-        "metric": f"generation through the Python entry point, {args.preset} sizes, bf16", "impl": "ours",
-        "prefill_tokens_per_s": st.prompt_tokens / st.prefill_seconds,
-        "decode_tokens_per_s": st.decode_tokens / st.decode_seconds,
-        "config": {"model": args.preset, "layers": cfg["num_hidden_layers"], "batch": B, "context": ctx,
-                   "prompt_tokens": sum(lens), "new_tokens_each": new, "sliding_window": cfg.get("sliding_window"),
-                   "weights_gb": engine.weight_bytes / 1e9, "cache_gb": engine.cache.nbytes() / 1e9},
-        "data": "synthetic: random weights, uniform random token ids"}))
+        "metric": f"decode tokens/s at batch {B}, {args.preset} sizes, bf16 (unequal prompts; also their prefill)",
+        "value": B * steps / secs, "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
+        "ms_per_step": secs / steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic: random weights N(0, 0.02) seed 0, uniform random token ids", "impl": "ours",
+        "config": {"model": args.preset, "layers": n_layers, "layers_of_full_model": full_layers,
+                   "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
+                   "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
+                   "sliding_window": window, "global_batch": B, "seq_len": ctx, "prompt_tokens": sum(lens),
+                   "prompt_len_min": min(lens), "prompt_len_max": max(lens), "parallelism": "single GPU",
+                   "weights_gb": round(engine.weight_bytes / 1e9, 2), "cache_gb": round(engine.cache.nbytes() / 1e9, 2),
+                   "l2": "inputs (weights) exceed L2; no flush"},
+        "e2e": {"value": st.decode_tokens / st.decode_seconds if st.decode_seconds > 0 else 0.0, "unit": "tokens/s",
+                "h2d_bytes_per_step": engine.packer.h2d_bytes_last, "d2h_bytes_per_step": B * 4,
+                "prefill_tokens_per_s": st.prompt_tokens / st.prefill_seconds if st.prefill_seconds > 0 else 0.0},
+        "gpu_launches": launches, "clocks": clocks, "prefill": prefill,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": achieved / pk["hbm_gbs"], "peak_source": pk["source"], "bytes_per_step": step_bytes},
+        "setup_seconds": time.time() - t0}))
     return 0
 
 
 def run_sweep(args):
     """Decode at batch 1, 8, 64 over contexts of 512 to 32,768 tokens and prefill of 512 to 16,384
     tokens, on the default sizes: one JSON line with time, achieved bandwidth or FLOP rate, and the
-    fraction of the peak, for every point.  For profiles/; not the contract's line."""
+    fraction of the peak, for every point.  Not the contract's line."""
     import torch
     from braidinfer_b200.config import preset
     from braidinfer_b200.engine import Engine
@@ -340,7 +432,7 @@ def run_timeline(args):
     profiler (device activity only), printed as one JSON line: for the kernels of one layer in the
     middle of the step, the time from the end of the kernel before to the end of this one (kernels
     overlap their predecessors' tails through programmatic dependent launch, so durations would
-    count time twice).  For profiles/; not the contract's line."""
+    count time twice).  Not the contract's line."""
     import torch
     from torch.profiler import ProfilerActivity, profile
     from braidinfer_b200.config import preset

@@ -73,12 +73,14 @@ class Model:
         """Give a sequence's slot and pages back."""
         self.engine.close(slot)
 
-    def replay(self, lines, out_dir: str) -> int:
+    def replay(self, lines, out_dir: str, dump_activations: Optional[str] = None) -> int:
         """Feed given token ids step by step and write logits, as `bin/trace_run` does
-        (`lines`: JSON step objects, as text lines or dicts)."""
+        (`lines`: JSON step objects, as text lines or dicts; `dump_activations`: a folder for
+        the residual stream after every run of a layer, as `--dump-activations` writes it)."""
         import json
         from .engine.trace import replay
-        return replay(self.engine, (l if isinstance(l, str) else json.dumps(l) for l in lines), out_dir)
+        return replay(self.engine, (l if isinstance(l, str) else json.dumps(l) for l in lines), out_dir,
+                      dump_dir=dump_activations)
 
     # -- the step API of the reference, for one sequence at a time
     def prefill(self, tokens: Sequence[int]):

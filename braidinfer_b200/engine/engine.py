@@ -148,7 +148,7 @@ class Engine:
     # ------------------------------------------------------------------ the step
     def step(self, entries: Sequence[Tuple[int, Sequence[int]]],
              want: Union[str, Sequence[Sequence[int]], None] = "last",
-             device_tokens: Optional[Tuple[torch.Tensor, Sequence[int]]] = None) -> Optional[torch.Tensor]:
+             device_tokens: Optional[Tuple[torch.Tensor, Sequence[int]]] = None, tap=None) -> Optional[torch.Tensor]:
         """Run `entries` = [(slot, tokens), ...] as one batch.
 
         `want` says whose logits come back: "last" (each sequence's last token), "all",
@@ -159,7 +159,11 @@ class Engine:
         `device_tokens` = (int32 tensor on the device, rows): in a step of one token a
         sequence, take entry i's token from tensor[rows[i]] instead of from `entries`
         (whose token is then a placeholder), so that a sampler's output can feed the next
-        step without a round trip through the host."""
+        step without a round trip through the host.
+
+        `tap(i, h)`: a function that is shown the residual stream [tokens of the step, width]
+        (float32, on the device; padding rows cut off) after the embedding (i = 0) and after
+        each schedule entry (i = 1 ...).  A step with a tap is launched kernel by kernel."""
         if not entries:
             return None
         slots = [int(s) for s, _ in entries]
@@ -184,7 +188,7 @@ class Engine:
         n_new = [len(t) for t in tokens]
         tables = self.cache.begin_step(slots, n_new)
         one_each = all(n == 1 for n in n_new)
-        graphable = self.use_graphs and one_each
+        graphable = self.use_graphs and one_each and tap is None
         if device_tokens is not None and not one_each:
             raise ValueError("device_tokens needs a step of one token a sequence")
         ctx = self.packer.pack(slots, tokens, before, want_l, tables, bucket_tables=one_each,
@@ -201,6 +205,8 @@ class Engine:
         try:
             if graphable:
                 logits = self._graph_step(ctx)
+            elif tap is not None:
+                logits = self.model.forward(ctx, self.cache, tap=lambda i, h: tap(i, h[:ctx.n_tokens]))
             else:
                 logits = self.model.forward(ctx, self.cache)
         except BaseException:

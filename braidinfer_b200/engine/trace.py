@@ -14,6 +14,14 @@ finished after this step; their slots and pages go back to the cache.
 Output: for a step in which something is wanted, <out>/<step>.f32 holds the logits at
 the wanted places, in the order of the entries and of `want`, as little-endian
 float32 [wanted, vocab].  After every step `done <step>` is printed and flushed.
+
+`--dump-activations DIR` also writes, for every step, DIR/<step>.act.f32: the residual
+stream of the step's tokens (in the order of the entries) after the embedding and after
+every run of a layer, float32 [1 + runs, tokens, width].  A wrong layer is then found by
+comparing these files with a plain implementation's instead of bisecting by hand; the
+reference has an in-kernel dump for the same purpose (kernels/dump.h:24-60, sink
+crates/braidinfer-runtime/src/tracer.rs:266-306).  Steps that dump are launched kernel
+by kernel and complete every deferred sum at once.
 """
 from __future__ import annotations
 
@@ -26,9 +34,11 @@ from typing import Dict, Optional, Sequence
 import numpy as np
 
 
-def replay(engine, lines, out_dir: str, say=None) -> int:
+def replay(engine, lines, out_dir: str, say=None, dump_dir: Optional[str] = None) -> int:
     """Drive `engine` with the steps in `lines` (an iterable of JSON strings)."""
     os.makedirs(out_dir, exist_ok=True)
+    if dump_dir:
+        os.makedirs(dump_dir, exist_ok=True)
     slots: Dict[str, int] = {}
     n = 0
     for line in lines:
@@ -46,7 +56,17 @@ def replay(engine, lines, out_dir: str, say=None) -> int:
             batch.append((slots[rid], [int(t) for t in e["tokens"]]))
             want.append([int(w) for w in e.get("want", [])])
         if batch:
-            logits = engine.step(batch, want=want)
+            taps = []
+            if dump_dir:
+                logits = engine.step(batch, want=want, tap=lambda i, h: taps.append(h.clone()))
+            else:
+                logits = engine.step(batch, want=want)
+            if dump_dir:
+                import torch
+                acts = torch.stack(taps).to("cpu").numpy().astype("<f4", copy=False)
+                tmp = os.path.join(dump_dir, f".{step}.act.f32.tmp")
+                acts.tofile(tmp)
+                os.replace(tmp, os.path.join(dump_dir, f"{step}.act.f32"))
             if logits is not None:
                 arr = logits.detach().to("cpu").numpy().astype("<f4", copy=False)
                 engine.check()
@@ -71,6 +91,9 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     ap.add_argument("--out", required=True, help="folder for <step>.f32 files")
     ap.add_argument("--max-tokens", type=int, required=True,
                     help="most tokens live requests hold at any time, each rounded up to a multiple of 64")
+    ap.add_argument("--dump-activations", metavar="DIR", default=None,
+                    help="also write the residual stream after the embedding and after every run of a layer, "
+                         "DIR/<step>.act.f32 = float32 [1 + runs, tokens of the step, width]")
     a = ap.parse_args(argv)
     from .engine import Engine
     engine = Engine.from_folder(a.model, dtype=a.dtype, max_tokens=a.max_tokens, verbose=True)
@@ -79,7 +102,7 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
         sys.stdout.write(msg + "\n")
         sys.stdout.flush()
 
-    replay(engine, sys.stdin, a.out, say)
+    replay(engine, sys.stdin, a.out, say, dump_dir=a.dump_activations)
     engine.check()
     return 0
 

@@ -66,15 +66,21 @@ class DecoderModel:
         return plan
 
     # ------------------------------------------------------------------ one step
-    def forward(self, ctx, cache) -> Optional[torch.Tensor]:
+    def forward(self, ctx, cache, tap=None) -> Optional[torch.Tensor]:
         """Run the step's tokens through the schedule; return float32 logits
-        [wanted rows, vocab] (None when nothing is wanted)."""
+        [wanted rows, vocab] (None when nothing is wanted).  `tap(i, h)`, if given, is shown
+        the float32 residual stream [rows, width] after the embedding (i = 0) and after
+        schedule entry i - 1 (sums that a part left deferred are completed first)."""
         h = self.embedding.forward(ctx.token_ids, ctx.rows)
+        if tap is not None:
+            tap(0, h)
         for e, entry in enumerate(self.spec.schedule):
             view = cache.layer_view(e)
             if view is not None:
                 view.page_table = ctx.page_tables[view.group]
             h = self.blocks[entry.layer].forward(h, ctx, view, cache.state_view(e))
+            if tap is not None:
+                tap(e + 1, ctx.resolve(h))
         if ctx.n_want == 0:
             ctx.drop_deferred()
             return None

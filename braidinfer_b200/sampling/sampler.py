@@ -26,6 +26,35 @@ class Sampler:
         self.K = kernels
         self.device = device
         self._draws = 0
+        self._stages = []            # (pinned int32, device int32, event of the last copy), used in turn
+        self._turn = 0
+        self._work_buf: Optional[torch.Tensor] = None
+
+    def _stage(self, words: np.ndarray) -> torch.Tensor:
+        """Copy a step's option words to the device through pinned memory without blocking the
+        host; three buffers in turn, each waiting for its own last copy only."""
+        n = int(words.size)
+        if len(self._stages) < 3:
+            self._stages.append([None, None, None])
+        st = self._stages[self._turn % len(self._stages)]
+        self._turn += 1
+        if st[0] is None or st[0].numel() < n:
+            cap = max(1024, 1 << (n - 1).bit_length())
+            st[0] = torch.empty(cap, dtype=torch.int32, pin_memory=True)
+            st[1] = torch.empty(cap, dtype=torch.int32, device=self.device)
+            st[2] = None
+        if st[2] is not None:
+            st[2].synchronize()
+        st[0].numpy()[:n] = words
+        st[1][:n].copy_(st[0][:n], non_blocking=True)
+        st[2] = torch.cuda.Event()
+        st[2].record()
+        return st[1]
+
+    def _work(self, rows: int, vocab: int) -> torch.Tensor:
+        if self._work_buf is None or self._work_buf.numel() < rows * vocab:
+            self._work_buf = torch.empty(rows * vocab, dtype=torch.float32, device=self.device)
+        return self._work_buf[:rows * vocab].view(rows, vocab)
 
     def choose(self, logits: torch.Tensor, params: Sequence[SamplingParams], seeds: Sequence[int],
                sequence_ids: Sequence[int], steps: Sequence[int], histories=None) -> List[int]:
@@ -100,14 +129,20 @@ class Sampler:
                     bias_tok.append(tok)
                     bias_val.append(delta)
                 bias_off.append(len(bias_tok))
-            fd = torch.from_numpy(f).to(self.device, non_blocking=True)
-            idev = torch.from_numpy(np.concatenate([k, np.asarray(bias_off, np.int32),
-                                                    np.asarray(bias_tok, np.int32)]).astype(np.int32)).to(self.device)
-            bv = torch.tensor(bias_val, dtype=torch.float32, device=self.device) if bias_val else None
-            work = torch.empty((rows, vocab), dtype=torch.float32, device=self.device)
-            self.K.sample(logits, work, out, fd[0], fd[3], top_k=idev[:rows], top_p=fd[1], min_p=fd[2],
-                          bias_off=idev[rows:2 * rows + 1], bias_tok=idev[2 * rows + 1:] if bias_tok else None,
-                          bias_val=bv)
+            # every option of the step in one pinned buffer and one copy that does not wait
+            nb = len(bias_tok)
+            words = np.concatenate([f.reshape(-1).view(np.int32), k, np.asarray(bias_off, np.int32),
+                                    np.asarray(bias_tok, np.int32), np.asarray(bias_val, np.float32).view(np.int32)])
+            dev = self._stage(words)
+            fd = dev[:4 * rows].view(torch.float32).view(4, rows)
+            o = 4 * rows
+            kd = dev[o:o + rows]; o += rows
+            bo = dev[o:o + rows + 1]; o += rows + 1
+            bt = dev[o:o + nb] if nb else None; o += nb
+            bv = dev[o:o + nb].view(torch.float32) if nb else None
+            work = self._work(rows, vocab)
+            self.K.sample(logits, work, out, fd[0], fd[3], top_k=kd, top_p=fd[1], min_p=fd[2],
+                          bias_off=bo, bias_tok=bt, bias_val=bv)
         host = torch.empty(rows, dtype=torch.int32, pin_memory=True)
         host.copy_(out, non_blocking=True)
         done = torch.cuda.Event()

@@ -211,7 +211,7 @@ def decoder_layer(h, weights, layer: int, cfg, positions):
 
 
 def forward_logits(weights: Dict[str, torch.Tensor], cfg, tokens: Sequence[int],
-                   dtype=torch.float32, schedule: Optional[List] = None) -> torch.Tensor:
+                   dtype=torch.float32, schedule: Optional[List] = None, hidden: Optional[List] = None) -> torch.Tensor:
     """Logits [T, V] at every position of one whole sequence.
 
     Embedding, the layers in order, final norm, output head
@@ -221,15 +221,20 @@ def forward_logits(weights: Dict[str, torch.Tensor], cfg, tokens: Sequence[int],
 
     ``schedule`` (this library's own) lists (layer, cache_of) pairs: the order in
     which layers run; ``cache_of`` names an earlier schedule entry whose keys and
-    values the entry reads instead of making its own.
+    values the entry reads instead of making its own.  ``hidden``, a list, receives the
+    residual stream [T, width] after the embedding and after every run of a layer.
     """
     w = {k: v.to(dtype) for k, v in weights.items()}
     T = len(tokens)
     positions = torch.arange(T)
     h = embedding(w["model.embed_tokens.weight"], tokens, dtype)
+    if hidden is not None:
+        hidden.append(h)
     if schedule is None:
         for layer in range(cfg.num_hidden_layers):
             h = decoder_layer(h, w, layer, cfg, positions)
+            if hidden is not None:
+                hidden.append(h)
     else:
         kept = []
         for layer, cache_of in schedule:
@@ -242,6 +247,8 @@ def forward_logits(weights: Dict[str, torch.Tensor], cfg, tokens: Sequence[int],
             n = rmsnorm(h, w[prefix + "post_attention_layernorm.weight"], cfg.rms_norm_eps)
             h = h + swiglu(n, w[prefix + "mlp.gate_proj.weight"], w[prefix + "mlp.up_proj.weight"],
                            w[prefix + "mlp.down_proj.weight"])
+            if hidden is not None:
+                hidden.append(h)
     h = rmsnorm(h, w["model.norm.weight"], cfg.rms_norm_eps)
     head = w.get("lm_head.weight", w["model.embed_tokens.weight"])
     return linear(h, head)

@@ -191,3 +191,48 @@ def test_fused_and_unfused_reduces_agree(model):
         outs.append(torch.cat([a, b, c]).clone())
         eng.check()
     assert (outs[0] - outs[1]).abs().max().item() < 1e-6
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_dump_of_the_residual_stream_after_every_layer(dtype, tmp_path):
+    """`bin/trace_run --dump-activations`: a prompt in one step, then two single tokens (which
+    would run through a CUDA graph without the dump); the residual stream after the embedding
+    and after every layer equals the plain implementation's, and the logits are the ones a
+    run without the dump writes."""
+    import plain_mistral as P
+    folder = sharpen(make_folder(tmp_path, "C"), 5.0)
+    orc = Oracle(folder)
+    toks = random_prompts(orc.cfg.vocab_size, [80], seed=9)[0]
+    other = random_prompts(orc.cfg.vocab_size, [7], seed=10)[0]
+    lines = [{"step": 0, "entries": [{"id": "a", "tokens": toks[:70], "want": [69]},
+                                     {"id": "b", "tokens": other[:5], "want": []}], "end": []}]
+    for k in range(2):
+        lines.append({"step": k + 1, "entries": [{"id": "a", "tokens": [toks[70 + k]], "want": [0]},
+                                                 {"id": "b", "tokens": [other[5 + k]], "want": [0]}], "end": []})
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out, out2, acts = str(tmp_path / "out"), str(tmp_path / "out2"), str(tmp_path / "acts")
+    text = "".join(json.dumps(l) + "\n" for l in lines)
+    for extra, o in ((["--dump-activations", acts], out), ([], out2)):
+        p = subprocess.run([sys.executable, os.path.join(root, "bin", "trace_run"), "--model", folder, "--dtype", dtype,
+                            "--out", o, "--max-tokens", "256"] + extra, input=text, capture_output=True, text=True,
+                           timeout=600)
+        assert p.returncode == 0, p.stderr
+        assert p.stdout.split("\n")[:3] == ["done 0", "done 1", "done 2"]
+    hid_a, hid_b = [], []
+    P.forward_logits(orc.w, orc.cfg, toks[:72], torch.float64, hidden=hid_a)
+    P.forward_logits(orc.w, orc.cfg, other[:7], torch.float64, hidden=hid_b)
+    width, runs = orc.cfg.hidden_size, orc.cfg.num_hidden_layers
+    tol = 2e-5 if dtype == "float32" else 4e-2                # the stream itself, of order 1, not logits
+    a0 = np.fromfile(os.path.join(acts, "0.act.f32"), dtype="<f4").reshape(1 + runs, 75, width)
+    for i in range(1 + runs):
+        assert np.abs(a0[i, :70] - hid_a[i][:70].numpy()).max() < tol, i
+        assert np.abs(a0[i, 70:] - hid_b[i][:5].numpy()).max() < tol, i
+    for k in range(2):
+        ak = np.fromfile(os.path.join(acts, f"{k + 1}.act.f32"), dtype="<f4").reshape(1 + runs, 2, width)
+        for i in range(1 + runs):
+            assert np.abs(ak[i, 0] - hid_a[i][70 + k].numpy()).max() < tol
+            assert np.abs(ak[i, 1] - hid_b[i][5 + k].numpy()).max() < tol
+    for s in range(3):                                        # the dump changes no logit beyond rounding
+        x = np.fromfile(os.path.join(out, f"{s}.f32"), dtype="<f4")
+        y = np.fromfile(os.path.join(out2, f"{s}.f32"), dtype="<f4")
+        assert x.shape == y.shape and np.abs(x - y).max() < (1e-5 if dtype == "float32" else 2e-2)
