@@ -4,9 +4,12 @@
 // inverse CDF with a uniform number that the caller supplies per row.
 //
 // One block per row of logits; all arithmetic float32.  Where the reference sorts,
-// this finds the cut value by bisection on the bit pattern of the floats, and keeps
-// the lowest indices of a tie at the cut (the reference's unstable sort leaves that
-// order open).  Argmax returns the lowest index of the maximum.
+// this finds the cut value on the bit pattern of the floats (top-k: the k-th largest key
+// digit by digit, eight bits a pass, from counts in shared memory; top-p: bisection on
+// the probability mass), and keeps the lowest indices of a tie at the cut (the
+// reference's unstable sort leaves that order open).  When top-k leaves at most a
+// block's worth of candidates, they are gathered into shared memory in index order and
+// the rest of the chain runs on them alone.  Argmax returns the lowest index of the maximum.
 #include "common.cuh"
 
 #define SAMP_THREADS 1024
@@ -167,6 +170,108 @@ __device__ void apply_cut(float* x, int n, unsigned int cut, int keep_equal, int
     __syncthreads();
 }
 
+// The k-th largest key of x[0..n): most significant digit first, eight bits a pass.  After a
+// pass `prefix` holds the digits found so far and `want` the rank still looked for among
+// the keys that share them.  Counts are integers, so the result does not depend on timing.
+__device__ unsigned int kth_largest_key(const float* x, int n, int k, int* hist /* [256] */, int* shi) {
+    unsigned int prefix = 0;
+    int want = k;
+    for (int shift = 24; shift >= 0; shift -= 8) {
+        for (int i = threadIdx.x; i < 256; i += blockDim.x) hist[i] = 0;
+        __syncthreads();
+        const unsigned int mask = (shift == 24) ? 0u : (0xffffffffu << (shift + 8));
+        for (int i = threadIdx.x; i < n; i += blockDim.x) {
+            const unsigned int key = float_key(x[i]);
+            if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 255u], 1);
+        }
+        __syncthreads();
+        // the highest digit d with count(digits >= d) >= want: one warp walks the 256 counts from the top
+        if (threadIdx.x < 32) {
+            int carried = 0, digit = 0, left = want;
+            bool done = false;
+            for (int base = 224; base >= 0 && !done; base -= 32) {
+                const int c = hist[base + 31 - threadIdx.x];                 // lane 0 holds the highest digit of the group
+                int inc = c;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const int t = __shfl_up_sync(0xffffffffu, inc, o);
+                    if ((int)threadIdx.x >= o) inc += t;
+                }
+                const unsigned int hit = __ballot_sync(0xffffffffu, carried + inc >= want);
+                if (hit) {
+                    const int lane = __ffs(hit) - 1;
+                    digit = base + 31 - lane;
+                    const int before = carried + __shfl_sync(0xffffffffu, inc, lane) - __shfl_sync(0xffffffffu, c, lane);
+                    left = want - before;
+                    done = true;
+                } else {
+                    carried += __shfl_sync(0xffffffffu, inc, 31);
+                }
+            }
+            if (threadIdx.x == 0) { shi[0] = digit; shi[1] = left; }
+        }
+        __syncthreads();
+        prefix |= ((unsigned int)shi[0]) << shift;
+        want = shi[1];
+        __syncthreads();
+    }
+    return prefix;
+}
+
+// The rest of the chain after top-k, on at most blockDim.x candidates held in shared memory in
+// index order (cv: values, ci: indices; thread t owns candidate t).  Same steps, same order of
+// sums along the index as the full-row form below.
+__device__ int sample_few(float* cv, const int* ci, int m, float mp, float tp, float u, float* shf, int* shi,
+                          int* found, int* nan_flag) {
+    const int t = threadIdx.x;
+    float v = (t < m) ? cv[t] : -INFINITY;
+    if (mp > 0.f) {                                                  // min-p
+        const float mx = block_reduce_max(v, shf);
+        if (v > -INFINITY && expf(v - mx) < mp) v = -INFINITY;
+        __syncthreads();
+    }
+    if (tp < 1.f) {                                                  // top-p
+        const float mx = block_reduce_max(v, shf);
+        const float total = block_reduce_sum(expf(v - mx), shf);
+        const float p = expf(v - mx) / total;
+        const unsigned int key = float_key(v);
+        unsigned int cut = 0;
+        for (int bit = 31; bit >= 0; --bit) {
+            const unsigned int cand = cut | (1u << bit);
+            if (block_reduce_sum(key >= cand ? p : 0.f, shf) >= tp) cut = cand;
+        }
+        const float above = block_reduce_sum(key > cut ? p : 0.f, shf);
+        const float pv = block_reduce_max(key == cut ? p : 0.f, shf);
+        int keep = 1;
+        if (pv > 0.f) {
+            float c = above;
+            keep = 0;
+            do { c += pv; ++keep; } while (c < tp && keep < m);
+        }
+        if (cut != 0) {
+            const int before = block_exclusive_iscan(key == cut ? 1 : 0, shi);
+            if (key < cut || (key == cut && before >= keep)) v = -INFINITY;
+            __syncthreads();
+        }
+    }
+    if (v != v && nan_flag) atomicExch(nan_flag, 1);
+    const float mx = block_reduce_max(v, shf);
+    const float total = block_reduce_sum(expf(v - mx), shf);
+    const float p = expf(v - mx) / total;
+    const float c = block_exclusive_scan(p, shf) + p;
+    if (t == 0) *found = 0x7fffffff;
+    __syncthreads();
+    if (t < m && u <= c) atomicMin(found, t);
+    __syncthreads();
+    int r = *found;
+    if (r == 0x7fffffff) {                                           // falls back to the largest (lowest index of a tie)
+        const int cand = (t < m && v == mx) ? t : 0x7fffffff;
+        r = block_reduce_imin(cand, shi);
+        if (r == 0x7fffffff) r = 0;
+    }
+    return ci[r];
+}
+
 __global__ void __launch_bounds__(SAMP_THREADS)
 sample_kernel(SampleArgs a) {
     pdl_trigger();
@@ -174,6 +279,9 @@ sample_kernel(SampleArgs a) {
     __shared__ float shf[32];
     __shared__ int shi[32];
     __shared__ int found;
+    __shared__ int hist[256];
+    __shared__ float cand_v[SAMP_THREADS];
+    __shared__ int cand_i[SAMP_THREADS];
     const int row = blockIdx.x, n = a.vocab;
     const float* in = a.logits + (size_t)row * a.ld;
     float* x = a.work + (size_t)row * n;
@@ -211,16 +319,39 @@ sample_kernel(SampleArgs a) {
     // top-k (sampling.rs:90-104): the k-th largest key by bisection
     const int k = a.top_k ? a.top_k[row] : 0;
     if (k > 0 && k < n) {
-        unsigned int cut = 0;
-        for (int bit = 31; bit >= 0; --bit) {
-            const unsigned int cand = cut | (1u << bit);
-            int c = 0;
-            for (int i = threadIdx.x; i < n; i += blockDim.x) c += (float_key(x[i]) >= cand);
-            if (block_reduce_isum(c, shi) >= k) cut = cand;
-        }
+        const unsigned int cut = kth_largest_key(x, n, k, hist, shi);
         int c = 0;
         for (int i = threadIdx.x; i < n; i += blockDim.x) c += (float_key(x[i]) > cut);
         const int above = block_reduce_isum(c, shi);
+        if (k <= (int)blockDim.x) {
+            // few candidates: gather them in index order (those above the cut, and the lowest
+            // indices of the tie at it), and finish the chain on them alone
+            const int chunk = (n + blockDim.x - 1) / blockDim.x;
+            const int b = min(n, (int)threadIdx.x * chunk), e = min(n, b + chunk);
+            int eq = 0, gt = 0;
+            for (int i = b; i < e; ++i) {
+                const unsigned int key = float_key(x[i]);
+                eq += (key == cut);
+                gt += (key > cut);
+            }
+            int eq_before = block_exclusive_iscan(eq, shi);
+            __syncthreads();
+            const int keep_equal = k - above;
+            const int kept_eq = max(0, min(eq, keep_equal - eq_before));
+            int at = block_exclusive_iscan(gt + kept_eq, shi);
+            for (int i = b; i < e; ++i) {
+                const float v = x[i];
+                const unsigned int key = float_key(v);
+                bool keep = key > cut;
+                if (key == cut) { keep = eq_before < keep_equal; ++eq_before; }
+                if (keep) { cand_v[at] = v; cand_i[at] = i; ++at; }
+            }
+            __syncthreads();
+            const int r = sample_few(cand_v, cand_i, k, a.min_p ? a.min_p[row] : 0.f, a.top_p ? a.top_p[row] : 1.f,
+                                     a.uniform[row], shf, shi, &found, a.nan_flag);
+            if (threadIdx.x == 0) a.out[row] = r;
+            return;
+        }
         apply_cut(x, n, cut, k - above, shi);
     }
 
