@@ -479,6 +479,109 @@ def run_timeline(args):
     return 0
 
 
+def run_chain(args):
+    """What the chain of dependent kernels of a decode step costs, at the default sizes: products alone chained to
+    themselves, and product + reducer pairs, each six times over distinct weights in one CUDA graph, timed with
+    events (L2 flushed before each replay).  With BRAIDINFER_TRACE=1 in the environment the library is built with
+    time stamps at the phase boundaries of the product and of the reduce + norm kernel (csrc/trace.cuh); the
+    line then also carries, for the o product + reducer chain, the median over CTAs of every stamp, in
+    microseconds from the chain's first entry.  Not the contract's line."""
+    import ctypes
+    import numpy as np
+    import torch
+    from braidinfer_b200.csrc import build
+    from braidinfer_b200.csrc.api import get_kernels, interleave_gate_up
+    K = get_kernels(verbose=True)
+    dev, B = "cuda", args.batch
+    hs, I, nq, nk, hd, NL = 4096, 14336, 32, 8, 128, 6
+    g = torch.Generator(device=dev).manual_seed(0)
+    rn = lambda *sh: (torch.randn(*sh, device=dev, generator=g) * 0.02).bfloat16()
+    W = {"qkv": [rn((nq + 2 * nk) * hd, hs) for _ in range(NL)], "o": [rn(hs, nq * hd) for _ in range(NL)],
+         "gate_up": [interleave_gate_up(rn(I, hs), rn(I, hs)) for _ in range(NL)], "down": [rn(hs, I) for _ in range(NL)]}
+    X = {"qkv": rn(B, hs), "o": rn(B, nq * hd), "gate_up": rn(B, hs), "down": rn(B, I)}
+    wn = torch.ones(hs, device=dev, dtype=torch.bfloat16)
+    h = torch.zeros(B, hs, device=dev)
+    out = torch.empty(B, hs, device=dev, dtype=torch.bfloat16)
+    act = torch.empty(B, I, device=dev, dtype=torch.bfloat16)
+    flush = torch.empty(256 << 20, device=dev, dtype=torch.uint8)
+
+    def product_only(name):
+        def f(l):
+            K.gemm_tc_partial(X[name], W[name][l])
+            K.pending_partial = None
+        return f
+
+    def with_reducer(name):
+        def f(l):
+            p = K.gemm_tc_partial(X[name], W[name][l])
+            if name == "gate_up":
+                K.streamk_reduce(p, act, swiglu=True)
+            else:
+                K.streamk_reduce_norm(p, h, wn, out, 1e-5)
+        return f
+
+    def graph_of(fn):
+        body = lambda: [fn(l) for l in range(NL)]
+        body()
+        torch.cuda.synchronize()
+        gr = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gr):
+            body()
+        K.pending_partial = None
+        return gr
+
+    def timed(gr, reps=20):
+        ts = []
+        for _ in range(reps):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(); gr.replay(); e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1) * 1e3 / NL)
+        return round(statistics.median(ts), 2)
+
+    pk = peaks()
+    res = {}
+    for name in ("o", "qkv", "down", "gate_up"):
+        ideal = W[name][0].numel() * 2 / (pk["hbm_gbs"] * 1e3)
+        res[name] = {"bytes_over_bandwidth_us": round(ideal, 2), "product_alone_us": timed(graph_of(product_only(name))),
+                     "product_and_reducer_us": timed(graph_of(with_reducer(name)))}
+    line = {"metric": "chains of decode-step kernels, Mistral-7B-v0.3 layer sizes, bf16", "impl": "ours", "batch": B,
+            "peaks": pk, "per_kernel_or_pair": res}
+    if build.trace_build():
+        gr = graph_of(with_reducer("o"))
+        for _ in range(2):
+            flush.zero_(); gr.replay()
+        traces = {}
+        for kname, ctas, names in (("gemm_tc", 160, ["entry", "set_up", "ring_asked", "wait_over", "first_stage_full",
+                                                     "last_accumulator", "epilogue_done", "all_done"]),
+                                   ("reduce_norm", 64, ["entry", "before_wait", "wait_over", "loaded_and_added",
+                                                        "block_sum_done", "stored"])):
+            read = getattr(K.lib, f"braid_{kname}_trace_read")
+            buf = (ctypes.c_ulonglong * (64 * ctas * 8))()
+            read(buf, 1)                                   # forget the warm-up launches
+            traces[kname] = (read, buf, ctas, names)
+        flush.zero_()
+        torch.cuda.synchronize()
+        gr.replay()
+        torch.cuda.synchronize()
+        t0, table = None, {}
+        for kname, (read, buf, ctas, names) in traces.items():
+            read(buf, 0)
+            t = np.frombuffer(buf, dtype=np.uint64).reshape(64, ctas, 8).astype(np.float64)
+            if t0 is None:
+                t0 = t[0, :, 0][t[0, :, 0] > 0].min()
+            rows = []
+            for l in range(NL):
+                ok = t[l, :, 0] > 0
+                if ok.any():
+                    rows.append({n: round(float(np.median(t[l, ok, i]) - t0) / 1e3, 2) for i, n in enumerate(names)})
+            table[kname] = rows
+        line["trace_o_product_and_reducer_us"] = table
+    print(json.dumps(line))
+    return 0
+
+
 def run_reference(args):
     print(json.dumps({"impl": "reference", "unavailable":
                       "mcelrath/braidinfer is Rust + HIP for AMD RDNA3: pip finds neither setup.py nor pyproject.toml, "
@@ -503,6 +606,9 @@ def main() -> int:
                     help="the default is the contract's run; the other two print their own line (see run_other_size)")
     ap.add_argument("--sweep", action="store_true",
                     help="decode over batch and context, prefill over prompt length; prints its own line (see run_sweep)")
+    ap.add_argument("--chain", action="store_true",
+                    help="what chains of decode-step kernels cost, with phase time stamps under BRAIDINFER_TRACE=1 "
+                         "(see run_chain)")
     ap.add_argument("--timeline", action="store_true",
                     help="one decode step under the torch profiler: a layer's kernels with their share (see run_timeline)")
     args = ap.parse_args()
@@ -515,6 +621,8 @@ def main() -> int:
         return run_sweep(args)
     if args.timeline:
         return run_timeline(args)
+    if args.chain:
+        return run_chain(args)
     if args.preset != "mistral_7b_v03":
         return run_other_size(args)
     return run_ours(args)

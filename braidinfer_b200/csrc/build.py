@@ -29,7 +29,7 @@ COMMON_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "--expt
 # Sources that do not depend on a model size.
 CORE_SOURCES = ["errors.cu", "elementwise.cu", "attn_simple.cu", "gemm_simt.cu", "gemm_tc.cu",
                 "fused_reduce.cu", "sampling.cu"]
-HEADERS = ["common.cuh", "streamk.cuh", "tcgen05.cuh", "attn_noalloc.h", "page.h"]
+HEADERS = ["common.cuh", "streamk.cuh", "tcgen05.cuh", "attn_noalloc.h", "page.h", "trace.cuh"]
 
 
 class BuildError(RuntimeError):
@@ -150,7 +150,15 @@ def build_library(name: str, sources: Sequence[str], defines: Sequence[str] = ()
     return target
 
 
+def trace_build() -> bool:
+    """BRAIDINFER_TRACE=1: the library is built with phase time stamps in its product and reduce
+    kernels (csrc/trace.cuh).  A library of its own name; the ordinary one is left alone."""
+    return os.environ.get("BRAIDINFER_TRACE", "0") not in ("", "0")
+
+
 def core_library(verbose: bool = True) -> Path:
+    if trace_build():
+        return build_library("braidinfer_core_trace", CORE_SOURCES, defines=["-DBRAID_TRACE"], verbose=verbose)
     return build_library("braidinfer_core", CORE_SOURCES, verbose=verbose)
 
 

@@ -12,6 +12,11 @@
 // Formulas are those of the unfused kernels (elementwise.cu cites the reference lines).
 #include "common.cuh"
 #include "streamk.cuh"
+#include "trace.cuh"
+
+// Slots of a traced reduce + norm launch: 0 entry, 1 before the dependency wait, 2 after it,
+// 3 partial sums and row loaded and added, 4 block-wide sum done, 5 stored.
+BRAID_TRACE_BUFFER(reduce_norm, 64)
 
 #define RN_MAX_THREADS 1024
 
@@ -22,6 +27,13 @@ template <typename TW, typename TO>
 __global__ void __launch_bounds__(RN_MAX_THREADS)
 streamk_reduce_norm_kernel(StreamK k, float* h, const TW* __restrict__ w, TO* __restrict__ out,
                            const int* __restrict__ row_index, int width, float eps) {
+#ifdef BRAID_TRACE
+    unsigned long long* trace_row = nullptr;
+    if (threadIdx.x == 0) {
+        trace_row = braid_trace_open(reduce_norm, 64);
+        BRAID_STAMP(trace_row, 0);
+    }
+#endif
     pdl_trigger();
     __shared__ float red[32];
     const int r = blockIdx.x;
@@ -42,7 +54,9 @@ streamk_reduce_norm_kernel(StreamK k, float* h, const TW* __restrict__ w, TO* __
         for (int e = 0; e < 4; ++e)
             if (g_first * 4 + e < width) w_first[e] = to_f32(w[g_first * 4 + e]);
     }
+    BRAID_STAMP(trace_row, 1);
     pdl_wait();
+    BRAID_STAMP(trace_row, 2);
     float v_first[4] = {0.f, 0.f, 0.f, 0.f};              // the new h of this thread's first group
     if (src >= 0) {
         float* hr = h + (size_t)src * width;
@@ -77,7 +91,9 @@ streamk_reduce_norm_kernel(StreamK k, float* h, const TW* __restrict__ w, TO* __
             if (g == g_first) { v_first[0] = v[0]; v_first[1] = v[1]; v_first[2] = v[2]; v_first[3] = v[3]; }
         }
     }
+    BRAID_STAMP(trace_row, 3);
     const float total = block_sum(ss, red);
+    BRAID_STAMP(trace_row, 4);
     if (src < 0) {
         for (int g = g_first; g < groups; g += blockDim.x)
             for (int e = 0; e < 4 && g * 4 + e < width; ++e) o[g * 4 + e] = from_f32<TO>(0.f);
@@ -105,6 +121,7 @@ streamk_reduce_norm_kernel(StreamK k, float* h, const TW* __restrict__ w, TO* __
             o[c + e] = from_f32<TO>(v * scale * to_f32(w[c + e]));
         }
     }
+    BRAID_STAMP(trace_row, 5);
 }
 
 extern "C" int braid_streamk_reduce_norm(const float* partial, const int* plan, int n_rows, float* h, const void* w,

@@ -35,6 +35,12 @@
 #include "common.cuh"
 #include "streamk.cuh"
 #include "tcgen05.cuh"
+#include "trace.cuh"
+
+// Slots of a traced launch: 0 entry, 1 barriers and tensor memory set up, 2 first ring of weight
+// tiles asked for, 3 dependency wait over, 4 first stage full, 5 last accumulator complete,
+// 6 epilogue done, 7 all warps done.
+BRAID_TRACE_BUFFER(gemm_tc, 160)
 
 #define TC_BLOCK_M 128
 #define TC_BLOCK_K 64
@@ -154,6 +160,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#ifdef BRAID_TRACE
+    __shared__ unsigned long long* trace_row_shared;
+    if (threadIdx.x == 0) {
+        trace_row_shared = braid_trace_open(gemm_tc, 160);
+        BRAID_STAMP(trace_row_shared, 0);
+    }
+#endif
     pdl_trigger();
     if (threadIdx.x == 0) {                    // the descriptors' own fetch, off the critical path
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
@@ -172,6 +185,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+#ifdef BRAID_TRACE
+    unsigned long long* const trace_row = trace_row_shared;
+    if (threadIdx.x == 0) BRAID_STAMP(trace_row, 1);
+#endif
 
     if (warp == 0) {
         if (lane == 0) {
@@ -193,7 +210,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                         tma_load_2d(&map_w, &full[n], sa, kx, t.m0);
                     }
             }
+            BRAID_STAMP(trace_row, 2);
             pdl_wait();
+            BRAID_STAMP(trace_row, 3);
             TcWalk<BLOCK_N, MODE> walk(a);
             TcUnit t;
             int issued = 0;                       // k blocks whose weight tile is already in flight
@@ -229,6 +248,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 for (int i = 0; i < t.num_kb; ++i) {
                     ok = mbar_wait(&full[stage], phase, abort_flag);
                     if (!ok) break;
+                    BRAID_STAMP_ONCE(trace_row, 4);
                     tc_fence_after();
                     const uint32_t sa = smem_u32(smem + stage * Cfg::kStageBytes);
                     const uint32_t sb = sa + Cfg::kABytes;
@@ -262,6 +282,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             const int m = (MODE == 2) ? (t.m0 + quarter * 32) / 2 + (lane & 15) : t.m0 + quarter * 32 + lane;
             ok = mbar_wait(&acc_full[buf], (full_phase >> buf) & 1u, abort_flag);
             if (!ok) break;
+            if (warp == 2 && lane == 0) BRAID_STAMP(trace_row, 5);
             tc_fence_after();
             const uint32_t trow = tmem_base + buf * Cfg::kAccCols + ((uint32_t)(quarter * 32) << 16);
             constexpr int CH = BLOCK_N >= 32 ? 32 : 16;       // columns per tensor-memory load and wait
@@ -331,8 +352,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             if (Cfg::kAccBufs == 2) buf ^= 1;
         }
     }
+    if (warp == 2 && lane == 0) BRAID_STAMP(trace_row, 6);
     tc_fence_before();
     __syncthreads();
+    if (threadIdx.x == 0) BRAID_STAMP(trace_row, 7);
     if (threadIdx.x == 0 && *abort_flag) atomicExch(a.error_flag, 1);
     if (warp == 1) {
         tc_fence_after();
