@@ -361,7 +361,7 @@ class Kernels:
         w_rows = w.shape[0]
         block_n = token_tile(n)
         ws = self._stream_k_workspace(n, w_rows, k, block_n)
-        plan = (c_int * 6)()
+        plan = (c_int * 8)()
         self.launches += 1
         self._check(self.lib.braid_gemm_tc(x.data_ptr(), w.data_ptr(), None, None, ws.data_ptr(), ws.numel() * 4,
                                            F32, 0, n, w_rows, k, x.stride(0), w.stride(0), 0, block_n, 1, plan,

@@ -129,7 +129,7 @@ extern "C" int braid_streamk_reduce_norm(const float* partial, const int* plan, 
                                          int width, float eps, void* stream) {
     if (rows_out <= 0) return BRAID_OK;
     if (width <= 0) BRAID_REFUSE("reduce_norm: width=%d must be positive", width);
-    StreamK k{partial, plan[0], plan[1], plan[2], plan[3], n_rows, plan[4], (long long)plan[5]};
+    const StreamK k = streamk_from_plan(partial, plan, n_rows);
     const int groups = (width + 3) / 4;
     int threads = ((groups + 31) / 32) * 32;
     if (threads > RN_MAX_THREADS) threads = RN_MAX_THREADS;
@@ -253,7 +253,7 @@ extern "C" int braid_streamk_reduce_rope_kv(const float* partial, const int* pla
     if (nqh <= 0 || nkh <= 0 || hd <= 0) BRAID_REFUSE("reduce_rope_kv: heads/head_dim must be positive");
     if (rope_dim < 0 || rope_dim > hd || (rope_dim & 1)) BRAID_REFUSE("reduce_rope_kv: rope_dim=%d must be even and <= head_dim=%d", rope_dim, hd);
     if (nqh + 2 * nkh > 65535) BRAID_REFUSE("reduce_rope_kv: %d heads exceed the grid limit", nqh + 2 * nkh);
-    ReduceRopeArgs a{{partial, plan[0], plan[1], plan[2], plan[3], rows, plan[4], (long long)plan[5]},
+    ReduceRopeArgs a{streamk_from_plan(partial, plan, rows),
                      (__nv_bfloat16*)qkv, inv_freq, positions, token_seq, page_table, (__nv_bfloat16*)cache,
                      rows, nqh, nkh, hd, rope_dim, adjacent, page_size, table_cols, num_pages, error_flag};
     braid_launch(streamk_reduce_rope_kv_kernel, dim3(rows, nqh + 2 * nkh), dim3(hd >= 128 ? 64 : 32), 0, (cudaStream_t)stream, a);

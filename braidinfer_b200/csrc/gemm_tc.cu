@@ -46,7 +46,6 @@ BRAID_TRACE_BUFFER(gemm_tc, 160)
 #define TC_BLOCK_K 64
 #define TC_UMMA_K 16
 #define TC_THREADS 192
-#define TC_GROUP_N 8            // token tiles that share their stay in L2 (see TcWalk)
 
 struct GemmTcArgs {
     void* out;                 // mode 0: [n, ldo] bf16/f32; 1: f32; 2: bf16/f32 [n, ldo]; 3: f32 [slot][n_rows][128]
@@ -57,6 +56,7 @@ struct GemmTcArgs {
     int m_tiles, n_tiles;
     int max_segs;              // mode 3: partial slots per CTA
     int* error_flag;
+    int tile_begin, tile_end;  // the tiles of the walk (tc_tile_coords) that this launch covers
 };
 
 template <int BLOCK_N, int MODE>
@@ -76,17 +76,18 @@ struct TcCfg {
 
 // Work of a persistent CTA.
 //
-// Modes 0-2: units u = blockIdx.x, blockIdx.x + gridDim.x, ...; a unit is one whole
-// [128 x BLOCK_N] output tile.  Token tiles vary fastest so that CTAs running side by
-// side share weight tiles in L2; with more than TC_GROUP_N token tiles they go in groups of
-// that many, each group against all the weights, or the tokens would not stay in L2.
+// Output tiles are numbered in walk order (tc_tile_coords in streamk.cuh); a launch covers tiles
+// [tile_begin, tile_end).
 //
-// Mode 3 ("stream-k", for steps whose whole tiles would leave SMs idle: a few tokens, or a
-// few hundred with few weight tiles): the
-// k blocks of all tiles form one line of m_tiles * n_tiles * total_kb blocks, cut into
+// Modes 0-2: units u = tile_begin + blockIdx.x, + gridDim.x, ...; a unit is one whole
+// [128 x BLOCK_N] output tile.
+//
+// Mode 3 ("stream-k", for steps whose whole tiles would leave SMs idle: a few tokens, or a few hundred
+// with few weight tiles): the
+// k blocks of the launch's tiles form one line of (tile_end - tile_begin) * total_kb blocks, cut into
 // gridDim.x equal ranges.  A CTA's range is a run of segments (tile, first k block,
 // count); it writes the float32 partial product of its j-th segment to slot
-// blockIdx.x * max_segs + j, and braid_gemm_tc's reduce kernel adds the slots of a tile
+// blockIdx.x * max_segs + j, and a reduce kernel adds the slots of a tile
 // in ascending CTA order.  Every CTA streams the same number of bytes whatever the shape.
 struct TcUnit { int m0, n0, slot, kb_begin, num_kb; };
 
@@ -99,27 +100,28 @@ struct TcWalk {
     __device__ TcWalk(const GemmTcArgs& a_) : a(a_) {
         total_kb = (a.k_in + TC_BLOCK_K - 1) / TC_BLOCK_K;
         if (MODE == 3) {
-            const long long w = (long long)a.m_tiles * a.n_tiles * total_kb;
+            const long long w = (long long)(a.tile_end - a.tile_begin) * total_kb;
             idx = (long long)blockIdx.x * w / gridDim.x;
             hi = (long long)(blockIdx.x + 1) * w / gridDim.x;
         } else {
             idx = hi = 0;
         }
-        u = blockIdx.x;
+        u = a.tile_begin + blockIdx.x;
         seg = 0;
     }
     __device__ bool next(TcUnit& t) {
         int tile;
         if (MODE == 3) {
             if (idx >= hi) return false;
-            tile = (int)(idx / total_kb);
-            t.kb_begin = (int)(idx - (long long)tile * total_kb);
+            const int in_line = (int)(idx / total_kb);
+            tile = a.tile_begin + in_line;
+            t.kb_begin = (int)(idx - (long long)in_line * total_kb);
             t.num_kb = (int)min((long long)(total_kb - t.kb_begin), hi - idx);
             t.slot = blockIdx.x * a.max_segs + seg;
             idx += t.num_kb;
             ++seg;
         } else {
-            if (u >= a.m_tiles * a.n_tiles) return false;
+            if (u >= a.tile_end) return false;
             tile = u;
             t.kb_begin = 0;
             t.num_kb = total_kb;
@@ -127,18 +129,7 @@ struct TcWalk {
             u += gridDim.x;
         }
         int mt, nt;
-        if (MODE == 3 || a.n_tiles <= TC_GROUP_N) {
-            nt = tile % a.n_tiles;
-            mt = tile / a.n_tiles;
-        } else {
-            // many token tiles: groups of TC_GROUP_N of them, each group against all weight tiles
-            // before the next, so that a group's tokens stay in L2 while the weights stream past
-            const int per_group = TC_GROUP_N * a.m_tiles;
-            const int grp = tile / per_group, r = tile - grp * per_group;
-            const int width = min(TC_GROUP_N, a.n_tiles - grp * TC_GROUP_N);
-            mt = r / width;
-            nt = grp * TC_GROUP_N + (r - mt * width);
-        }
+        tc_tile_coords(tile, a.m_tiles, a.n_tiles, mt, nt);
         t.m0 = mt * TC_BLOCK_M;
         t.n0 = nt * BLOCK_N;
         return true;
@@ -320,8 +311,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 const bool mine = true;
                 if (mine && m < a.m_out) {
                     if (MODE == 3) {
-                        // slot layout [n_rows][128]: this thread's output feature is column quarter * 32 + lane
-                        float* dst = (float*)a.out + ((size_t)t.slot * a.n_rows + t.n0 + c0) * TC_BLOCK_M + quarter * 32 + lane;
+                        // slot layout [BLOCK_N][128]: this thread's output feature is column quarter * 32 + lane
+                        float* dst = (float*)a.out + ((size_t)t.slot * BLOCK_N + c0) * TC_BLOCK_M + quarter * 32 + lane;
 #pragma unroll
                         for (int i = 0; i < CH; ++i)
                             if (t.n0 + c0 + i < a.n_rows) dst[(size_t)i * TC_BLOCK_M] = v[i];
@@ -364,33 +355,41 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 }
 
 // ------------------------------------------------------------------ stream-k reduce
-// mode 0: store; 1: res + sum (float32); 2: columns [0, I) are gate and [I, 2I) are up,
-// out[n, I] = silu(gate) * up.  One thread per four consecutive outputs of a row.
+// Adds up the partial products of the tiles of a stream-k line and finishes them: mode 0 store;
+// 1 res + sum (float32); 2 the tile's weight rows interleave gate and up in blocks of 16 (its 128
+// rows are 64 outputs), out = silu(gate) * up.  One thread per four consecutive outputs of a
+// token; threads are laid over the line's tiles.
 template <int MODE>
 __global__ void streamk_reduce_kernel(StreamK k, void* __restrict__ out, const float* __restrict__ res,
                                       int m_out, long long ldo, int out_dtype) {
     pdl_trigger();
-    const int groups = (m_out + 3) / 4;
+    constexpr int GROUPS = (MODE == 2) ? 16 : 32;          // groups of four outputs that a tile holds per token
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= (long long)k.n_rows * groups) return;
-    const int n = (int)(i / groups), m = (int)(i - (long long)n * groups) * 4;
+    const long long per_tile = (long long)k.block_n * GROUPS;
+    const int in_line = (int)(i / per_tile);
+    if ((long long)in_line * k.total_kb >= k.w) return;
+    const int r = (int)(i - (long long)in_line * per_tile);
+    const int row = r / GROUPS, g = r - row * GROUPS;
+    int mt, nt;
+    tc_tile_coords(k.tile_begin + in_line, k.m_tiles, k.n_tiles, mt, nt);
+    const int n = nt * k.block_n + row;
+    // output feature m and, within the tile's 128 weight rows, the column(s) that hold its sum
+    const int m = (MODE == 2) ? mt * 64 + g * 4 : mt * STREAMK_TILE_M + g * 4;
+    const int c0 = (MODE == 2) ? mt * STREAMK_TILE_M + (g / 4) * 32 + (g % 4) * 4 : m;
+    if (n >= k.n_rows || m >= m_out) return;
     // where the partial sums lie is arithmetic only: done before the wait for the product
-    // interleaved rows (mode 2): outputs [16t, 16t+16) have gate in columns 32t.. and up in 32t+16..
-    const int c0 = (MODE == 2) ? (m / 16) * 32 + (m % 16) : m;
-    const StreamKSpan sp0 = streamk_span(k, n, c0);
-    StreamKSpan sp1 = sp0;
-    if (MODE == 2) sp1 = streamk_span(k, n, c0 + 16);
+    const StreamKSpan sp = streamk_span_of_tile(k, in_line);
     pdl_wait();
     float v[4];
     if (MODE == 2) {
-        const float4 g4 = streamk_sum4(k, sp0, n, c0);
-        const float4 u4 = streamk_sum4(k, sp1, n, c0 + 16);
+        const float4 g4 = streamk_sum4(k, sp, n, c0);
+        const float4 u4 = streamk_sum4(k, sp, n, c0 + 16);
         v[0] = g4.x / (1.f + expf(-g4.x)) * u4.x;
         v[1] = g4.y / (1.f + expf(-g4.y)) * u4.y;
         v[2] = g4.z / (1.f + expf(-g4.z)) * u4.z;
         v[3] = g4.w / (1.f + expf(-g4.w)) * u4.w;
     } else {
-        const float4 s4 = streamk_sum4(k, sp0, n, c0);
+        const float4 s4 = streamk_sum4(k, sp, n, c0);
         v[0] = s4.x; v[1] = s4.y; v[2] = s4.z; v[3] = s4.w;
     }
 #pragma unroll
@@ -401,6 +400,19 @@ __global__ void streamk_reduce_kernel(StreamK k, void* __restrict__ out, const f
         else if (out_dtype == BRAID_F32) ((float*)out)[o] = v[e];
         else ((__nv_bfloat16*)out)[o] = __float2bfloat16_rn(v[e]);
     }
+}
+
+static int launch_streamk_reduce(const StreamK& k, void* out, const float* res, int m_out, long long ldo, int out_dtype,
+                                 int mode, cudaStream_t s) {
+    const long long tiles = k.w / k.total_kb;
+    const long long total = tiles * k.block_n * (mode == 2 ? 16 : 32);
+    const int threads = 128;
+    const long long blocks = (total + threads - 1) / threads;
+    if (blocks > 0x7fffffffLL) BRAID_REFUSE("streamk_reduce: %lld outputs exceed one launch", total);
+    if (mode == 0) braid_launch(streamk_reduce_kernel<0>, dim3((int)blocks), dim3(threads), 0, s, k, out, res, m_out, ldo, out_dtype);
+    else if (mode == 1) braid_launch(streamk_reduce_kernel<1>, dim3((int)blocks), dim3(threads), 0, s, k, out, res, m_out, ldo, out_dtype);
+    else braid_launch(streamk_reduce_kernel<2>, dim3((int)blocks), dim3(threads), 0, s, k, out, res, m_out, ldo, out_dtype);
+    BRAID_LAUNCH_CHECK();
 }
 
 // ------------------------------------------------------------------ host side
@@ -454,18 +466,22 @@ static int dispatch_tc(int block_n, const CUtensorMap& mw, const CUtensorMap& mx
     BRAID_REFUSE("gemm_tc: token tile %d is not one of 16, 32, 64, 128, 256", block_n);
 }
 
-struct StreamKPlan { int grid, max_segs, total_kb, m_tiles, n_tiles; long long w, bytes; };
+struct StreamKPlan { int grid, max_segs, total_kb, m_tiles, n_tiles, tile_begin, tiles; long long w, bytes; };
 
 static StreamKPlan plan_stream_k(int n_rows, int w_rows, int k_in, int block_n) {
     StreamKPlan p;
     p.total_kb = (k_in + TC_BLOCK_K - 1) / TC_BLOCK_K;
     p.m_tiles = (w_rows + TC_BLOCK_M - 1) / TC_BLOCK_M;
     p.n_tiles = (n_rows + block_n - 1) / block_n;
-    p.w = (long long)p.m_tiles * p.n_tiles * p.total_kb;
+    const long long all = (long long)p.m_tiles * p.n_tiles;
+    p.tile_begin = 0;                  // the line holds every tile (the kernels take any first tile)
+    p.tiles = (int)(all - p.tile_begin);
+    p.w = (long long)p.tiles * p.total_kb;
     p.grid = (int)(p.w < sm_count() ? p.w : sm_count());
+    if (p.grid <= 0) { p.grid = 0; p.max_segs = 0; p.bytes = 0; return p; }
     const long long per = (p.w + p.grid - 1) / p.grid;
     p.max_segs = (int)((per + p.total_kb - 1) / p.total_kb) + 1;
-    p.bytes = (long long)p.grid * p.max_segs * n_rows * TC_BLOCK_M * 4;
+    p.bytes = (long long)p.grid * p.max_segs * block_n * TC_BLOCK_M * 4;
     return p;
 }
 
@@ -487,7 +503,7 @@ extern "C" long long braid_gemm_tc_workspace_bytes(int n_rows, int w_rows, int k
 // (`workspace_bytes` says how many it has; too few is refused, never written past).
 // block_n names the token tile: 16, 32, 64, 128 or 256.  With stream_k and plan_out != null only
 // the partial products are computed; plan_out receives {grid, max_segs, total_kb,
-// n_tiles, block_n, w} for the kernel that adds them up (fused_reduce.cu).
+// n_tiles, block_n, w, m_tiles, tile_begin} for the kernel that adds them up (fused_reduce.cu).
 extern "C" int braid_gemm_tc(const void* x, const void* w, void* out, const float* res, void* workspace,
                              long long workspace_bytes, int out_dtype, int mode, int n_rows, int m_out, int k_in,
                              long long ldx, long long ldw, long long ldo, int block_n, int stream_k,
@@ -519,35 +535,33 @@ extern "C" int braid_gemm_tc(const void* x, const void* w, void* out, const floa
     rc = make_map(&mx, x, n_rows, k_in, ldx, block_n);
     if (rc) return rc;
 
-    if (!stream_k) {
-        const int m_tiles = (w_rows + TC_BLOCK_M - 1) / TC_BLOCK_M;
-        const int n_tiles = (n_rows + block_n - 1) / block_n;
-        GemmTcArgs a{out, res, n_rows, m_out, k_in, ldo, out_dtype, m_tiles, n_tiles, 0, error_flag};
-        const long long units = (long long)m_tiles * n_tiles;
-        dim3 grid((unsigned)(units < sm_count() ? units : sm_count()), 1, 1);
-        if (mode == 0) return dispatch_tc<0>(block_n, mw, mx, a, grid, s);
-        if (mode == 1) return dispatch_tc<1>(block_n, mw, mx, a, grid, s);
-        return dispatch_tc<2>(block_n, mw, mx, a, grid, s);
+    const int m_tiles = (w_rows + TC_BLOCK_M - 1) / TC_BLOCK_M;
+    const int n_tiles = (n_rows + block_n - 1) / block_n;
+    const int all_tiles = m_tiles * n_tiles;
+    StreamKPlan p{};
+    if (stream_k) p = plan_stream_k(n_rows, w_rows, k_in, block_n);
+    const int whole_end = stream_k ? p.tile_begin : all_tiles;       // tiles [0, whole_end) run as whole tiles
+    if (whole_end > 0) {
+        GemmTcArgs a{out, res, n_rows, m_out, k_in, ldo, out_dtype, m_tiles, n_tiles, 0, error_flag, 0, whole_end};
+        dim3 grid((unsigned)(whole_end < sm_count() ? whole_end : sm_count()), 1, 1);
+        if (mode == 0) rc = dispatch_tc<0>(block_n, mw, mx, a, grid, s);
+        else if (mode == 1) rc = dispatch_tc<1>(block_n, mw, mx, a, grid, s);
+        else rc = dispatch_tc<2>(block_n, mw, mx, a, grid, s);
+        if (rc) return rc;
     }
-    const StreamKPlan p = plan_stream_k(n_rows, w_rows, k_in, block_n);
-    GemmTcArgs a{workspace, nullptr, n_rows, w_rows, k_in, 0, BRAID_F32, p.m_tiles, p.n_tiles, p.max_segs, error_flag};
+    if (!stream_k || p.tiles == 0) return BRAID_OK;
+    GemmTcArgs a{workspace, nullptr, n_rows, w_rows, k_in, 0, BRAID_F32, p.m_tiles, p.n_tiles, p.max_segs, error_flag,
+                 p.tile_begin, p.tile_begin + p.tiles};
     rc = dispatch_tc<3>(block_n, mw, mx, a, dim3(p.grid, 1, 1), s);
     if (rc) return rc;
     if (plan_out) {
         // the caller adds the partial products up itself (fused with what follows the product)
         plan_out[0] = p.grid; plan_out[1] = p.max_segs; plan_out[2] = p.total_kb; plan_out[3] = p.n_tiles;
-        plan_out[4] = block_n; plan_out[5] = (int)p.w;
+        plan_out[4] = block_n; plan_out[5] = (int)p.w; plan_out[6] = p.m_tiles; plan_out[7] = p.tile_begin;
         return BRAID_OK;
     }
-    const long long total = (long long)n_rows * ((m_out + 3) / 4);
-    const int threads = 128;
-    const long long blocks = (total + threads - 1) / threads;
-    if (blocks > 0x7fffffffLL) BRAID_REFUSE("gemm_tc: %lld outputs exceed one reduce launch", total);
-    StreamK k{(const float*)workspace, p.grid, p.max_segs, p.total_kb, p.n_tiles, n_rows, block_n, p.w};
-    if (mode == 0) braid_launch(streamk_reduce_kernel<0>, dim3((int)blocks), dim3(threads), 0, s, k, out, res, m_out, ldo, out_dtype);
-    else if (mode == 1) braid_launch(streamk_reduce_kernel<1>, dim3((int)blocks), dim3(threads), 0, s, k, out, res, m_out, ldo, out_dtype);
-    else braid_launch(streamk_reduce_kernel<2>, dim3((int)blocks), dim3(threads), 0, s, k, out, res, m_out, ldo, out_dtype);
-    BRAID_LAUNCH_CHECK();
+    StreamK k{(const float*)workspace, p.grid, p.max_segs, p.total_kb, p.n_tiles, n_rows, block_n, p.w, p.m_tiles, p.tile_begin};
+    return launch_streamk_reduce(k, out, res, m_out, ldo, out_dtype, mode, s);
 }
 
 // Add up the partial products of an earlier stream-k call made with plan_out (the same
@@ -557,14 +571,5 @@ extern "C" int braid_streamk_reduce(const float* partial, const int* plan, int n
     if (n_rows <= 0 || m_out <= 0) return BRAID_OK;
     if (mode < 0 || mode > 2) BRAID_REFUSE("streamk_reduce: unknown epilogue %d", mode);
     if (mode == 1 && (!res || out_dtype != BRAID_F32)) BRAID_REFUSE("streamk_reduce: the residual epilogue writes float32 and needs res");
-    StreamK k{partial, plan[0], plan[1], plan[2], plan[3], n_rows, plan[4], (long long)plan[5]};
-    const long long total = (long long)n_rows * ((m_out + 3) / 4);
-    const int threads = 128;
-    const long long blocks = (total + threads - 1) / threads;
-    if (blocks > 0x7fffffffLL) BRAID_REFUSE("streamk_reduce: %lld outputs exceed one launch", total);
-    cudaStream_t s = (cudaStream_t)stream;
-    if (mode == 0) braid_launch(streamk_reduce_kernel<0>, dim3((int)blocks), dim3(threads), 0, s, k, out, res, m_out, ldo, out_dtype);
-    else if (mode == 1) braid_launch(streamk_reduce_kernel<1>, dim3((int)blocks), dim3(threads), 0, s, k, out, res, m_out, ldo, out_dtype);
-    else braid_launch(streamk_reduce_kernel<2>, dim3((int)blocks), dim3(threads), 0, s, k, out, res, m_out, ldo, out_dtype);
-    BRAID_LAUNCH_CHECK();
+    return launch_streamk_reduce(streamk_from_plan(partial, plan, n_rows), out, res, m_out, ldo, out_dtype, mode, (cudaStream_t)stream);
 }

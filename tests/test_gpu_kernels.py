@@ -394,7 +394,8 @@ def test_plain_matrix_product(K, dtype, n, m, k):
     (16, 128, 64, False), (33, 200, 96, False), (1, 331, 120, False), (300, 1000, 520, False),
     (700, 384, 1024, False), (2048, 512, 256, False), (8, 512, 4096, True), (20, 256, 2048, True),
     (64, 1408, 1024, True), (3, 200, 8200, True), (1, 128, 64, True), (40, 20000, 320, True), (300, 640, 2048, True),
-    (2500, 400, 192, False), (4300, 136, 64, False)])      # 10 and 17 token tiles: groups of 8 and a narrower last group
+    (2500, 400, 192, False), (4300, 136, 64, False),       # 10 and 17 token tiles: groups of 8 and a narrower last group
+    (2500, 400, 192, True), (4300, 136, 64, True), (700, 384, 1024, True)])      # the same walk with partial sums
 def test_tensor_core_matrix_product(K, n, m, k, sk):
     x, w = rnd(n, k, dtype=torch.bfloat16, scale=0.5), rnd(m, k, dtype=torch.bfloat16, scale=0.5, seed=1)
     ref = x.double() @ w.double().t()
@@ -417,7 +418,8 @@ def test_tensor_core_matrix_product(K, n, m, k, sk):
 
 @pytest.mark.parametrize("n, inter, k, sk", [(300, 384, 512, False), (17, 200, 96, False), (20, 256, 2048, True),
                                              (64, 1000, 520, True), (8, 14336, 512, True), (700, 1000, 264, False),
-                                             (2048, 176, 64, False), (5, 63, 128, True), (2400, 300, 128, False)])
+                                             (2048, 176, 64, False), (5, 63, 128, True), (2400, 300, 128, False),
+                                             (2400, 300, 128, True), (300, 1000, 264, True)])
 def test_tensor_core_swiglu_epilogue(K, n, inter, k, sk):
     from braidinfer_b200.csrc.api import interleave_gate_up
     x = rnd(n, k, dtype=torch.bfloat16, scale=0.5)
@@ -442,7 +444,7 @@ def test_stream_k_refuses_a_workspace_that_is_too_small_and_takes_any_token_tile
         K.check_device_errors()
         assert (out.double() - want).abs().max().item() < want.abs().max().item() / 128      # bfloat16 output
     need = K.lib.braid_gemm_tc_workspace_bytes(300, 512, 256, 128)
-    assert need > K.lib.braid_gemm_tc_workspace_bytes(300, 512, 256, 256) > 0
+    assert need > 0 and 0 < K.lib.braid_gemm_tc_workspace_bytes(300, 512, 256, 256) != need        # sized for the tile named
     assert K.lib.braid_gemm_tc_workspace_bytes(300, 512, 256, 48) == -1
     ws = torch.empty(need // 4, dtype=torch.float32, device=DEV)
     out = torch.empty(300, 512, device=DEV, dtype=torch.bfloat16)
