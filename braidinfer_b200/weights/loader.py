@@ -10,6 +10,13 @@ Tensors that the folder holds and no part asks for (older exports store
 `UnexpectedTensorsWarning` and in the error, if there is one; `strict=True` makes
 them an error of their own.
 
+Names: the parts ask for the names Mistral model folders use.  A folder that stores the same
+tensors under one more prefix (a model wrapped into a larger one: ``language_model.model.layers.0...``)
+is found by the reference through the text before ``layers.0.`` in any tensor name
+(crates/braidinfer-runtime/src/model/model_load.rs:219-239); here the same discovery runs when
+asked-for names are missing: if every one of them is there under one common prefix, that prefix
+is used.
+
 Element types: floating tensors stored in 16 bits are kept in bfloat16, a tensor
 stored in 32 bits stays float32, integer tables become int32.  A float32 run widens
 everything floating to float32 (exactly; bfloat16 -> float32 loses nothing).  A
@@ -69,11 +76,39 @@ def target_dtype(stored: torch.dtype, spec: TensorSpec, run_dtype: torch.dtype) 
     return torch.bfloat16
 
 
+def discover_prefix(found_names, specs: Mapping[str, TensorSpec]) -> str:
+    """The prefix P under which most of the asked-for, non-optional names are stored as P + name,
+    or "" when no prefix holds more of them than the names as they are.  Candidates are the texts
+    before an asked-for first-layer name inside a stored name (model_load.rs:219-239 takes the
+    text before "layers.0."; a candidate with "mtp" in it, a draft head, comes last there and here)."""
+    names = set(found_names)
+    required = [n for n, s in specs.items() if not s.optional]
+    anchors = [n for n in required if "layers.0." in n] or required[:1]
+    candidates = []
+    for stored in found_names:
+        for a in anchors:
+            if stored.endswith(a) and len(stored) > len(a):
+                p = stored[:-len(a)]
+                if p not in candidates:
+                    candidates.append(p)
+    candidates.sort(key=lambda p: ("mtp" in p, len(p)))
+    best, best_hits = "", sum(n in names for n in required)
+    for p in candidates:
+        hits = sum(p + n in names for n in required)
+        if hits > best_hits:
+            best, best_hits = p, hits
+    return best
+
+
 def load_tensors(folder: str, specs: Mapping[str, TensorSpec], run_dtype: torch.dtype,
                  device, strict: bool = False) -> Dict[str, torch.Tensor]:
     """Check the folder against `specs`, then copy every asked-for tensor to `device`.
     `strict`: tensors nobody asks for are an error instead of a warning."""
     found = open_model_folder(folder)
+    if any(n not in found and not s.optional for n, s in specs.items()):
+        prefix = discover_prefix(list(found), specs)
+        if prefix:                       # the same tensors under one more prefix: look them up there
+            found = {(n[len(prefix):] if n.startswith(prefix) else n): v for n, v in found.items()}
     missing = [n for n, s in specs.items() if n not in found and not s.optional]
     unexpected = [n for n in found if n not in specs]
     wrong_shape, wrong_dtype = [], []

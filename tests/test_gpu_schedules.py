@@ -49,16 +49,25 @@ def test_graph_steps_past_the_first_table_widths(name, dtype, tmp_path):
     assert torch.equal(with_graphs, without)
 
 
-def test_one_layer_at_the_measured_models_widths():
-    """Width 4096, 32 query and 8 kv heads of 128, feed-forward 14336: the tile sizes, the
-    stream-k plans and the attention kernels that the measured model runs, met by float64."""
+WIDE = {
+    # the measured model's layer: width 4096, 32 query and 8 kv heads of 128, feed-forward 14336
+    "7b": dict(hidden_size=4096, num_attention_heads=32, num_key_value_heads=8, head_dim=128, intermediate_size=14336,
+               vocab_size=2048, rope_theta=1e6, rms_norm_eps=1e-5, sliding_window=None),
+    # a width that is not heads x head size (5120 against 32 x 128), and a window that the prompts run past
+    "12b_window": dict(hidden_size=5120, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
+                       intermediate_size=14336, vocab_size=3000, rope_theta=1e6, rms_norm_eps=1e-5, sliding_window=40),
+}
+
+
+@pytest.mark.parametrize("name", sorted(WIDE))
+def test_one_layer_at_real_widths(name):
+    """The tile sizes, the stream-k plans and the attention kernels that the measured models run, met by
+    float64: three unequal prompts in one step, then six single tokens each."""
     from braidinfer_b200.engine import Engine
     from braidinfer_b200.models import architecture_for
     from braidinfer_b200.weights import draw_tensors, tensor_specs_of
-    d = {"architectures": ["MistralForCausalLM"], "num_hidden_layers": 1, "hidden_size": 4096,
-         "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": 14336,
-         "vocab_size": 2048, "rope_theta": 1e6, "rms_norm_eps": 1e-5, "tie_word_embeddings": False,
-         "max_position_embeddings": 4096}
+    d = dict(WIDE[name], architectures=["MistralForCausalLM"], num_hidden_layers=1, tie_word_embeddings=False,
+             max_position_embeddings=4096)
     arch = architecture_for(d)
     drawn = draw_tensors(tensor_specs_of(arch.build_spec(arch.config_from_dict(d))), 5, torch.bfloat16)
     eng = Engine(d, {n: t.to("cuda:0") for n, t in drawn.items()}, dtype="bfloat16", max_tokens=64 * 6, max_slots=3,

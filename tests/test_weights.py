@@ -122,6 +122,25 @@ def test_float16_weights_are_rounded_with_a_word_and_kept_whole_in_float32(tmp_p
     assert torch.equal(got32[name], half.float())
 
 
+def test_tensors_under_one_more_prefix_are_found(tmp_path):
+    # a model wrapped into a larger one stores "language_model.model.layers.0..." and so on; a draft head beside it
+    # ("mtp.") must not be taken for the model
+    folder = make_folder(tmp_path, "A")
+    mine = read_weights(folder)
+    tensors = {"language_model." + n: f.tensor(k).clone() for n, (f, k) in open_model_folder(folder).items()}
+    tensors["mtp.model.layers.0.input_layernorm.weight"] = torch.zeros(64, dtype=torch.bfloat16)
+    save_file(tensors, os.path.join(folder, "model.safetensors"))
+    with pytest.warns(UnexpectedTensorsWarning):
+        got = load_tensors(folder, specs_for(TINY_A), torch.bfloat16, "cpu")
+    assert set(got) == set(mine) and all(torch.equal(got[n].double(), mine[n]) for n in mine)
+    # one tensor missing under the prefix: the error names it by the name that was asked for
+    del tensors["language_model.model.norm.weight"]
+    save_file(tensors, os.path.join(folder, "model.safetensors"))
+    with pytest.raises(WeightsError) as e:
+        load_tensors(folder, specs_for(TINY_A), torch.bfloat16, "cpu")
+    assert e.value.missing == ["model.norm.weight"]
+
+
 def test_tied_head_needs_no_head_tensor(tmp_path):
     folder = make_folder(tmp_path, "C")
     assert "lm_head.weight" not in open_model_folder(folder)
