@@ -432,6 +432,41 @@ def test_tensor_core_swiglu_epilogue(K, n, inter, k, sk):
     assert ((out.double() - want).abs() <= want.abs() / 100 + 1e-3).all()
 
 
+@pytest.mark.parametrize("n, m, k", [(129, 136, 64), (300, 1000, 520), (700, 20000, 200), (2500, 400, 192),
+                                     (4300, 136, 72), (256, 256, 4104)])
+def test_product_on_pairs_of_sms(K, n, m, k):
+    """Tiles of 256 x 256 on two SMs each (more tiles than pairs at 20,000 rows; ragged edges in all three
+    sizes): float64 beside it, and the bits of the one-SM kernel with the same token tile, in all three epilogues."""
+    from braidinfer_b200.csrc.api import interleave_gate_up
+    x, w = rnd(n, k, dtype=torch.bfloat16, scale=0.5), rnd(m, k, dtype=torch.bfloat16, scale=0.5, seed=1)
+    ref = x.double() @ w.double().t()
+    scale = max(1.0, ref.abs().max().item())
+    for dtype, tol in ((torch.float32, 1e-5 * scale), (torch.bfloat16, scale / 128)):
+        pair, single = (torch.full((n, m), 9.0, device=DEV, dtype=dtype) for _ in range(2))
+        K.gemm_tc_pair(x, w, pair)
+        K.gemm_tc(x, w, single, block_n=256)
+        assert (pair.double() - ref).abs().max() < tol
+        assert torch.equal(pair, single)
+    res = rnd(n, m, seed=2)
+    res1 = res.clone()
+    K.gemm_tc_pair(x, w, res, residual=res)
+    K.gemm_tc(x, w, res1, residual=res1, block_n=256)
+    assert torch.equal(res, res1)
+    inter = m // 2
+    wi = interleave_gate_up(w[:inter], w[inter:2 * inter])
+    pair, single = (torch.full((n, inter), 9.0, device=DEV, dtype=torch.bfloat16) for _ in range(2))
+    K.gemm_tc_pair(x, wi, pair, swiglu=True)
+    K.gemm_tc(x, wi, single, swiglu=True, block_n=256)
+    g, u = ref[:, :inter], ref[:, inter:2 * inter]
+    want = g / (1 + torch.exp(-g)) * u
+    # gate and up carry the float32 product's error e <= 1e-5 * scale each (asserted above); |silu'| <= 1.1 and
+    # |silu(g)| <= |g| pass it on as 1.1 e |u| + e |g|, beside the bfloat16 rounding of the result
+    passed_on = 1e-5 * scale * (1.1 * u.abs() + g.abs())
+    assert ((pair.double() - want).abs() <= want.abs() / 100 + passed_on + 1e-3).all()
+    assert torch.equal(pair, single)
+    K.check_device_errors()
+
+
 def test_stream_k_refuses_a_workspace_that_is_too_small_and_takes_any_token_tile(K):
     """The partial sums of a stream-k product must fit the workspace it is given: the entry point
     checks that on the host for the very plan the kernel walks, whatever token tile is named."""
