@@ -112,7 +112,7 @@ class Kernels:
                                     c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_int, c_int,
                                     c_void_p, c_void_p, c_void_p]
         L.braid_gemm_tc2.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
-                                     c_longlong, c_longlong, c_longlong, c_void_p, c_void_p]
+                                     c_longlong, c_longlong, c_longlong, c_int, c_void_p, c_void_p]
         L.braid_streamk_reduce.argtypes = [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_longlong,
                                            c_int, c_int, c_void_p]
         L.braid_streamk_reduce_norm.argtypes = [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int,
@@ -361,9 +361,11 @@ class Kernels:
                                            self._error_flag.data_ptr() + 4, self._stream()), "gemm_tc")
 
     def gemm_tc_pair(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor,
-                     residual: Optional[torch.Tensor] = None, swiglu: bool = False) -> None:
+                     residual: Optional[torch.Tensor] = None, swiglu: bool = False, direct_out: bool = False) -> None:
         """As `gemm_tc` with whole tiles, on pairs of SMs: tiles of 256 weight rows x 256 tokens, each CTA of
-        a pair loading half of both operands (tcgen05.mma.cta_group::2).  For prompts."""
+        a pair loading half of both operands (tcgen05.mma.cta_group::2).  For prompts.  The output leaves
+        through TMA stores (a TMA reduce-add for a residual summed in place) where it can be addressed so;
+        `direct_out` makes every thread store its own elements instead, as it does anyway otherwise."""
         n, k = x.shape
         w_rows = w.shape[0]
         m = out.shape[1] if swiglu else w_rows
@@ -374,7 +376,8 @@ class Kernels:
         self.launches += 1
         self._check(self.lib.braid_gemm_tc2(x.data_ptr(), w.data_ptr(), out.data_ptr(), _ptr(residual),
                                             dtype_code(out.dtype), mode, n, m, k, x.stride(0), w.stride(0),
-                                            out.stride(0), self._error_flag.data_ptr() + 4, self._stream()),
+                                            out.stride(0), int(direct_out), self._error_flag.data_ptr() + 4,
+                                            self._stream()),
                     "gemm_tc_pair")
 
     def gemm_tc_partial(self, x: torch.Tensor, w: torch.Tensor) -> "PartialProduct":

@@ -16,7 +16,11 @@
 //                       the accumulator buffer are signalled in both CTAs (commit with
 //                       .multicast::cluster, which is no load);
 //   warps 2..5 (both)   epilogue of the CTA's 128 rows: store, float32 residual sum, or SwiGLU
-//                       (as in gemm_tc.cu); they arrive on the leader's `acc_empty`.
+//                       (as in gemm_tc.cu); they arrive on the leader's `acc_empty`.  Where the
+//                       output can be addressed by TMA, 32 tokens at a time go through a staging
+//                       tile in shared memory and leave as one TMA store; the residual sum in
+//                       place (out == res) is a TMA reduce-add, so no thread waits for a load of
+//                       the residual from global memory.
 //
 // Persistent: one cluster per pair of SMs walks the tiles in the order of tc_tile_coords.
 // Every wait is bounded by time; a wait that runs out sets *error_flag, and the kernel frees
@@ -35,7 +39,9 @@
 #define T2_A_BYTES (T2_BLOCK_M * T2_BLOCK_K * 2)
 #define T2_B_BYTES (T2_HALF_N * T2_BLOCK_K * 2)
 #define T2_STAGE_BYTES (T2_A_BYTES + T2_B_BYTES)
-#define T2_SMEM_BYTES (T2_STAGES * T2_STAGE_BYTES + 1024 + 256)
+#define T2_CHUNK 32              // token columns per tensor-memory load, and rows of a staging tile
+#define T2_OUT_BYTES (T2_CHUNK * T2_BLOCK_M * 4)          // one staging tile: [32 tokens][128 outputs] float32
+#define T2_SMEM_BYTES (T2_STAGES * T2_STAGE_BYTES + 2 * T2_OUT_BYTES + 1024 + 256)
 #define T2_TMEM_COLS 512        // two accumulator buffers of 256 columns
 #define T2_PEER_BIT_MASK 0xFEFFFFFFu      // a shared::cluster address with the CTA-rank bit cleared: the pair's leader
 
@@ -93,6 +99,32 @@ __device__ __forceinline__ void mbar_arrive_leader(uint64_t* bar) {
         ::"r"(smem_u32(bar)) : "memory");
 }
 
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* src, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"(map), "r"(smem_u32(src)), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, const void* src, int x, int y) {
+    asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"(map), "r"(smem_u32(src)), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// At most one group of stores may still be reading its staging tile.
+__device__ __forceinline__ void bulk_wait_read_1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void epilogue_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+// True only if it is true in all 128 epilogue threads: they meet at barriers inside a tile, so
+// they enter a tile together or not at all.
+__device__ __forceinline__ bool epilogue_all(bool ok) {
+    uint32_t r;
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t"
+        "setp.ne.u32 q, %1, 0;\n\t"
+        "bar.red.and.pred p, 1, 128, q;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(r) : "r"((uint32_t)ok) : "memory");
+    return r != 0;
+}
+
 struct T2Unit { int m0, n0; };
 
 struct T2Walk {
@@ -113,12 +145,14 @@ struct T2Walk {
     }
 };
 
-template <int MODE>
+template <int MODE, bool TMA_OUT>
 __global__ void __launch_bounds__(T2_THREADS, 1)
-gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, GemmTc2Args a) {
+gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                const __grid_constant__ CUtensorMap map_out, GemmTc2Args a) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    uint64_t* bars = (uint64_t*)(smem + T2_STAGES * T2_STAGE_BYTES);
+    uint8_t* staging = smem + T2_STAGES * T2_STAGE_BYTES;             // two tiles of T2_OUT_BYTES
+    uint64_t* bars = (uint64_t*)(staging + 2 * T2_OUT_BYTES);
     uint64_t* full = bars;                                  // counted in the leader only
     uint64_t* empty = bars + T2_STAGES;                     // one in each CTA, for its own loader
     uint64_t* acc_full = bars + 2 * T2_STAGES;              // [2], one in each CTA, for its own epilogue
@@ -133,6 +167,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
     if (threadIdx.x == 0) {
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
+        if (TMA_OUT) asm volatile("prefetch.tensormap [%0];" ::"l"(&map_out) : "memory");
         for (int s = 0; s < T2_STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
         for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 2 * 128); }
         *abort_flag = 0;
@@ -219,9 +254,10 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
         }
     } else {
         const int quarter = warp & 3;
+        const bool issuer = threadIdx.x == 64;             // the one thread that issues and awaits the TMA stores
         pdl_wait();
         int buf = 0;
-        uint32_t full_phase = 0;
+        uint32_t full_phase = 0, chunk_no = 0;
         bool ok = true;
         T2Walk walk(a);
         T2Unit t;
@@ -229,15 +265,54 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
             const int m0 = t.m0 + (int)rank * T2_BLOCK_M;                  // this CTA's 128 rows of the pair's 256
             const int m = (MODE == 2) ? (m0 + quarter * 32) / 2 + (lane & 15) : m0 + quarter * 32 + lane;
             ok = mbar_wait(&acc_full[buf], (full_phase >> buf) & 1u, abort_flag);
+            if (TMA_OUT) ok = epilogue_all(ok);
             if (!ok) break;
             tc_fence_after();
             const uint32_t trow = tmem_base + buf * T2_BLOCK_N + ((uint32_t)(quarter * 32) << 16);
-            constexpr int CH = 32;
+            constexpr int CH = T2_CHUNK;
 #pragma unroll 1
             for (int c0 = 0; c0 < T2_BLOCK_N; c0 += CH) {
                 if (t.n0 + c0 >= a.n_rows) break;
                 float v[CH];
                 tmem_ld32(trow + c0, v);
+                if (TMA_OUT) {
+                    // the staging tile is free once the store before the last one has read it
+                    uint8_t* tile = staging + (chunk_no & 1u) * T2_OUT_BYTES;
+                    ++chunk_no;
+                    if (issuer) bulk_wait_read_1();
+                    epilogue_sync();
+                    if (MODE == 2) {
+                        // [32 tokens][64 outputs] bfloat16; the halves of a warp swap values as below
+                        const bool is_up = (lane & 16) != 0;
+                        __nv_bfloat16* dst = (__nv_bfloat16*)tile + (is_up ? 64 : 0) + quarter * 16 + (lane & 15);
+#pragma unroll
+                        for (int p2 = 0; p2 < CH / 2; ++p2) {
+                            const float from_up = __shfl_xor_sync(0xffffffffu, v[2 * p2], 16);
+                            const float from_gate = __shfl_xor_sync(0xffffffffu, v[2 * p2 + 1], 16);
+                            const float g = is_up ? from_gate : v[2 * p2];
+                            const float u = is_up ? v[2 * p2 + 1] : from_up;
+                            dst[2 * p2 * 64] = __float2bfloat16_rn(__fdividef(g, 1.f + __expf(-g)) * u);
+                        }
+                    } else if (a.out_dtype == BRAID_F32) {
+                        float* dst = (float*)tile + quarter * 32 + lane;
+#pragma unroll
+                        for (int i = 0; i < CH; ++i) dst[i * T2_BLOCK_M] = v[i];
+                    } else {
+                        __nv_bfloat16* dst = (__nv_bfloat16*)tile + quarter * 32 + lane;
+#pragma unroll
+                        for (int i = 0; i < CH; ++i) dst[i * T2_BLOCK_M] = __float2bfloat16_rn(v[i]);
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    epilogue_sync();
+                    const int x0 = MODE == 2 ? m0 / 2 : m0;
+                    if (issuer && x0 < a.m_out) {
+                        // rows and columns past the matrix are clipped by the tensor map
+                        if (MODE == 1) tma_reduce_add_2d(&map_out, tile, x0, t.n0 + c0);
+                        else tma_store_2d(&map_out, tile, x0, t.n0 + c0);
+                        bulk_commit();
+                    }
+                    continue;
+                }
                 if (MODE == 2) {
                     // rows interleave gate and up in blocks of 16 (see gemm_tc.cu): the halves of a warp swap values
                     const bool is_up = (lane & 16) != 0;
@@ -281,6 +356,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
             full_phase ^= (1u << buf);
             buf ^= 1;
         }
+        if (TMA_OUT && issuer) bulk_wait_all();           // the stores are complete, not only read, before the kernel ends
     }
     tc_fence_before();
     __syncthreads();
@@ -307,11 +383,27 @@ static int make_map2(CUtensorMap* map, const void* base, long long rows, long lo
     return BRAID_OK;
 }
 
-template <int MODE>
-static int launch_tc2(const CUtensorMap& mw, const CUtensorMap& mx, const GemmTc2Args& a, int pairs, cudaStream_t s) {
+// The output as TMA sees it: `inner` contiguous elements a row, `rows` rows `ld` elements apart; box = 32 rows x box_inner.
+static int make_map_out(CUtensorMap* map, void* base, int out_dtype, long long inner, long long rows, long long ld, int box_inner) {
+    TcEncodeTiledFn fn = tc_encode_tiled_fn();
+    if (!fn) BRAID_REFUSE("gemm_tc2: the driver does not export cuTensorMapEncodeTiled");
+    const int esize = out_dtype == BRAID_F32 ? 4 : 2;
+    cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * esize};
+    cuuint32_t box[2] = {(cuuint32_t)box_inner, T2_CHUNK};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, out_dtype == BRAID_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base,
+                    dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                    CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) BRAID_REFUSE("gemm_tc2: cuTensorMapEncodeTiled failed with %d for the output (inner=%lld rows=%lld ld=%lld)", (int)r, inner, rows, ld);
+    return BRAID_OK;
+}
+
+template <int MODE, bool TMA_OUT>
+static int launch_tc2(const CUtensorMap& mw, const CUtensorMap& mx, const CUtensorMap& mo, const GemmTc2Args& a, int pairs, cudaStream_t s) {
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc2_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, T2_SMEM_BYTES);
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc2_kernel<MODE, TMA_OUT>, cudaFuncAttributeMaxDynamicSharedMemorySize, T2_SMEM_BYTES);
         if (e != cudaSuccess) { braid_set_error("gemm_tc2: cannot reserve %d bytes of shared memory: %s", T2_SMEM_BYTES, cudaGetErrorString(e)); return (int)e; }
         configured = true;
     }
@@ -327,15 +419,17 @@ static int launch_tc2(const CUtensorMap& mw, const CUtensorMap& mx, const GemmTc
     attr[1].val.programmaticStreamSerializationAllowed = braid_pdl_enabled();
     cfg.attrs = attr;
     cfg.numAttrs = 2;
-    cudaLaunchKernelEx(&cfg, gemm_tc2_kernel<MODE>, mw, mx, a);
+    cudaLaunchKernelEx(&cfg, gemm_tc2_kernel<MODE, TMA_OUT>, mw, mx, mo, a);
     BRAID_LAUNCH_CHECK();
 }
 
 // As braid_gemm_tc with whole tiles (mode 0 store, 1 float32 residual sum, 2 SwiGLU over interleaved
-// gate/up rows), for prompts: tiles of 256 weight rows x 256 tokens on pairs of SMs.
+// gate/up rows), for prompts: tiles of 256 weight rows x 256 tokens on pairs of SMs.  The output leaves
+// through TMA where it can be addressed so (16-byte aligned base and row stride; the residual sum in
+// place; SwiGLU in bfloat16) unless `direct_out` is set; otherwise each thread stores its own elements.
 extern "C" int braid_gemm_tc2(const void* x, const void* w, void* out, const float* res, int out_dtype, int mode,
                               int n_rows, int m_out, int k_in, long long ldx, long long ldw, long long ldo,
-                              int* error_flag, void* stream) {
+                              int direct_out, int* error_flag, void* stream) {
     if (n_rows <= 0 || m_out <= 0) return BRAID_OK;
     if (mode < 0 || mode > 2) BRAID_REFUSE("gemm_tc2: unknown epilogue %d", mode);
     if (k_in <= 0) BRAID_REFUSE("gemm_tc2: k=%d must be positive", k_in);
@@ -345,11 +439,21 @@ extern "C" int braid_gemm_tc2(const void* x, const void* w, void* out, const flo
     if (out_dtype != BRAID_F32 && out_dtype != BRAID_BF16) BRAID_REFUSE("gemm_tc2: unknown out dtype code %d", out_dtype);
     if (!error_flag) BRAID_REFUSE("gemm_tc2: error_flag is required");
     const int w_rows = (mode == 2) ? 2 * ((m_out + 15) / 16) * 16 : m_out;
-    CUtensorMap mw, mx;
+    CUtensorMap mw, mx, mo;
     int rc = make_map2(&mw, w, w_rows, k_in, ldw);
     if (rc) return rc;
     rc = make_map2(&mx, x, n_rows, k_in, ldx);
     if (rc) return rc;
+    const int esize = out_dtype == BRAID_F32 ? 4 : 2;
+    bool tma_out = !direct_out && ((uintptr_t)out & 15) == 0 && (ldo * esize) % 16 == 0 && ldo >= m_out;
+    if (mode == 1 && (const void*)res != (const void*)out) tma_out = false;       // the reduce-add sums into what is there
+    if (mode == 2 && out_dtype != BRAID_BF16) tma_out = false;
+    if (tma_out) {
+        rc = make_map_out(&mo, out, out_dtype, m_out, n_rows, ldo, mode == 2 ? T2_BLOCK_M / 2 : T2_BLOCK_M);
+        if (rc) return rc;
+    } else {
+        mo = mx;                                   // never read
+    }
     const int m_tiles = (w_rows + 2 * T2_BLOCK_M - 1) / (2 * T2_BLOCK_M);
     const int n_tiles = (n_rows + T2_BLOCK_N - 1) / T2_BLOCK_N;
     int dev = 0, sms = 0;
@@ -359,7 +463,12 @@ extern "C" int braid_gemm_tc2(const void* x, const void* w, void* out, const flo
     const int pairs = (int)(units < sms / 2 ? units : sms / 2);
     GemmTc2Args a{out, res, n_rows, m_out, k_in, ldo, out_dtype, m_tiles, n_tiles, error_flag};
     cudaStream_t s = (cudaStream_t)stream;
-    if (mode == 0) return launch_tc2<0>(mw, mx, a, pairs, s);
-    if (mode == 1) return launch_tc2<1>(mw, mx, a, pairs, s);
-    return launch_tc2<2>(mw, mx, a, pairs, s);
+    if (tma_out) {
+        if (mode == 0) return launch_tc2<0, true>(mw, mx, mo, a, pairs, s);
+        if (mode == 1) return launch_tc2<1, true>(mw, mx, mo, a, pairs, s);
+        return launch_tc2<2, true>(mw, mx, mo, a, pairs, s);
+    }
+    if (mode == 0) return launch_tc2<0, false>(mw, mx, mo, a, pairs, s);
+    if (mode == 1) return launch_tc2<1, false>(mw, mx, mo, a, pairs, s);
+    return launch_tc2<2, false>(mw, mx, mo, a, pairs, s);
 }

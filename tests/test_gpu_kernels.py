@@ -433,29 +433,34 @@ def test_tensor_core_swiglu_epilogue(K, n, inter, k, sk):
 
 
 @pytest.mark.parametrize("n, m, k", [(129, 136, 64), (300, 1000, 520), (700, 20000, 200), (2500, 400, 192),
-                                     (4300, 136, 72), (256, 256, 4104)])
-def test_product_on_pairs_of_sms(K, n, m, k):
+                                     (4300, 136, 72), (256, 256, 4104), (300, 331, 520), (513, 778, 128)])
+@pytest.mark.parametrize("direct_out", [False, True])
+def test_product_on_pairs_of_sms(K, n, m, k, direct_out):
     """Tiles of 256 x 256 on two SMs each (more tiles than pairs at 20,000 rows; ragged edges in all three
-    sizes): float64 beside it, and the bits of the one-SM kernel with the same token tile, in all three epilogues."""
+    sizes): float64 beside it, and the bits of the one-SM kernel with the same token tile, in all three
+    epilogues, with the output leaving through TMA and thread by thread (331 and 389 bfloat16 outputs a row
+    cannot be addressed by TMA: those go thread by thread whatever is asked)."""
+    import functools
+    pair_product = functools.partial(K.gemm_tc_pair, direct_out=direct_out)
     from braidinfer_b200.csrc.api import interleave_gate_up
     x, w = rnd(n, k, dtype=torch.bfloat16, scale=0.5), rnd(m, k, dtype=torch.bfloat16, scale=0.5, seed=1)
     ref = x.double() @ w.double().t()
     scale = max(1.0, ref.abs().max().item())
     for dtype, tol in ((torch.float32, 1e-5 * scale), (torch.bfloat16, scale / 128)):
         pair, single = (torch.full((n, m), 9.0, device=DEV, dtype=dtype) for _ in range(2))
-        K.gemm_tc_pair(x, w, pair)
+        pair_product(x, w, pair)
         K.gemm_tc(x, w, single, block_n=256)
         assert (pair.double() - ref).abs().max() < tol
         assert torch.equal(pair, single)
     res = rnd(n, m, seed=2)
     res1 = res.clone()
-    K.gemm_tc_pair(x, w, res, residual=res)
+    pair_product(x, w, res, residual=res)
     K.gemm_tc(x, w, res1, residual=res1, block_n=256)
     assert torch.equal(res, res1)
     inter = m // 2
     wi = interleave_gate_up(w[:inter], w[inter:2 * inter])
     pair, single = (torch.full((n, inter), 9.0, device=DEV, dtype=torch.bfloat16) for _ in range(2))
-    K.gemm_tc_pair(x, wi, pair, swiglu=True)
+    pair_product(x, wi, pair, swiglu=True)
     K.gemm_tc(x, wi, single, swiglu=True, block_n=256)
     g, u = ref[:, :inter], ref[:, inter:2 * inter]
     want = g / (1 + torch.exp(-g)) * u
