@@ -59,34 +59,11 @@ def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
 PAIR_TOKEN_TILE = 256        # the token tile of the kernel that runs on pairs of SMs
 
 
-class RowScale:
-    """A row scale still to be applied: the RMSNorm of a tensor whose rows were left unscaled.
-    `shares` [tiles, stride >= rows] float32 holds each row's sum of squares in `tiles` shares (one per
-    128 columns of the normalised tensor, as the product that wrote it left them); the scale of row n is
-    rsqrt(sum over shares[:, n] / width + eps).  Whoever multiplies the unscaled rows by a matrix applies
-    the scale to its results instead (`in_scale` of the tensor-core products)."""
-
-    def __init__(self, shares: torch.Tensor, width: int, eps: float) -> None:
-        self.shares, self.width, self.eps = shares, int(width), float(eps)
-
-    def args(self):
-        return (self.shares.data_ptr(), self.shares.shape[0], self.shares.stride(0), float(self.width), self.eps)
-
-    def values(self) -> torch.Tensor:
-        """The scales themselves (for tests and for parts written in torch)."""
-        return torch.rsqrt(self.shares.sum(0) / self.width + self.eps)
-
-
-_NO_SCALE = (None, 0, 0, 0.0, 0.0)
-
-
 class PartialProduct:
     """Partial products of a stream-k GEMM waiting in the workspace to be added up."""
 
-    def __init__(self, workspace: torch.Tensor, plan, n_rows: int, w_rows: int,
-                 in_scale: Optional["RowScale"] = None) -> None:
+    def __init__(self, workspace: torch.Tensor, plan, n_rows: int, w_rows: int) -> None:
         self.workspace, self.plan, self.n_rows, self.w_rows = workspace, plan, n_rows, w_rows
-        self.in_scale = in_scale      # a row scale of the product's input that the adding-up has to apply
 
 
 class Kernels:
@@ -106,9 +83,6 @@ class Kernels:
         self._declare()
         self._error_flag = torch.zeros(8, dtype=torch.int32, device="cuda")
         self._tc_workspace: Optional[torch.Tensor] = None
-        # one counter per output tile of a product that finishes its own stream-k sums; the kernel
-        # leaves them zero
-        self._tile_counters = torch.zeros(1 << 16, dtype=torch.int32, device="cuda")
         self._attn_libs = {}
         self.pending_partial = None     # the open PartialProduct, if any (it owns the GEMM workspace)
         self.workspace_generation = 0   # grows when a scratch buffer moves (captured graphs are stale then)
@@ -134,21 +108,16 @@ class Kernels:
                                         c_float, c_void_p, c_void_p]
         L.braid_gemm_simt.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                                       c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_void_p]
-        scale = [c_void_p, c_int, c_longlong, c_float, c_float]        # RowScale.args()
         L.braid_gemm_tc.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int,
                                     c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_int, c_int,
-                                    c_void_p] + scale + [c_void_p, c_void_p]
-        L.braid_gemm_tc_finish.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_int,
-                                           c_int, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong,
-                                           c_int] + scale + [c_void_p, c_int, c_void_p, c_longlong, c_void_p,
-                                                             c_longlong, c_void_p, c_void_p]
+                                    c_void_p, c_void_p, c_void_p]
         L.braid_gemm_tc2.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                      c_longlong, c_longlong, c_longlong, c_int, c_void_p, c_void_p]
         L.braid_streamk_reduce.argtypes = [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_longlong,
                                            c_int, c_int, c_void_p]
         L.braid_streamk_reduce_norm.argtypes = [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int,
                                                 c_void_p, c_int, c_int, c_float, c_void_p]
-        L.braid_streamk_reduce_rope_kv.argtypes = [c_void_p] * 8 + [c_int] * 9 + scale + [c_void_p, c_void_p]
+        L.braid_streamk_reduce_rope_kv.argtypes = [c_void_p] * 8 + [c_int] * 9 + [c_void_p, c_void_p]
         L.braid_gemm_tc_workspace_bytes.argtypes = [c_int, c_int, c_int, c_int]
         L.braid_gemm_tc_workspace_bytes.restype = c_longlong
         L.braid_argmax.argtypes = [c_void_p, c_longlong, c_void_p, c_int, c_int, c_void_p, c_void_p]
@@ -156,7 +125,7 @@ class Kernels:
                                   [c_void_p, c_void_p]
         for name in ("braid_embed", "braid_rmsnorm", "braid_silu_mul", "braid_residual_add",
                      "braid_rope_kv_write", "braid_cast", "braid_attn_simple", "braid_gemm_simt",
-                     "braid_gemm_tc", "braid_gemm_tc2", "braid_gemm_tc_finish", "braid_argmax", "braid_sample", "braid_streamk_reduce",
+                     "braid_gemm_tc", "braid_gemm_tc2", "braid_argmax", "braid_sample", "braid_streamk_reduce",
                      "braid_streamk_reduce_norm", "braid_streamk_reduce_rope_kv"):
             getattr(L, name).restype = c_int
 
@@ -176,7 +145,6 @@ class Kernels:
         flags = self._error_flag.tolist()
         if any(flags):
             self._error_flag.zero_()
-            self._tile_counters.zero_()          # a kernel that gave up may have left some counted
             names = ["cache write outside the sequence's pages", "tensor-core GEMM wait ran out",
                      "NaN among the logits",
                      "tcgen05 attention gave up (a wait ran out, a visible position had no page, or its shared "
@@ -362,17 +330,14 @@ class Kernels:
         return self.tc_workspace(need)
 
     def gemm_tc(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, residual: Optional[torch.Tensor] = None,
-                swiglu: bool = False, block_n: int = 0, stream_k: bool = False,
-                in_scale: Optional[RowScale] = None) -> None:
+                swiglu: bool = False, block_n: int = 0, stream_k: bool = False) -> None:
         """bfloat16 x [n, k] times w [m, k]^T on the tensor cores.  With `swiglu`, w holds
         gate and up rows interleaved in blocks of 16 (`interleave_gate_up`) and out is [n, I].  `stream_k` spreads the weight stream
         evenly over all SMs whatever the shape (for up to a few hundred tokens) and adds a reduce kernel.
         Whole tiles of more than 128 tokens run on pairs of SMs (`gemm_tc_pair`: faster at every
         measured size, and bit for bit the same result) unless `block_n` names a token tile."""
         n, k = x.shape
-        if stream_k and in_scale is not None:
-            return self.gemm_tc_finish(x, w, out, residual=residual, swiglu=swiglu, block_n=block_n, in_scale=in_scale)
-        if not stream_k and block_n == 0 and token_tile(n) == PAIR_TOKEN_TILE and in_scale is None:
+        if not stream_k and block_n == 0 and token_tile(n) == PAIR_TOKEN_TILE:
             return self.gemm_tc_pair(x, w, out, residual=residual, swiglu=swiglu)
         w_rows = w.shape[0]
         m = out.shape[1] if swiglu else w_rows
@@ -393,53 +358,7 @@ class Kernels:
                                            ws.numel() * 4 if ws is not None else 0,
                                            dtype_code(out.dtype), mode, n, m, k, x.stride(0), w.stride(0),
                                            out.stride(0), block_n, int(stream_k), None,
-                                           *(in_scale.args() if in_scale is not None else _NO_SCALE),
                                            self._error_flag.data_ptr() + 4, self._stream()), "gemm_tc")
-
-    def gemm_tc_finish(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, residual: Optional[torch.Tensor] = None,
-                       swiglu: bool = False, block_n: int = 0, in_scale: Optional[RowScale] = None,
-                       norm_weight: Optional[torch.Tensor] = None, norm_eps: float = 0.0,
-                       scaled_out: Optional[torch.Tensor] = None) -> Optional[RowScale]:
-        """The stream-k product whose partial sums are added up inside the kernel, by whichever CTA is
-        last to deliver its part of a tile: no kernel between this product and the next.  Epilogues as
-        `gemm_tc`.  With `norm_weight` (and `residual`, float32 `out`): also what the RMSNorm that
-        follows needs, `scaled_out` = bfloat16(out * norm_weight) and the returned RowScale, so that the
-        norm costs no kernel either: the product that reads `scaled_out` takes the RowScale as `in_scale`."""
-        n, k = x.shape
-        w_rows = w.shape[0]
-        m = out.shape[1] if swiglu else w_rows
-        if swiglu and w_rows != 2 * (-(-m // 16) * 16):
-            raise KernelError(f"the SwiGLU epilogue wants {2 * (-(-m // 16) * 16)} interleaved weight rows for "
-                              f"{m} outputs, got {w_rows} (see interleave_gate_up)")
-        if self.pending_partial is not None:
-            raise KernelError("a deferred sum still lives in the GEMM workspace; resolve it before the next "
-                              "stream-k product")
-        block_n = block_n or token_tile(n)
-        ws = self._stream_k_workspace(n, w_rows, k, block_n)
-        tiles = -(-w_rows // 128) * -(-n // block_n)
-        if tiles > self._tile_counters.numel():
-            self._tile_counters = torch.zeros(2 * tiles, dtype=torch.int32, device="cuda")
-            self.workspace_generation += 1
-        finish = 2 if swiglu else (1 if residual is not None else 0)
-        scale_out = None
-        gamma = hb = shares = None
-        if norm_weight is not None:
-            if residual is None or swiglu or scaled_out is None:
-                raise KernelError("the norm's inputs come with the residual epilogue and need scaled_out")
-            finish = 3
-            gamma, hb = norm_weight, scaled_out
-            shares = torch.empty((-(-w_rows // 128), -(-n // 4) * 4), dtype=torch.float32, device=x.device)
-            scale_out = RowScale(shares, m, norm_eps)
-        self.launches += 1
-        self._check(self.lib.braid_gemm_tc_finish(
-            x.data_ptr(), w.data_ptr(), out.data_ptr(), _ptr(residual), ws.data_ptr(), ws.numel() * 4,
-            self._tile_counters.data_ptr(), self._tile_counters.numel(), dtype_code(out.dtype), finish, n, m, k,
-            x.stride(0), w.stride(0), out.stride(0), block_n,
-            *(in_scale.args() if in_scale is not None else _NO_SCALE),
-            _ptr(gamma), dtype_code(gamma.dtype) if gamma is not None else 0, _ptr(hb),
-            hb.stride(0) if hb is not None else 0, _ptr(shares), shares.stride(0) if shares is not None else 0,
-            self._error_flag.data_ptr() + 4, self._stream()), "gemm_tc_finish")
-        return scale_out
 
     def gemm_tc_pair(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor,
                      residual: Optional[torch.Tensor] = None, swiglu: bool = False, direct_out: bool = False) -> None:
@@ -461,7 +380,7 @@ class Kernels:
                                             self._stream()),
                     "gemm_tc_pair")
 
-    def gemm_tc_partial(self, x: torch.Tensor, w: torch.Tensor, in_scale: Optional[RowScale] = None) -> "PartialProduct":
+    def gemm_tc_partial(self, x: torch.Tensor, w: torch.Tensor) -> "PartialProduct":
         """The stream-k product without its reduce: the partial products stay in the
         workspace, and the returned handle lets one of the `streamk_reduce*` calls add
         them up together with what follows.  Only one such handle may be open at a time."""
@@ -475,9 +394,8 @@ class Kernels:
         self.launches += 1
         self._check(self.lib.braid_gemm_tc(x.data_ptr(), w.data_ptr(), None, None, ws.data_ptr(), ws.numel() * 4,
                                            F32, 0, n, w_rows, k, x.stride(0), w.stride(0), 0, block_n, 1, plan,
-                                           *_NO_SCALE,      # the scale is applied by whoever adds up
                                            self._error_flag.data_ptr() + 4, self._stream()), "gemm_tc_partial")
-        p = PartialProduct(ws, plan, n, w_rows, in_scale)
+        p = PartialProduct(ws, plan, n, w_rows)
         self.pending_partial = p
         return p
 
@@ -490,8 +408,6 @@ class Kernels:
                        swiglu: bool = False) -> None:
         m = out.shape[1] if swiglu else p.w_rows
         mode = 2 if swiglu else (1 if residual is not None else 0)
-        if p.in_scale is not None:
-            raise KernelError("this partial product carries a row scale, which the plain adding-up does not apply")
         self._close_partial(p)
         self.launches += 1
         self._check(self.lib.braid_streamk_reduce(p.workspace.data_ptr(), p.plan, p.n_rows, out.data_ptr(), _ptr(residual),
@@ -503,8 +419,6 @@ class Kernels:
         """h += sum of the partial products (written back unless rows are gathered), then
         out = RMSNorm(h) * w, in one kernel."""
         rows_out, width = out.shape
-        if p.in_scale is not None:
-            raise KernelError("this partial product carries a row scale, which reduce + norm does not apply")
         self._close_partial(p)
         self.launches += 1
         self._check(self.lib.braid_streamk_reduce_norm(p.workspace.data_ptr(), p.plan, p.n_rows, h.data_ptr(), w.data_ptr(),
@@ -524,8 +438,7 @@ class Kernels:
         self._check(self.lib.braid_streamk_reduce_rope_kv(
             p.workspace.data_ptr(), p.plan, qkv.data_ptr(), inv_freq.data_ptr(), positions.data_ptr(),
             token_seq.data_ptr(), _ptr(page_table), _ptr(cache), qkv.shape[0], nqh, nkh, hd, rope_dim, int(adjacent),
-            page_size, cols, num_pages, *(p.in_scale.args() if p.in_scale is not None else _NO_SCALE),
-            self._error_flag.data_ptr(), self._stream()), "streamk_reduce_rope_kv")
+            page_size, cols, num_pages, self._error_flag.data_ptr(), self._stream()), "streamk_reduce_rope_kv")
 
     @staticmethod
     def gemm_tc_eligible(x: torch.Tensor, w: torch.Tensor) -> bool:

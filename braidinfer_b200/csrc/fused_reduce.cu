@@ -156,27 +156,7 @@ struct ReduceRopeArgs {
     int rows, nqh, nkh, hd, rope_dim, adjacent;
     int page_size, table_cols, num_pages;
     int* error_flag;
-    // a row scale still to be applied to the product (the RMSNorm of its input, see gemm_tc.cu), or null
-    const float* ss_in;          // [ss_in_tiles][ss_in_stride] shares of each row's sum of squares
-    int ss_in_tiles;
-    long long ss_in_stride;
-    float ss_in_width, ss_in_eps;
 };
-
-// rsqrt(mean square + eps) of the row from its shares, 1 without a scale.  The loads are independent of
-// the partial sums asked for next, so their trips overlap.
-__device__ __forceinline__ float reduce_rope_row_scale(const ReduceRopeArgs& a, int row) {
-    if (!a.ss_in) return 1.f;
-    float ss = 0.f;
-    for (int t0 = 0; t0 < a.ss_in_tiles; t0 += 8) {
-        float p[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) p[i] = (t0 + i < a.ss_in_tiles) ? __ldcg(a.ss_in + (size_t)(t0 + i) * a.ss_in_stride + row) : 0.f;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) ss += p[i];
-    }
-    return rsqrtf(ss / a.ss_in_width + a.ss_in_eps);
-}
 
 __global__ void streamk_reduce_rope_kv_kernel(ReduceRopeArgs a) {
     pdl_trigger();
@@ -216,7 +196,6 @@ __global__ void streamk_reduce_rope_kv_kernel(ReduceRopeArgs a) {
             sp1 = streamk_span(a.k, row, col0 + (a.adjacent ? 2 * p_first + 1 : p_first + half));
         }
         pdl_wait();
-        const float rs = reduce_rope_row_scale(a, row);
         for (int p = threadIdx.x; p < half; p += blockDim.x) {
             const int i0 = a.adjacent ? 2 * p : p;
             const int i1 = a.adjacent ? 2 * p + 1 : p + half;
@@ -230,8 +209,8 @@ __global__ void streamk_reduce_rope_kv_kernel(ReduceRopeArgs a) {
             // the product is rounded to bfloat16 before it is rotated, as after a plain product
             float f0, f1;
             streamk_sum_pair(a.k, s0, s1, row, col0 + i0, col0 + i1, f0, f1);
-            const float x0 = __bfloat162float(__float2bfloat16_rn(f0 * rs));
-            const float x1 = __bfloat162float(__float2bfloat16_rn(f1 * rs));
+            const float x0 = __bfloat162float(__float2bfloat16_rn(f0));
+            const float x1 = __bfloat162float(__float2bfloat16_rn(f1));
             const __nv_bfloat16 y0 = __float2bfloat16_rn(x0 * cs - x1 * sn);
             const __nv_bfloat16 y1 = __float2bfloat16_rn(x0 * sn + x1 * cs);
             dst_row[i0] = y0;
@@ -239,7 +218,7 @@ __global__ void streamk_reduce_rope_kv_kernel(ReduceRopeArgs a) {
             if (dst) { dst[i0] = y0; dst[i1] = y1; }
         }
         for (int i = a.rope_dim + threadIdx.x; i < a.hd; i += blockDim.x) {
-            const __nv_bfloat16 y = __float2bfloat16_rn(streamk_sum(a.k, streamk_span(a.k, row, col0 + i), row, col0 + i) * rs);
+            const __nv_bfloat16 y = __float2bfloat16_rn(streamk_sum(a.k, streamk_span(a.k, row, col0 + i), row, col0 + i));
             dst_row[i] = y;
             if (dst) dst[i] = y;
         }
@@ -248,18 +227,17 @@ __global__ void streamk_reduce_rope_kv_kernel(ReduceRopeArgs a) {
         StreamKSpan sp0 = {};
         if (i_first < a.hd) sp0 = streamk_span(a.k, row, col0 + i_first);
         pdl_wait();
-        const float rs = reduce_rope_row_scale(a, row);
         for (int i = threadIdx.x; i < a.hd; i += 2 * blockDim.x) {
             const StreamKSpan s0 = (i == i_first) ? sp0 : streamk_span(a.k, row, col0 + i);
             const int i2 = i + blockDim.x;                  // a thread's elements go two at a time
             if (i2 < a.hd) {
                 float f0, f1;
                 streamk_sum_pair(a.k, s0, streamk_span(a.k, row, col0 + i2), row, col0 + i, col0 + i2, f0, f1);
-                const __nv_bfloat16 y0 = __float2bfloat16_rn(f0 * rs), y1 = __float2bfloat16_rn(f1 * rs);
+                const __nv_bfloat16 y0 = __float2bfloat16_rn(f0), y1 = __float2bfloat16_rn(f1);
                 dst_row[i] = y0; dst_row[i2] = y1;
                 if (dst) { dst[i] = y0; dst[i2] = y1; }
             } else {
-                const __nv_bfloat16 y = __float2bfloat16_rn(streamk_sum(a.k, s0, row, col0 + i) * rs);
+                const __nv_bfloat16 y = __float2bfloat16_rn(streamk_sum(a.k, s0, row, col0 + i));
                 dst_row[i] = y;
                 if (dst) dst[i] = y;
             }
@@ -270,19 +248,14 @@ __global__ void streamk_reduce_rope_kv_kernel(ReduceRopeArgs a) {
 extern "C" int braid_streamk_reduce_rope_kv(const float* partial, const int* plan, void* qkv, const float* inv_freq,
                                             const int* positions, const int* token_seq, const int* page_table,
                                             void* cache, int rows, int nqh, int nkh, int hd, int rope_dim, int adjacent,
-                                            int page_size, int table_cols, int num_pages, const float* ss_in,
-                                            int ss_in_tiles, long long ss_in_stride, float ss_in_width, float ss_in_eps,
-                                            int* error_flag, void* stream) {
+                                            int page_size, int table_cols, int num_pages, int* error_flag, void* stream) {
     if (rows <= 0) return BRAID_OK;
     if (nqh <= 0 || nkh <= 0 || hd <= 0) BRAID_REFUSE("reduce_rope_kv: heads/head_dim must be positive");
     if (rope_dim < 0 || rope_dim > hd || (rope_dim & 1)) BRAID_REFUSE("reduce_rope_kv: rope_dim=%d must be even and <= head_dim=%d", rope_dim, hd);
     if (nqh + 2 * nkh > 65535) BRAID_REFUSE("reduce_rope_kv: %d heads exceed the grid limit", nqh + 2 * nkh);
-    if (ss_in && (ss_in_tiles <= 0 || ss_in_stride < rows || !(ss_in_width > 0.f)))
-        BRAID_REFUSE("reduce_rope_kv: row scale of %d shares, stride %lld, width %g for %d rows", ss_in_tiles, ss_in_stride, (double)ss_in_width, rows);
     ReduceRopeArgs a{streamk_from_plan(partial, plan, rows),
                      (__nv_bfloat16*)qkv, inv_freq, positions, token_seq, page_table, (__nv_bfloat16*)cache,
-                     rows, nqh, nkh, hd, rope_dim, adjacent, page_size, table_cols, num_pages, error_flag,
-                     ss_in, ss_in_tiles, ss_in_stride, ss_in_width, ss_in_eps};
+                     rows, nqh, nkh, hd, rope_dim, adjacent, page_size, table_cols, num_pages, error_flag};
     braid_launch(streamk_reduce_rope_kv_kernel, dim3(rows, nqh + 2 * nkh), dim3(hd >= 128 ? 64 : 32), 0, (cudaStream_t)stream, a);
     BRAID_LAUNCH_CHECK();
 }

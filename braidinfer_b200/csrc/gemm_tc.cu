@@ -20,18 +20,7 @@
 //                    epilogue warp holds 16 outputs' gate (lanes 0..15) and up (lanes
 //                    16..31) and pairs them with a shuffle; out = silu(gate) * up,
 //                 3  float32 partial sums of a run of k blocks ("stream-k"), added up
-//                    by a reduce kernel with one of the epilogues above,
-//                 4  the same partial sums, finished in this kernel: the CTA that is last to
-//                    deliver its part of a tile (a counter per tile tells it) adds the tile's
-//                    parts up in ascending CTA order and runs the epilogue (`finish`): store,
-//                    residual sum, SwiGLU, or residual sum plus what the next RMSNorm needs
-//                    (the new residual times the norm's weights in bfloat16, and the tile's
-//                    share of each token's sum of squares).  Nobody waits for anybody, and a
-//                    step needs no kernel between two products.
-//               The tokens may come with a row scale still to be applied (`ss_in`: per-token sums
-//               of squares in shares, from finish 3 of the product before): modes 0, 2 and 4
-//               multiply each token's results by rsqrt(sum / width + eps), which completes the
-//               RMSNorm of that product's output.
+//                    by a reduce kernel with one of the epilogues above.
 //
 // The kernel is persistent: one CTA per SM walks its share of the work units (output tile
 // x slice of k).  The loader runs ahead across units, and with two accumulator buffers
@@ -68,22 +57,6 @@ struct GemmTcArgs {
     int max_segs;              // mode 3: partial slots per CTA
     int* error_flag;
     int tile_begin, tile_end;  // the tiles of the walk (tc_tile_coords) that this launch covers
-    // mode 4: `out`, `res`, `m_out`, `ldo`, `out_dtype` describe the finished output as in modes 0-2
-    float* partial;            // [slot][BLOCK_N][128] float32
-    int* counters;             // one per tile of the line, zero between launches
-    int finish;                // 0 store, 1 res + sum, 2 SwiGLU, 3 res + sum and the next norm's inputs
-    // the row scale of the tokens (modes 0, 2, 4), or null
-    const float* ss_in;        // [ss_in_tiles][ss_in_stride]: shares of each token's sum of squares
-    int ss_in_tiles;
-    long long ss_in_stride;
-    float ss_in_width, ss_in_eps;
-    // finish 3
-    const void* gamma;         // [m_out] weights of the norm that follows
-    int gamma_dtype;
-    __nv_bfloat16* hb;         // [n, ldhb]: bf16(new residual * gamma)
-    long long ldhb;
-    float* ss_out;             // [m_tiles][ss_out_stride]
-    long long ss_out_stride;
 };
 
 template <int BLOCK_N, int MODE>
@@ -116,7 +89,7 @@ struct TcCfg {
 // count); it writes the float32 partial product of its j-th segment to slot
 // blockIdx.x * max_segs + j, and a reduce kernel adds the slots of a tile
 // in ascending CTA order.  Every CTA streams the same number of bytes whatever the shape.
-struct TcUnit { int m0, n0, slot, kb_begin, num_kb, tile, mt; };   // tile: index in the line (mode 3, 4)
+struct TcUnit { int m0, n0, slot, kb_begin, num_kb; };
 
 template <int BLOCK_N, int MODE>
 struct TcWalk {
@@ -126,7 +99,7 @@ struct TcWalk {
     int u, seg;
     __device__ TcWalk(const GemmTcArgs& a_) : a(a_) {
         total_kb = (a.k_in + TC_BLOCK_K - 1) / TC_BLOCK_K;
-        if (MODE >= 3) {
+        if (MODE == 3) {
             const long long w = (long long)(a.tile_end - a.tile_begin) * total_kb;
             idx = (long long)blockIdx.x * w / gridDim.x;
             hi = (long long)(blockIdx.x + 1) * w / gridDim.x;
@@ -138,11 +111,10 @@ struct TcWalk {
     }
     __device__ bool next(TcUnit& t) {
         int tile;
-        if (MODE >= 3) {
+        if (MODE == 3) {
             if (idx >= hi) return false;
             const int in_line = (int)(idx / total_kb);
             tile = a.tile_begin + in_line;
-            t.tile = in_line;
             t.kb_begin = (int)(idx - (long long)in_line * total_kb);
             t.num_kb = (int)min((long long)(total_kb - t.kb_begin), hi - idx);
             t.slot = blockIdx.x * a.max_segs + seg;
@@ -154,126 +126,15 @@ struct TcWalk {
             t.kb_begin = 0;
             t.num_kb = total_kb;
             t.slot = 0;
-            t.tile = u - a.tile_begin;
             u += gridDim.x;
         }
         int mt, nt;
         tc_tile_coords(tile, a.m_tiles, a.n_tiles, mt, nt);
         t.m0 = mt * TC_BLOCK_M;
         t.n0 = nt * BLOCK_N;
-        t.mt = mt;
         return true;
     }
 };
-
-// ------------------------------------------------------------------ the epilogues of mode 4
-__device__ __forceinline__ float gamma_at(const GemmTcArgs& a, int m) {
-    return a.gamma_dtype == BRAID_F32 ? ((const float*)a.gamma)[m] : __bfloat162float(((const __nv_bfloat16*)a.gamma)[m]);
-}
-
-// CH results of one weight row (`v`, tokens n0c .. n0c + CH - 1 of row quarter * 32 + lane of the tile at m0)
-// to their place, by a.finish.  Called by all 128 epilogue threads together (finish 3 meets at barriers).
-template <int CH>
-__device__ __forceinline__ void finish_chunk(const GemmTcArgs& a, float (&v)[CH], int m0, int mt, int n0c, int quarter,
-                                             int lane, const float* rs, float (*ss_s)[32]) {
-    if (rs) {
-#pragma unroll
-        for (int i = 0; i < CH; ++i) v[i] *= rs[i];
-    }
-    if (a.finish == 2) {
-        // rows interleave gate and up in blocks of 16: the halves of a warp swap values (see mode 2)
-        const int m = (m0 + quarter * 32) / 2 + (lane & 15);
-        const bool is_up = (lane & 16) != 0;
-        const size_t o0 = (size_t)(n0c + (is_up ? 1 : 0)) * a.ldo + m;
-#pragma unroll
-        for (int p2 = 0; p2 < CH / 2; ++p2) {
-            const float from_up = __shfl_xor_sync(0xffffffffu, v[2 * p2], 16);
-            const float from_gate = __shfl_xor_sync(0xffffffffu, v[2 * p2 + 1], 16);
-            const float g = is_up ? from_gate : v[2 * p2];
-            const float u = is_up ? v[2 * p2 + 1] : from_up;
-            const float y = __fdividef(g, 1.f + __expf(-g)) * u;
-            const int n = n0c + 2 * p2 + (is_up ? 1 : 0);
-            if (m < a.m_out && n < a.n_rows) {
-                if (a.out_dtype == BRAID_F32) ((float*)a.out)[o0 + (size_t)(2 * p2) * a.ldo] = y;
-                else ((__nv_bfloat16*)a.out)[o0 + (size_t)(2 * p2) * a.ldo] = __float2bfloat16_rn(y);
-            }
-        }
-        return;
-    }
-    const int m = m0 + quarter * 32 + lane;
-    const bool row_ok = m < a.m_out;
-    const size_t o0 = (size_t)n0c * a.ldo + m;
-    if (a.finish == 0) {
-        if (row_ok) {
-#pragma unroll
-            for (int i = 0; i < CH; ++i) {
-                if (n0c + i >= a.n_rows) break;
-                if (a.out_dtype == BRAID_F32) ((float*)a.out)[o0 + (size_t)i * a.ldo] = v[i];
-                else ((__nv_bfloat16*)a.out)[o0 + (size_t)i * a.ldo] = __float2bfloat16_rn(v[i]);
-            }
-        }
-        return;
-    }
-    float old[CH];
-#pragma unroll
-    for (int i = 0; i < CH; ++i) old[i] = (row_ok && n0c + i < a.n_rows) ? __ldcg(a.res + o0 + (size_t)i * a.ldo) : 0.f;
-    if (a.finish == 1) {
-        if (row_ok) {
-#pragma unroll
-            for (int i = 0; i < CH; ++i)
-                if (n0c + i < a.n_rows) ((float*)a.out)[o0 + (size_t)i * a.ldo] = old[i] + v[i];
-        }
-        return;
-    }
-    // finish 3: the new residual, its product with the next norm's weights in bfloat16, and this tile's
-    // share of each token's sum of squares (rows past the width and tokens past the step add nothing)
-    const float gm = row_ok ? gamma_at(a, m) : 0.f;
-#pragma unroll
-    for (int i = 0; i < CH; ++i) {
-        const bool live = row_ok && n0c + i < a.n_rows;
-        const float hn = old[i] + v[i];
-        if (live) {
-            ((float*)a.out)[o0 + (size_t)i * a.ldo] = hn;
-            a.hb[(size_t)(n0c + i) * a.ldhb + m] = __float2bfloat16_rn(hn * gm);
-        }
-        float sq = live ? hn * hn : 0.f;
-#pragma unroll
-        for (int d = 16; d > 0; d >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, d);
-        if (lane == 0) ss_s[quarter][i] = sq;
-    }
-    epilogue_sync();
-    const int e = quarter * 32 + lane;
-    if (e < CH && n0c + e < a.n_rows)
-        a.ss_out[(size_t)mt * a.ss_out_stride + n0c + e] = ((ss_s[0][e] + ss_s[1][e]) + ss_s[2][e]) + ss_s[3][e];
-    epilogue_sync();                       // ss_s is free for the next chunk
-}
-
-// Columns [c0, c0 + CH) of row `row` of a tile, added up over the tile's slots in ascending CTA order.  The
-// slots are asked for a few at a time before any is added, so their trips to L2 overlap.
-template <int BLOCK_N, int CH>
-__device__ __forceinline__ void tile_chunk_sum(const StreamK& k, const StreamKSpan& sp, int c0, int row, float (&acc)[CH]) {
-    constexpr int BATCH = 64 / CH;
-    const size_t slot_elems = (size_t)BLOCK_N * STREAMK_TILE_M;
-    const float* base = k.partial + (size_t)c0 * STREAMK_TILE_M + row;
-#pragma unroll
-    for (int i = 0; i < CH; ++i) acc[i] = 0.f;
-    for (int c = sp.c_first; c <= sp.c_last; c += BATCH) {
-        float p[BATCH][CH];
-#pragma unroll
-        for (int b = 0; b < BATCH; ++b) {
-            const int cc = c + b;
-            const float* src = base + (cc == sp.c_first ? (size_t)sp.slot_first : (size_t)cc * k.max_segs) * slot_elems;
-#pragma unroll
-            for (int i = 0; i < CH; ++i) p[b][i] = (cc <= sp.c_last) ? __ldcg(src + (size_t)i * STREAMK_TILE_M) : 0.f;
-        }
-#pragma unroll
-        for (int b = 0; b < BATCH; ++b)
-            if (c + b <= sp.c_last) {
-#pragma unroll
-                for (int i = 0; i < CH; ++i) acc[i] += p[b][i];
-            }
-    }
-}
 
 template <int BLOCK_N, int MODE>
 __global__ void __launch_bounds__(TC_THREADS, 1)
@@ -288,10 +149,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     uint64_t* acc_empty = acc_full + 2;                    // [kAccBufs]
     uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
-
-    __shared__ float rs_s[BLOCK_N];            // row scale of the tile's tokens
-    __shared__ float ss_s[4][32];              // finish 3: a chunk's sums of squares, per epilogue warp
-    __shared__ int last_s;                     // mode 4: this CTA is the last to deliver its part of the tile
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 #ifdef BRAID_TRACE
@@ -404,107 +261,28 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     } else {
         // epilogue warps: warp w may read tensor-memory lanes 32 * (w % 4) ...
         const int quarter = warp & 3;
-        const int e = threadIdx.x - 64;           // 0..127 among the epilogue threads
         pdl_wait();
         int buf = 0;
         uint32_t full_phase = 0;                  // bit b: phase of accumulator buffer b
         bool ok = true;
         TcWalk<BLOCK_N, MODE> walk(a);
         TcUnit t;
-        // with a row scale, or in mode 4, the epilogue threads meet at barriers inside a unit: they then
-        // agree on whether a wait ran out, so that none of them waits at a barrier for one that left
-        const bool scaled = (MODE == 0 || MODE == 2 || MODE == 4) && a.ss_in != nullptr;
-        const bool meets = MODE == 4 || scaled;
-        int rs_n0 = -1;
-        StreamK sk = {};
-        if (MODE == 4)
-            sk = StreamK{a.partial, (int)gridDim.x, a.max_segs, walk.total_kb, a.n_tiles, a.n_rows, BLOCK_N,
-                         (long long)(a.tile_end - a.tile_begin) * walk.total_kb, a.m_tiles, a.tile_begin};
         while (ok && walk.next(t)) {
             // mode 2: every 32 weight rows are 16 gate rows then the 16 up rows of the same outputs,
             // so a warp's lanes 0..15 hold gate and lanes 16..31 hold up of outputs [m - lane % 16 ...]
             const int m = (MODE == 2) ? (t.m0 + quarter * 32) / 2 + (lane & 15) : t.m0 + quarter * 32 + lane;
-            if (scaled && t.n0 != rs_n0) {
-                // rsqrt(mean square + eps) of this tile's tokens, from the shares the product before left
-                epilogue_sync();                              // the last unit's readers are done
-                for (int j = e; j < BLOCK_N; j += 128) {
-                    const int n = t.n0 + j;
-                    float ss = 0.f;
-                    if (n < a.n_rows)
-                        for (int t0 = 0; t0 < a.ss_in_tiles; t0 += 8) {
-                            float p[8];
-#pragma unroll
-                            for (int i = 0; i < 8; ++i)
-                                p[i] = (t0 + i < a.ss_in_tiles) ? __ldcg(a.ss_in + (size_t)(t0 + i) * a.ss_in_stride + n) : 0.f;
-#pragma unroll
-                            for (int i = 0; i < 8; ++i) ss += p[i];
-                        }
-                    rs_s[j] = rsqrtf(ss / a.ss_in_width + a.ss_in_eps);
-                }
-                epilogue_sync();
-                rs_n0 = t.n0;
-            }
             ok = mbar_wait(&acc_full[buf], (full_phase >> buf) & 1u, abort_flag);
-            if (meets) ok = epilogue_all(ok);
             if (!ok) break;
             if (warp == 2 && lane == 0) BRAID_STAMP(trace_row, 5);
             tc_fence_after();
             const uint32_t trow = tmem_base + buf * Cfg::kAccCols + ((uint32_t)(quarter * 32) << 16);
             constexpr int CH = BLOCK_N >= 32 ? 32 : 16;       // columns per tensor-memory load and wait
-            if constexpr (MODE == 4) {
-                const bool whole = t.num_kb == walk.total_kb;          // no other CTA has a part of this tile
-                const StreamKSpan sp = streamk_span_of_tile(sk, t.tile);
-#pragma unroll 1
-                for (int c0 = 0; c0 < BLOCK_N; c0 += CH) {
-                    if (t.n0 + c0 >= a.n_rows) break;
-                    float v[CH];
-                    if (CH == 32) tmem_ld32(trow + c0, v);
-                    else tmem_ld16(trow + c0, v);
-                    if (whole) {
-                        finish_chunk<CH>(a, v, t.m0, t.mt, t.n0 + c0, quarter, lane, scaled ? rs_s + c0 : nullptr, ss_s);
-                    } else {
-                        float* dst = a.partial + ((size_t)t.slot * BLOCK_N + c0) * TC_BLOCK_M + quarter * 32 + lane;
-#pragma unroll
-                        for (int i = 0; i < CH; ++i)
-                            if (t.n0 + c0 + i < a.n_rows) dst[(size_t)i * TC_BLOCK_M] = v[i];
-                    }
-                }
-                tc_fence_before();
-                mbar_arrive(&acc_empty[buf]);                          // the products of the next unit may go on
-                full_phase ^= (1u << buf);
-                if (Cfg::kAccBufs == 2) buf ^= 1;
-                if (whole) continue;
-                // this CTA's part is delivered; the last to deliver finishes the tile
-                __threadfence();
-                epilogue_sync();
-                if (e == 0) {
-                    const int before = atomicAdd(a.counters + t.tile, 1);
-                    const int last = before == sp.c_last - sp.c_first;
-                    if (last) a.counters[t.tile] = 0;                 // as the next launch wants to find it
-                    last_s = last;
-                }
-                epilogue_sync();
-                if (!last_s) continue;
-                __threadfence();
-#pragma unroll 1
-                for (int c0 = 0; c0 < BLOCK_N; c0 += CH) {
-                    if (t.n0 + c0 >= a.n_rows) break;
-                    float v[CH];
-                    tile_chunk_sum<BLOCK_N, CH>(sk, sp, c0, quarter * 32 + lane, v);
-                    finish_chunk<CH>(a, v, t.m0, t.mt, t.n0 + c0, quarter, lane, scaled ? rs_s + c0 : nullptr, ss_s);
-                }
-                continue;
-            } else {
 #pragma unroll 1
             for (int c0 = 0; c0 < BLOCK_N; c0 += CH) {
                 if (t.n0 + c0 >= a.n_rows) break;
                 float v[CH];
                 if (CH == 32) tmem_ld32(trow + c0, v);
                 else tmem_ld16(trow + c0, v);
-                if (scaled) {
-#pragma unroll
-                    for (int i = 0; i < CH; ++i) v[i] *= rs_s[c0 + i];
-                }
                 if (MODE == 2) {
                     // The halves of a warp swap values; the gate half then finishes the even
                     // columns and the up half the odd ones, so all lanes compute and store.
@@ -563,7 +341,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             mbar_arrive(&acc_empty[buf]);
             full_phase ^= (1u << buf);
             if (Cfg::kAccBufs == 2) buf ^= 1;
-            }
         }
     }
     if (warp == 2 && lane == 0) BRAID_STAMP(trace_row, 6);
@@ -730,8 +507,7 @@ extern "C" long long braid_gemm_tc_workspace_bytes(int n_rows, int w_rows, int k
 extern "C" int braid_gemm_tc(const void* x, const void* w, void* out, const float* res, void* workspace,
                              long long workspace_bytes, int out_dtype, int mode, int n_rows, int m_out, int k_in,
                              long long ldx, long long ldw, long long ldo, int block_n, int stream_k,
-                             int* plan_out, const float* ss_in, int ss_in_tiles, long long ss_in_stride,
-                             float ss_in_width, float ss_in_eps, int* error_flag, void* stream) {
+                             int* plan_out, int* error_flag, void* stream) {
     if (n_rows <= 0 || m_out <= 0) return BRAID_OK;
     if (mode < 0 || mode > 2) BRAID_REFUSE("gemm_tc: unknown epilogue %d", mode);
     if (k_in <= 0) BRAID_REFUSE("gemm_tc: k=%d must be positive", k_in);
@@ -743,11 +519,6 @@ extern "C" int braid_gemm_tc(const void* x, const void* w, void* out, const floa
     const int w_rows = (mode == 2) ? 2 * ((m_out + 15) / 16) * 16 : m_out;
     if (!valid_block_n(block_n)) BRAID_REFUSE("gemm_tc: token tile %d is not one of 16, 32, 64, 128, 256", block_n);
     if (stream_k && !workspace) BRAID_REFUSE("gemm_tc: the stream-k form needs a workspace");
-    if (ss_in && mode == 1) BRAID_REFUSE("gemm_tc: the residual epilogue takes no row scale");
-    if (ss_in && stream_k && !plan_out)
-        BRAID_REFUSE("gemm_tc: a stream-k product with a row scale is finished in the kernel (braid_gemm_tc_finish)");
-    if (ss_in && (ss_in_tiles <= 0 || ss_in_stride < n_rows || !(ss_in_width > 0.f)))
-        BRAID_REFUSE("gemm_tc: row scale of %d shares, stride %lld, width %g for %d rows", ss_in_tiles, ss_in_stride, (double)ss_in_width, n_rows);
     if (stream_k) {
         // the partial sums of every CTA's segments must fit: checked here, on the host, for the very
         // plan the kernel will walk
@@ -772,8 +543,6 @@ extern "C" int braid_gemm_tc(const void* x, const void* w, void* out, const floa
     const int whole_end = stream_k ? p.tile_begin : all_tiles;       // tiles [0, whole_end) run as whole tiles
     if (whole_end > 0) {
         GemmTcArgs a{out, res, n_rows, m_out, k_in, ldo, out_dtype, m_tiles, n_tiles, 0, error_flag, 0, whole_end};
-        a.ss_in = ss_in; a.ss_in_tiles = ss_in_tiles; a.ss_in_stride = ss_in_stride;
-        a.ss_in_width = ss_in_width; a.ss_in_eps = ss_in_eps;
         dim3 grid((unsigned)(whole_end < sm_count() ? whole_end : sm_count()), 1, 1);
         if (mode == 0) rc = dispatch_tc<0>(block_n, mw, mx, a, grid, s);
         else if (mode == 1) rc = dispatch_tc<1>(block_n, mw, mx, a, grid, s);
@@ -782,7 +551,7 @@ extern "C" int braid_gemm_tc(const void* x, const void* w, void* out, const floa
     }
     if (!stream_k || p.tiles == 0) return BRAID_OK;
     GemmTcArgs a{workspace, nullptr, n_rows, w_rows, k_in, 0, BRAID_F32, p.m_tiles, p.n_tiles, p.max_segs, error_flag,
-                 p.tile_begin, p.tile_begin + p.tiles};          // the members after these are zero
+                 p.tile_begin, p.tile_begin + p.tiles};
     rc = dispatch_tc<3>(block_n, mw, mx, a, dim3(p.grid, 1, 1), s);
     if (rc) return rc;
     if (plan_out) {
@@ -793,53 +562,6 @@ extern "C" int braid_gemm_tc(const void* x, const void* w, void* out, const floa
     }
     StreamK k{(const float*)workspace, p.grid, p.max_segs, p.total_kb, p.n_tiles, n_rows, block_n, p.w, p.m_tiles, p.tile_begin};
     return launch_streamk_reduce(k, out, res, m_out, ldo, out_dtype, mode, s);
-}
-
-// The stream-k product finished inside the kernel (mode 4): no reduce kernel follows.  `finish`: 0 store,
-// 1 out = res + product (float32), 2 SwiGLU over interleaved gate/up rows, 3 out = res + product (float32),
-// hb = bfloat16(out * gamma) and ss_out[weight tile][token] = that tile's share of the token's sum of squares,
-// for the RMSNorm that follows: whoever reads hb multiplies by rsqrt(sum of the shares / width + eps).
-// `ss_in` (or null) is such a scale still to be applied to this product's tokens.  `counters`: at least one
-// int per output tile, zero on entry and zero again when the kernel has finished.
-extern "C" int braid_gemm_tc_finish(const void* x, const void* w, void* out, const float* res, void* workspace,
-                                    long long workspace_bytes, int* counters, int n_counters, int out_dtype, int finish,
-                                    int n_rows, int m_out, int k_in, long long ldx, long long ldw, long long ldo,
-                                    int block_n, const float* ss_in, int ss_in_tiles, long long ss_in_stride,
-                                    float ss_in_width, float ss_in_eps, const void* gamma, int gamma_dtype, void* hb,
-                                    long long ldhb, float* ss_out, long long ss_out_stride, int* error_flag, void* stream) {
-    if (n_rows <= 0 || m_out <= 0) return BRAID_OK;
-    if (finish < 0 || finish > 3) BRAID_REFUSE("gemm_tc_finish: unknown epilogue %d", finish);
-    if (k_in <= 0) BRAID_REFUSE("gemm_tc_finish: k=%d must be positive", k_in);
-    if ((ldx % 8) || (ldw % 8)) BRAID_REFUSE("gemm_tc_finish: row strides (%lld, %lld) must be multiples of 8 elements for TMA", ldx, ldw);
-    if (((uintptr_t)x & 15) || ((uintptr_t)w & 15)) BRAID_REFUSE("gemm_tc_finish: operands must be 16-byte aligned for TMA");
-    if ((finish == 1 || finish == 3) && (!res || out_dtype != BRAID_F32))
-        BRAID_REFUSE("gemm_tc_finish: the residual epilogues write float32 and need res");
-    if (out_dtype != BRAID_F32 && out_dtype != BRAID_BF16) BRAID_REFUSE("gemm_tc_finish: unknown out dtype code %d", out_dtype);
-    if (finish == 3 && (!gamma || !hb || !ss_out || ss_out_stride < n_rows || ldhb < m_out ||
-                        (gamma_dtype != BRAID_F32 && gamma_dtype != BRAID_BF16)))
-        BRAID_REFUSE("gemm_tc_finish: epilogue 3 needs the norm's weights, hb [rows, >= %d] and ss_out with a stride >= %d", m_out, n_rows);
-    if (ss_in && (ss_in_tiles <= 0 || ss_in_stride < n_rows || !(ss_in_width > 0.f)))
-        BRAID_REFUSE("gemm_tc_finish: row scale of %d shares, stride %lld, width %g for %d rows", ss_in_tiles, ss_in_stride, (double)ss_in_width, n_rows);
-    if (!error_flag || !workspace || !counters) BRAID_REFUSE("gemm_tc_finish: error_flag, workspace and counters are required");
-    if (!valid_block_n(block_n)) BRAID_REFUSE("gemm_tc_finish: token tile %d is not one of 16, 32, 64, 128, 256", block_n);
-    const int w_rows = (finish == 2) ? 2 * ((m_out + 15) / 16) * 16 : m_out;
-    const StreamKPlan p = plan_stream_k(n_rows, w_rows, k_in, block_n);
-    if (p.bytes > workspace_bytes)
-        BRAID_REFUSE("gemm_tc_finish: %d rows x %d x %d with token tile %d needs %lld bytes of workspace, it was given %lld",
-                     n_rows, w_rows, k_in, block_n, p.bytes, workspace_bytes);
-    if (p.tiles > n_counters) BRAID_REFUSE("gemm_tc_finish: %d tiles need as many counters, %d were given", p.tiles, n_counters);
-    if (p.tiles == 0) return BRAID_OK;
-    CUtensorMap mw, mx;
-    int rc = make_map(&mw, w, w_rows, k_in, ldw, TC_BLOCK_M);
-    if (rc) return rc;
-    rc = make_map(&mx, x, n_rows, k_in, ldx, block_n);
-    if (rc) return rc;
-    GemmTcArgs a{out, res, n_rows, m_out, k_in, ldo, out_dtype, p.m_tiles, p.n_tiles, p.max_segs, error_flag,
-                 p.tile_begin, p.tile_begin + p.tiles};
-    a.partial = (float*)workspace; a.counters = counters; a.finish = finish;
-    a.ss_in = ss_in; a.ss_in_tiles = ss_in_tiles; a.ss_in_stride = ss_in_stride; a.ss_in_width = ss_in_width; a.ss_in_eps = ss_in_eps;
-    a.gamma = gamma; a.gamma_dtype = gamma_dtype; a.hb = (__nv_bfloat16*)hb; a.ldhb = ldhb; a.ss_out = ss_out; a.ss_out_stride = ss_out_stride;
-    return dispatch_tc<4>(block_n, mw, mx, a, dim3(p.grid, 1, 1), (cudaStream_t)stream);
 }
 
 // Add up the partial products of an earlier stream-k call made with plan_out (the same

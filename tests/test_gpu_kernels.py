@@ -489,106 +489,13 @@ def test_stream_k_refuses_a_workspace_that_is_too_small_and_takes_any_token_tile
     ws = torch.empty(need // 4, dtype=torch.float32, device=DEV)
     out = torch.empty(300, 512, device=DEV, dtype=torch.bfloat16)
     args = lambda nbytes, tile: (x.data_ptr(), w.data_ptr(), out.data_ptr(), None, ws.data_ptr(), nbytes, BF16, 0,
-                                 300, 512, 256, 256, 256, 512, tile, 1, None, None, 0, 0, 0.0, 0.0,
-                                 K._error_flag.data_ptr() + 4, K._stream())
+                                 300, 512, 256, 256, 256, 512, tile, 1, None, K._error_flag.data_ptr() + 4, K._stream())
     assert K.lib.braid_gemm_tc(*args(need - 4, 128)) != 0            # refused on the host: nothing is launched
     assert b"bytes of workspace" in K.lib.braid_last_error()
     assert K.lib.braid_gemm_tc(*args(need, 48)) != 0 and b"token tile" in K.lib.braid_last_error()
     assert K.lib.braid_gemm_tc(*args(need, 128)) == 0
     K.check_device_errors()
     assert (out.double() - want).abs().max().item() < want.abs().max().item() / 128
-
-
-def shares_of(t, tiles):
-    """A tensor's sums of squares by row, cut into `tiles` shares of unequal size (as a product leaves them)."""
-    from braidinfer_b200.csrc.api import RowScale
-    n, width = t.shape
-    cuts = [0] + sorted(torch.randperm(width - 1, generator=torch.Generator().manual_seed(tiles))[:tiles - 1].add(1).tolist()) + [width]
-    shares = torch.zeros(tiles, -(-n // 4) * 4, device=DEV)
-    for i in range(tiles):
-        shares[i, :n] = t[:, cuts[i]:cuts[i + 1]].double().pow(2).sum(1).float()
-    return shares
-
-
-@pytest.mark.parametrize("n, m, k", [(8, 4096, 512), (1, 256, 64), (5, 200, 8200), (16, 1408, 1024), (40, 20000, 320),
-                                     (100, 640, 2048), (300, 384, 1024), (700, 392, 264)])
-def test_stream_k_product_that_finishes_itself(K, n, m, k):
-    """The partial sums are added up inside the product's kernel, by the CTA that delivers a tile's last part:
-    every epilogue beside float64, with and without a row scale on the input, twice with the same bits, and
-    the tile counters back at zero."""
-    from braidinfer_b200.csrc.api import RowScale, interleave_gate_up
-    x, w = rnd(n, k, dtype=torch.bfloat16, scale=0.5), rnd(m, k, dtype=torch.bfloat16, scale=0.5, seed=1)
-    ref = x.double() @ w.double().t()
-    scale = max(1.0, ref.abs().max().item())
-    # a row scale as the norm of some tensor of width 333 would leave it, in 7 shares
-    scale_in = RowScale(shares_of(rnd(n, 333, seed=5, scale=3.0), 7), 333, 1e-3)
-    rs = scale_in.values()[:n].double()[:, None]
-    assert (rs - torch.rsqrt(rnd(n, 333, seed=5, scale=3.0).double().pow(2).mean(1) + 1e-3)[:, None]).abs().max() < 1e-5
-    for sc, factor in ((None, 1.0), (scale_in, rs)):
-        out = torch.full((n, m), 9.0, device=DEV)
-        assert K.gemm_tc_finish(x, w, out, in_scale=sc) is None
-        assert (out.double() - ref * factor).abs().max() < 1e-5 * scale * max(1.0, float(torch.as_tensor(factor).max()))
-        again = torch.full((n, m), 7.0, device=DEV)
-        K.gemm_tc_finish(x, w, again, in_scale=sc)
-        assert torch.equal(out, again)
-        outb = torch.full((n, m), 9.0, device=DEV, dtype=torch.bfloat16)
-        K.gemm_tc_finish(x, w, outb, in_scale=sc)
-        assert (outb.double() - ref * factor).abs().max() < scale * max(1.0, float(torch.as_tensor(factor).max())) / 128
-    # the same bits as partial sums added up by the reduce kernel
-    sep = torch.empty(n, m, device=DEV)
-    K.gemm_tc(x, w, sep, stream_k=True)
-    fin = torch.empty(n, m, device=DEV)
-    K.gemm_tc_finish(x, w, fin)
-    assert torch.equal(sep, fin)
-    # residual sum in place
-    res = rnd(n, m, seed=2)
-    want = res.double() + ref
-    K.gemm_tc_finish(x, w, res, residual=res)
-    assert (res.double() - want).abs().max() < 1e-5 * scale
-    # residual sum and the next norm's inputs
-    gamma = (1 + rnd(m, seed=3, scale=0.3)).to(torch.bfloat16)
-    h = rnd(n, m, seed=4)
-    want_h = h.double() + ref
-    hb = torch.full((n, m), 9.0, device=DEV, dtype=torch.bfloat16)
-    out_scale = K.gemm_tc_finish(x, w, h, residual=h, norm_weight=gamma, norm_eps=1e-5, scaled_out=hb)
-    assert (h.double() - want_h).abs().max() < 1e-5 * scale
-    assert ((hb.double() - want_h * gamma.double()).abs() <= (want_h * gamma.double()).abs() / 200 + 1e-4 * scale).all()
-    want_rs = torch.rsqrt(want_h.pow(2).mean(1) + 1e-5)
-    assert out_scale.shares.shape[0] == -(-m // 128)
-    assert ((out_scale.values()[:n].double() - want_rs).abs() / want_rs).max() < 1e-5
-    # SwiGLU over interleaved rows, scaled and not
-    inter = m // 2
-    wi = interleave_gate_up(w[:inter], w[inter:2 * inter])
-    for sc, factor in ((None, 1.0), (scale_in, rs)):
-        g, u = ref[:, :inter] * factor, ref[:, inter:2 * inter] * factor
-        want = g / (1 + torch.exp(-g)) * u
-        act = torch.full((n, inter), 9.0, device=DEV, dtype=torch.bfloat16)
-        K.gemm_tc_finish(x, wi, act, swiglu=True, in_scale=sc)
-        passed_on = 1e-5 * scale * max(1.0, float(torch.as_tensor(factor).max())) * (1.1 * u.abs() + g.abs())
-        assert ((act.double() - want).abs() <= want.abs() / 100 + passed_on + 1e-3).all()
-    K.check_device_errors()
-    assert int(K._tile_counters.abs().sum()) == 0
-
-
-@pytest.mark.parametrize("n, m, k", [(8, 512, 256), (100, 640, 512), (40, 328, 264)])
-def test_whole_tile_products_apply_a_row_scale(K, n, m, k):
-    from braidinfer_b200.csrc.api import RowScale, interleave_gate_up
-    x, w = rnd(n, k, dtype=torch.bfloat16, scale=0.5), rnd(m, k, dtype=torch.bfloat16, scale=0.5, seed=1)
-    sc = RowScale(shares_of(rnd(n, 200, seed=5, scale=2.0), 3), 200, 1e-5)
-    ref = (x.double() @ w.double().t()) * sc.values()[:n].double()[:, None]
-    scale = max(1.0, ref.abs().max().item())
-    out = torch.empty(n, m, device=DEV)
-    K.gemm_tc(x, w, out, in_scale=sc)
-    assert (out.double() - ref).abs().max() < 1e-5 * scale
-    inter = m // 2
-    g, u = ref[:, :inter], ref[:, inter:2 * inter]
-    want = g / (1 + torch.exp(-g)) * u
-    act = torch.empty(n, inter, device=DEV, dtype=torch.bfloat16)
-    K.gemm_tc(x, interleave_gate_up(w[:inter], w[inter:2 * inter]), act, swiglu=True, in_scale=sc)
-    assert ((act.double() - want).abs() <= want.abs() / 100 + 1e-5 * scale * (1.1 * u.abs() + g.abs()) + 1e-3).all()
-    with pytest.raises(KernelError, match="row scale"):
-        K.gemm_tc(x, w, out, residual=out, in_scale=sc)
-    K.check_device_errors()
 
 
 def test_tensor_core_product_refuses_what_tma_cannot_address(K):
