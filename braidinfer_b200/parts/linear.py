@@ -16,24 +16,31 @@ from .spec import TensorSpec
 _SMS = None
 
 
-def stream_k_pays(rows: int, w_rows: int, sms: Optional[int] = None) -> bool:
-    """Whether the product of `rows` tokens with a [w_rows, k] weight should be spread evenly over
+def stream_k_pays(rows: int, w_rows: int, k_in: int, sms: Optional[int] = None) -> bool:
+    """Whether the product of `rows` tokens with a [w_rows, k_in] weight should be spread evenly over
     all SMs along k as well ("stream-k" partial sums plus a kernel that adds them up) rather than
-    cut into whole [128 x token tile] output tiles: it pays when whole tiles would leave SMs idle.
-    Measured on the 7B layer sizes at 1 to 2,048 tokens: up to 768 tokens a last round of tiles less
-    than 70 % full (80 % for up to 32 tokens, 60 % between 257 and 512) loses more than the adding-up
-    costs; beyond that the partial sums themselves cost too much."""
-    from ..csrc.api import token_tile
+    cut into whole output tiles: it pays when whole tiles would leave SMs idle and the partial sums
+    (rows x w_rows floats a CTA that shares a tile) are small beside the weights (w_rows x k_in).
+    Measured on the 7B layer sizes at 1 to 2,048 tokens.  Up to 128 tokens whole tiles are [128 x token
+    tile] on single SMs: stream-k when the last round of tiles would be less than 70 % full (80 % for up
+    to 32 tokens).  Beyond, whole tiles are [256 x 256] on pairs of SMs: stream-k when their last round
+    would be less than 70 % full and rows <= min(k_in / 16, 512): at 256 tokens every product of width
+    4096 but gate+up, at 512 only down (k_in = 14336), from 513 on none."""
+    from ..csrc.api import PAIR_TOKEN_TILE, token_tile
     global _SMS
     if sms is None:
         if _SMS is None:
             _SMS = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
         sms = _SMS
-    if rows > 768:
-        return False
-    tiles = -(-w_rows // 128) * -(-rows // token_tile(rows))
+    tile = token_tile(rows)
+    if tile == PAIR_TOKEN_TILE:
+        if rows > min(k_in // 16, 512):
+            return False
+        units, pairs = -(-w_rows // 256) * -(-rows // tile), max(sms // 2, 1)
+        return units / (-(-units // pairs) * pairs) < 0.7
+    tiles = -(-w_rows // 128) * -(-rows // tile)
     fill = tiles / (-(-tiles // sms) * sms)
-    return fill < (0.8 if rows <= 32 else 0.7 if rows <= 256 else 0.6 if rows <= 512 else 0.7)
+    return fill < (0.8 if rows <= 32 else 0.7)
 
 
 class Linear:
@@ -100,7 +107,7 @@ class Linear:
             K.cast(y, y2)
             return y2
         use_tc = (self.rt.gemm_backend == "auto" and x.dtype == torch.bfloat16 and K.gemm_tc_eligible(x, w))
-        sk = use_tc and stream_k_pays(rows, w_rows)
+        sk = use_tc and stream_k_pays(rows, w_rows, x.shape[1])
         can_defer = (defer_to is not None and sk and not swiglu
                      and self.rt.fuse_reduce and K.pending_partial is None)
         if residual is not None:

@@ -161,14 +161,17 @@ def test_pipelined_loop_makes_the_same_decisions():
 
 def test_where_a_product_is_spread_along_k():
     """`stream_k_pays` at the points it was measured on (148 SMs, 7B layer sizes): partial sums
-    wherever whole tiles would leave SMs idle, whole tiles where they fill them."""
+    wherever whole tiles would leave SMs idle and the sums are small beside the weights, whole tiles
+    where they fill the SMs or the tokens are many."""
     from braidinfer_b200.parts.linear import stream_k_pays
-    qkv, o, gate_up, down, head = 6144, 4096, 2 * 14336, 4096, 32768
-    for rows in (1, 8, 32, 64, 128, 256):
-        assert stream_k_pays(rows, qkv, 148) and stream_k_pays(rows, o, 148) and stream_k_pays(rows, down, 148)
-    assert stream_k_pays(8, gate_up, 148) and stream_k_pays(32, gate_up, 148)        # 224 tiles: 76 % full
-    assert not stream_k_pays(64, gate_up, 148) and not stream_k_pays(128, gate_up, 148)
-    assert not any(stream_k_pays(r, head, 148) for r in (1, 8, 64, 512))             # 256 tiles: 86 % full
-    assert not stream_k_pays(384, qkv, 148) and stream_k_pays(384, down, 148) and stream_k_pays(512, o, 148)
-    assert stream_k_pays(640, o, 148) and stream_k_pays(768, down, 148) and not stream_k_pays(768, qkv, 148)
-    assert not stream_k_pays(769, o, 148) and not stream_k_pays(2048, down, 148)
+    pays = lambda rows, shape: stream_k_pays(rows, shape[0], shape[1], 148)
+    qkv, o, gate_up, down, head = (6144, 4096), (4096, 4096), (2 * 14336, 4096), (4096, 14336), (32768, 4096)
+    for rows in (1, 8, 32, 64, 128, 160, 256):
+        assert pays(rows, qkv) and pays(rows, o) and pays(rows, down)
+    assert pays(8, gate_up) and pays(32, gate_up)                                    # 224 tiles: 76 % full
+    assert not any(pays(r, gate_up) for r in (64, 128, 160, 256, 512))
+    assert not any(pays(r, head) for r in (1, 8, 64, 512))                           # 256 tiles: 86 % full
+    assert not pays(384, qkv) and not pays(384, o) and pays(384, down)               # the sums outweigh k = 4096
+    assert not pays(512, o) and pays(512, down) and not pays(512, qkv)
+    assert not any(pays(768, s) for s in (qkv, o, down))
+    assert not pays(769, o) and not pays(2048, down)
