@@ -92,7 +92,17 @@ __device__ __forceinline__ int block_exclusive_iscan(int v, int* sh /* [32] */) 
 }
 
 // Lowest index of the largest value of x[0..n); a NaN anywhere raises *nan_flag.
-__device__ int block_argmax(const float* x, int n, float* shf, int* shi, int* nan_flag) {
+// A row of logits.  In shared memory it is laid out with one float of padding after every 32: the chain
+// reads it both with consecutive threads on consecutive elements and with every thread on a run of
+// elements of its own (the sums along the index), and without the padding the runs of a warp's threads
+// start 32 floats apart, on one bank.
+struct Row {
+    float* p;
+    int padded;
+    __device__ __forceinline__ float& operator[](int i) const { return p[padded ? i + (i >> 5) : i]; }
+};
+
+__device__ int block_argmax(Row x, int n, float* shf, int* shi, int* nan_flag) {
     float best = -INFINITY;
     int best_i = 0x7fffffff;
     bool saw_nan = false;
@@ -115,7 +125,7 @@ argmax_kernel(const float* __restrict__ logits, long long ld, int* __restrict__ 
     pdl_wait();
     __shared__ float shf[32];
     __shared__ int shi[32];
-    const int r = block_argmax(logits + (size_t)blockIdx.x * ld, vocab, shf, shi, nan_flag);
+    const int r = block_argmax(Row{const_cast<float*>(logits) + (size_t)blockIdx.x * ld, 0}, vocab, shf, shi, nan_flag);
     if (threadIdx.x == 0) out[blockIdx.x] = r;
 }
 
@@ -149,11 +159,12 @@ struct SampleArgs {
     const int* bias_tok;
     const float* bias_val;
     int* nan_flag;
+    int row_in_smem;         // the launch has vocab floats of dynamic shared memory for the row
 };
 
 // Keep the `keep` lowest-index elements whose key equals `cut` and everything above
 // it; set the rest to -inf.
-__device__ void apply_cut(float* x, int n, unsigned int cut, int keep_equal, int* shi) {
+__device__ void apply_cut(Row x, int n, unsigned int cut, int keep_equal, int* shi) {
     const int chunk = (n + blockDim.x - 1) / blockDim.x;
     const int b = min(n, (int)threadIdx.x * chunk), e = min(n, b + chunk);
     int eq = 0;
@@ -173,7 +184,7 @@ __device__ void apply_cut(float* x, int n, unsigned int cut, int keep_equal, int
 // The k-th largest key of x[0..n): most significant digit first, eight bits a pass.  After a
 // pass `prefix` holds the digits found so far and `want` the rank still looked for among
 // the keys that share them.  Counts are integers, so the result does not depend on timing.
-__device__ unsigned int kth_largest_key(const float* x, int n, int k, int* hist /* [256] */, int* shi) {
+__device__ unsigned int kth_largest_key(Row x, int n, int k, int* hist /* [256] */, int* shi) {
     unsigned int prefix = 0;
     int want = k;
     for (int shift = 24; shift >= 0; shift -= 8) {
@@ -272,6 +283,10 @@ __device__ int sample_few(float* cv, const int* ci, int m, float mp, float tp, f
     return ci[r];
 }
 
+#define SAMP_ROW_SMEM_BYTES (216 * 1024)
+// bytes of a padded row of n floats (see Row)
+static inline size_t samp_row_bytes(int n) { return ((size_t)n + (size_t)(n >> 5) + 1) * sizeof(float); }
+
 __global__ void __launch_bounds__(SAMP_THREADS)
 sample_kernel(SampleArgs a) {
     pdl_trigger();
@@ -282,10 +297,13 @@ sample_kernel(SampleArgs a) {
     __shared__ int hist[256];
     __shared__ float cand_v[SAMP_THREADS];
     __shared__ int cand_i[SAMP_THREADS];
+    extern __shared__ float row_s[];                     // the row itself, when it fits (a.row_in_smem)
     const int row = blockIdx.x, n = a.vocab;
     const float* in = a.logits + (size_t)row * a.ld;
-    float* x = a.work + (size_t)row * n;
-    if (x != in)
+    // The chain passes over the row a dozen times; a row that fits in shared memory is copied there
+    // once and never touches global memory again.  Longer rows live in the caller's scratch.
+    const Row x{a.row_in_smem ? row_s : a.work + (size_t)row * n, a.row_in_smem};
+    if (x.p != in)
         for (int i = threadIdx.x; i < n; i += blockDim.x) x[i] = in[i];
     __syncthreads();
     // logit bias: additive, one entry after another (sampling.rs:57-65)
@@ -444,8 +462,21 @@ extern "C" int braid_sample(const float* logits, float* work, long long ld, int*
     if (rows <= 0) return BRAID_OK;
     if (vocab <= 0) BRAID_REFUSE("sample: vocab=%d must be positive", vocab);
     if (!temperature || !uniform) BRAID_REFUSE("sample: temperature and uniform arrays are required");
+    // a row of up to SAMP_ROW_SMEM_BYTES stays in shared memory for the whole chain
+    const size_t row_bytes = samp_row_bytes(vocab);
+    const int in_smem = row_bytes <= SAMP_ROW_SMEM_BYTES;
+    if (in_smem) {
+        static bool configured = false;
+        if (!configured) {
+            cudaError_t e = cudaFuncSetAttribute(sample_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SAMP_ROW_SMEM_BYTES);
+            if (e != cudaSuccess) { braid_set_error("sample: cannot reserve %d bytes of shared memory: %s", SAMP_ROW_SMEM_BYTES, cudaGetErrorString(e)); return (int)e; }
+            configured = true;
+        }
+    } else if (!work) {
+        BRAID_REFUSE("sample: a row of %d logits does not fit in shared memory and needs the work buffer", vocab);
+    }
     SampleArgs a{logits, work, ld, out, vocab, temperature, top_k, top_p, min_p, rep_penalty, uniform,
-                 hist_off, hist_tok, hist_cnt, bias_off, bias_tok, bias_val, nan_flag};
-    braid_launch(sample_kernel, dim3(rows), dim3(SAMP_THREADS), 0, (cudaStream_t)stream, a);
+                 hist_off, hist_tok, hist_cnt, bias_off, bias_tok, bias_val, nan_flag, in_smem};
+    braid_launch(sample_kernel, dim3(rows), dim3(SAMP_THREADS), in_smem ? row_bytes : 0, (cudaStream_t)stream, a);
     BRAID_LAUNCH_CHECK();
 }
