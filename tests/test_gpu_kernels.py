@@ -503,6 +503,14 @@ def test_tensor_core_product_refuses_what_tma_cannot_address(K):
     assert not K.gemm_tc_eligible(x, w)
     with pytest.raises(KernelError, match="multiples of 8"):
         K.gemm_tc(x, w, torch.empty(4, 128, device=DEV))
+    with pytest.raises(KernelError, match="multiples of 8"):
+        K.gemm_tc_pair(x, w, torch.empty(4, 128, device=DEV))
+    x8, w8 = rnd(4, 64, dtype=torch.bfloat16), rnd(128, 64, dtype=torch.bfloat16)
+    with pytest.raises(KernelError, match="residual epilogue"):
+        K.gemm_tc_pair(x8, w8, torch.empty(4, 128, device=DEV, dtype=torch.bfloat16),
+                       residual=torch.empty(4, 128, device=DEV))
+    with pytest.raises(KernelError, match="interleaved weight rows"):
+        K.gemm_tc_pair(x8, w8, torch.empty(4, 30, device=DEV, dtype=torch.bfloat16), swiglu=True)
     with pytest.raises(KernelError, match="head_dim"):
         K.attn_simple(rnd(1, 300 * 3), torch.empty(1, 300, device=DEV), torch.zeros(1, 2, 1, 64, 300, device=DEV),
                       torch.zeros(1, 1, dtype=torch.int32, device=DEV), torch.zeros(1, dtype=torch.int32, device=DEV),
