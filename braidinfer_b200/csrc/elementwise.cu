@@ -374,8 +374,8 @@ extern "C" int braid_rope_kv_write(void* qkv, int dtype, const float* inv_freq, 
     if ((dtype == BRAID_F32 || dtype == BRAID_BF16) && hd % (2 * vec) == 0 && rope_dim % (2 * vec) == 0 &&
         (((uintptr_t)qkv | (uintptr_t)cache) & 15) == 0) {
         const size_t smem = (size_t)rope_dim * sizeof(float);
-        if (dtype == BRAID_F32) braid_launch(rope_kv_vec_kernel<float>, dim3(rows), dim3(256), smem, s, a);
-        else braid_launch(rope_kv_vec_kernel<__nv_bfloat16>, dim3(rows), dim3(256), smem, s, a);
+        if (dtype == BRAID_F32) braid_launch(rope_kv_vec_kernel<float>, dim3(rows), dim3(128), smem, s, a);
+        else braid_launch(rope_kv_vec_kernel<__nv_bfloat16>, dim3(rows), dim3(128), smem, s, a);
         BRAID_LAUNCH_CHECK();
     }
     dim3 grid(rows, nqh + 2 * nkh);
