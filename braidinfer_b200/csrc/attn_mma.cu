@@ -298,16 +298,19 @@ template <int HD>
 __global__ void attn_combine_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ out,
                                     const int* __restrict__ token_seq, int out_row_stride, int nqh, int n_splits) {
     pdl_trigger();
-    pdl_wait();
+    // the step's tables are on the device before the step's first kernel: read before the wait
     const int row = blockIdx.x, head = blockIdx.y;
-    if (token_seq[row] < 0) return;
+    const bool padding = token_seq[row] < 0;
+    pdl_wait();
+    if (padding) return;
     const float* p = partial + ((size_t)row * nqh + head) * n_splits * (HD + 2);
+    constexpr int B = 16;                                  // slices asked for at once: one trip for up to 16
     for (int d = threadIdx.x; d < HD; d += blockDim.x) {
         float M = -INFINITY, L = 0.f, acc = 0.f;
-        for (int s0 = 0; s0 < n_splits; s0 += 8) {
-            float m[8], l[8], o[8];
+        for (int s0 = 0; s0 < n_splits; s0 += B) {
+            float m[B], l[B], o[B];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
+            for (int i = 0; i < B; ++i) {
                 const bool in = s0 + i < n_splits;
                 const float* ps = p + (size_t)(in ? s0 + i : 0) * (HD + 2);
                 m[i] = in ? ps[0] : -INFINITY;
@@ -316,13 +319,13 @@ __global__ void attn_combine_kernel(const float* __restrict__ partial, __nv_bflo
             }
             float Mn = M;
 #pragma unroll
-            for (int i = 0; i < 8; ++i) Mn = fmaxf(Mn, m[i]);
+            for (int i = 0; i < B; ++i) Mn = fmaxf(Mn, m[i]);
             if (Mn == -INFINITY) continue;
             const float c = exp2f(M - Mn);                 // exp2(-inf) = 0 the first time
             L *= c;
             acc *= c;
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
+            for (int i = 0; i < B; ++i) {
                 const float wgt = (m[i] == -INFINITY) ? 0.f : exp2f(m[i] - Mn);
                 L = fmaf(l[i], wgt, L);
                 acc = fmaf(o[i], wgt, acc);
