@@ -382,8 +382,8 @@ __global__ void streamk_reduce_kernel(StreamK k, void* __restrict__ out, const f
     pdl_wait();
     float v[4];
     if (MODE == 2) {
-        const float4 g4 = streamk_sum4(k, sp, n, c0);
-        const float4 u4 = streamk_sum4(k, sp, n, c0 + 16);
+        float4 g4, u4;
+        streamk_sum4_pair(k, sp, n, c0, c0 + 16, g4, u4);
         v[0] = g4.x / (1.f + expf(-g4.x)) * u4.x;
         v[1] = g4.y / (1.f + expf(-g4.y)) * u4.y;
         v[2] = g4.z / (1.f + expf(-g4.z)) * u4.z;

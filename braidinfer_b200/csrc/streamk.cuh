@@ -148,3 +148,34 @@ __device__ __forceinline__ float4 streamk_sum4(const StreamK& k, const StreamKSp
     }
     return acc;
 }
+
+// Two groups of four consecutive columns of one tile at once (a SwiGLU output's gate and up sums): the
+// slots of both are asked for together, so the two sums cost one trip, not two.  Each sum adds its own
+// slots in ascending CTA order, as streamk_sum4 does.
+__device__ __forceinline__ void streamk_sum4_pair(const StreamK& k, const StreamKSpan& s, int n, int col0, int col1,
+                                                  float4& out0, float4& out1) {
+    const size_t slot_elems = streamk_slot_elems(k);
+    const float* b0 = k.partial + streamk_in_slot(k, n, col0);
+    const float* b1 = k.partial + streamk_in_slot(k, n, col1);
+    const size_t stride = (size_t)k.max_segs * slot_elems;
+    float4 a0 = *reinterpret_cast<const float4*>(b0 + (size_t)s.slot_first * slot_elems);
+    float4 a1 = *reinterpret_cast<const float4*>(b1 + (size_t)s.slot_first * slot_elems);
+    constexpr int B = STREAMK_BATCH / 2;
+    for (int c0 = s.c_first + 1; c0 <= s.c_last; c0 += B) {
+        float4 v0[B], v1[B];
+#pragma unroll
+        for (int i = 0; i < B; ++i) {
+            const bool in = c0 + i <= s.c_last;
+            v0[i] = in ? *reinterpret_cast<const float4*>(b0 + (size_t)(c0 + i) * stride) : make_float4(0.f, 0.f, 0.f, 0.f);
+            v1[i] = in ? *reinterpret_cast<const float4*>(b1 + (size_t)(c0 + i) * stride) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int i = 0; i < B; ++i)
+            if (c0 + i <= s.c_last) {
+                a0.x += v0[i].x; a0.y += v0[i].y; a0.z += v0[i].z; a0.w += v0[i].w;
+                a1.x += v1[i].x; a1.y += v1[i].y; a1.z += v1[i].z; a1.w += v1[i].w;
+            }
+    }
+    out0 = a0;
+    out1 = a1;
+}
