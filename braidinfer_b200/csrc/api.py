@@ -59,11 +59,37 @@ def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
 PAIR_TOKEN_TILE = 256        # the token tile of the kernel that runs on pairs of SMs
 
 
+class RowScale:
+    """A row scale still to be applied: an RMSNorm whose rows were left unscaled (csrc/rowscale.cuh).
+    `shares` [n, stride >= rows] float32 holds each row's sum of squares in n shares, as the kernel that
+    wrote the rows left them; the scale of row r is rsqrt(sum over shares[:, r] / width + eps).  The
+    product that reads the unscaled rows applies the scale to its own results (`in_scale`)."""
+
+    def __init__(self, shares: torch.Tensor, width: int, eps: float) -> None:
+        self.shares, self.width, self.eps = shares, int(width), float(eps)
+
+    def args(self):
+        return (self.shares.data_ptr(), self.shares.shape[0], self.shares.stride(0), float(self.width), self.eps)
+
+    def values(self) -> torch.Tensor:
+        """The scales themselves (for tests and for parts written in torch)."""
+        return torch.rsqrt(self.shares.sum(0) / self.width + self.eps)
+
+
+_NO_SCALE = (None, 0, 0, 0.0, 0.0)
+
+
+def _scale_args(scale: Optional["RowScale"]):
+    return scale.args() if scale is not None else _NO_SCALE
+
+
 class PartialProduct:
     """Partial products of a stream-k GEMM waiting in the workspace to be added up."""
 
-    def __init__(self, workspace: torch.Tensor, plan, n_rows: int, w_rows: int) -> None:
+    def __init__(self, workspace: torch.Tensor, plan, n_rows: int, w_rows: int,
+                 in_scale: Optional["RowScale"] = None) -> None:
         self.workspace, self.plan, self.n_rows, self.w_rows = workspace, plan, n_rows, w_rows
+        self.in_scale = in_scale      # a row scale of the product's input that the adding-up has to apply
 
 
 class Kernels:
@@ -108,16 +134,19 @@ class Kernels:
                                         c_float, c_void_p, c_void_p]
         L.braid_gemm_simt.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                                       c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_void_p]
+        scale = [c_void_p, c_int, c_longlong, c_float, c_float]        # RowScale.args()
         L.braid_gemm_tc.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int,
                                     c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_int, c_int,
-                                    c_void_p, c_void_p, c_void_p]
+                                    c_void_p] + scale + [c_void_p, c_void_p]
+        L.braid_streamk_reduce_prep.argtypes = [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                                                c_longlong, c_int, c_void_p]
         L.braid_gemm_tc2.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                      c_longlong, c_longlong, c_longlong, c_int, c_void_p, c_void_p]
         L.braid_streamk_reduce.argtypes = [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_longlong,
-                                           c_int, c_int, c_void_p]
+                                           c_int, c_int] + scale + [c_void_p]
         L.braid_streamk_reduce_norm.argtypes = [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int,
                                                 c_void_p, c_int, c_int, c_float, c_void_p]
-        L.braid_streamk_reduce_rope_kv.argtypes = [c_void_p] * 8 + [c_int] * 9 + [c_void_p, c_void_p]
+        L.braid_streamk_reduce_rope_kv.argtypes = [c_void_p] * 8 + [c_int] * 9 + scale + [c_void_p, c_void_p]
         L.braid_gemm_tc_workspace_bytes.argtypes = [c_int, c_int, c_int, c_int]
         L.braid_gemm_tc_workspace_bytes.restype = c_longlong
         L.braid_argmax.argtypes = [c_void_p, c_longlong, c_void_p, c_int, c_int, c_void_p, c_void_p]
@@ -126,7 +155,8 @@ class Kernels:
         for name in ("braid_embed", "braid_rmsnorm", "braid_silu_mul", "braid_residual_add",
                      "braid_rope_kv_write", "braid_cast", "braid_attn_simple", "braid_gemm_simt",
                      "braid_gemm_tc", "braid_gemm_tc2", "braid_argmax", "braid_sample", "braid_streamk_reduce",
-                     "braid_streamk_reduce_norm", "braid_streamk_reduce_rope_kv"):
+                     "braid_streamk_reduce_norm", "braid_streamk_reduce_rope_kv", "braid_streamk_reduce_prep",
+                     "braid_streamk_reduce_prep_cols"):
             getattr(L, name).restype = c_int
 
     def _check(self, rc: int, what: str) -> None:
@@ -330,14 +360,16 @@ class Kernels:
         return self.tc_workspace(need)
 
     def gemm_tc(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, residual: Optional[torch.Tensor] = None,
-                swiglu: bool = False, block_n: int = 0, stream_k: bool = False) -> None:
+                swiglu: bool = False, block_n: int = 0, stream_k: bool = False,
+                in_scale: Optional[RowScale] = None) -> None:
         """bfloat16 x [n, k] times w [m, k]^T on the tensor cores.  With `swiglu`, w holds
         gate and up rows interleaved in blocks of 16 (`interleave_gate_up`) and out is [n, I].  `stream_k` spreads the weight stream
         evenly over all SMs whatever the shape (for up to a few hundred tokens) and adds a reduce kernel.
         Whole tiles of more than 128 tokens run on pairs of SMs (`gemm_tc_pair`: faster at every
-        measured size, and bit for bit the same result) unless `block_n` names a token tile."""
+        measured size, and bit for bit the same result) unless `block_n` names a token tile.
+        `in_scale`: a row scale that x still wants; the store and SwiGLU epilogues apply it to their results."""
         n, k = x.shape
-        if not stream_k and block_n == 0 and token_tile(n) == PAIR_TOKEN_TILE:
+        if not stream_k and block_n == 0 and token_tile(n) == PAIR_TOKEN_TILE and in_scale is None:
             return self.gemm_tc_pair(x, w, out, residual=residual, swiglu=swiglu)
         w_rows = w.shape[0]
         m = out.shape[1] if swiglu else w_rows
@@ -357,7 +389,7 @@ class Kernels:
         self._check(self.lib.braid_gemm_tc(x.data_ptr(), w.data_ptr(), out.data_ptr(), _ptr(residual), _ptr(ws),
                                            ws.numel() * 4 if ws is not None else 0,
                                            dtype_code(out.dtype), mode, n, m, k, x.stride(0), w.stride(0),
-                                           out.stride(0), block_n, int(stream_k), None,
+                                           out.stride(0), block_n, int(stream_k), None, *_scale_args(in_scale),
                                            self._error_flag.data_ptr() + 4, self._stream()), "gemm_tc")
 
     def gemm_tc_pair(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor,
@@ -380,7 +412,7 @@ class Kernels:
                                             self._stream()),
                     "gemm_tc_pair")
 
-    def gemm_tc_partial(self, x: torch.Tensor, w: torch.Tensor) -> "PartialProduct":
+    def gemm_tc_partial(self, x: torch.Tensor, w: torch.Tensor, in_scale: Optional[RowScale] = None) -> "PartialProduct":
         """The stream-k product without its reduce: the partial products stay in the
         workspace, and the returned handle lets one of the `streamk_reduce*` calls add
         them up together with what follows.  Only one such handle may be open at a time."""
@@ -394,8 +426,9 @@ class Kernels:
         self.launches += 1
         self._check(self.lib.braid_gemm_tc(x.data_ptr(), w.data_ptr(), None, None, ws.data_ptr(), ws.numel() * 4,
                                            F32, 0, n, w_rows, k, x.stride(0), w.stride(0), 0, block_n, 1, plan,
+                                           *_NO_SCALE,          # whoever adds the sums up applies the scale
                                            self._error_flag.data_ptr() + 4, self._stream()), "gemm_tc_partial")
-        p = PartialProduct(ws, plan, n, w_rows)
+        p = PartialProduct(ws, plan, n, w_rows, in_scale)
         self.pending_partial = p
         return p
 
@@ -411,7 +444,8 @@ class Kernels:
         self._close_partial(p)
         self.launches += 1
         self._check(self.lib.braid_streamk_reduce(p.workspace.data_ptr(), p.plan, p.n_rows, out.data_ptr(), _ptr(residual),
-                                                  m, out.stride(0), dtype_code(out.dtype), mode, self._stream()),
+                                                  m, out.stride(0), dtype_code(out.dtype), mode, *_scale_args(p.in_scale),
+                                                  self._stream()),
                     "streamk_reduce")
 
     def streamk_reduce_norm(self, p: "PartialProduct", h: torch.Tensor, w: torch.Tensor, out: torch.Tensor, eps: float,
@@ -419,6 +453,8 @@ class Kernels:
         """h += sum of the partial products (written back unless rows are gathered), then
         out = RMSNorm(h) * w, in one kernel."""
         rows_out, width = out.shape
+        if p.in_scale is not None:
+            raise KernelError("this partial product carries a row scale, which reduce + norm does not apply")
         self._close_partial(p)
         self.launches += 1
         self._check(self.lib.braid_streamk_reduce_norm(p.workspace.data_ptr(), p.plan, p.n_rows, h.data_ptr(), w.data_ptr(),
@@ -438,7 +474,29 @@ class Kernels:
         self._check(self.lib.braid_streamk_reduce_rope_kv(
             p.workspace.data_ptr(), p.plan, qkv.data_ptr(), inv_freq.data_ptr(), positions.data_ptr(),
             token_seq.data_ptr(), _ptr(page_table), _ptr(cache), qkv.shape[0], nqh, nkh, hd, rope_dim, int(adjacent),
-            page_size, cols, num_pages, self._error_flag.data_ptr(), self._stream()), "streamk_reduce_rope_kv")
+            page_size, cols, num_pages, *_scale_args(p.in_scale), self._error_flag.data_ptr(), self._stream()),
+            "streamk_reduce_rope_kv")
+
+    def streamk_reduce_prep(self, p: Optional["PartialProduct"], h: torch.Tensor, w: torch.Tensor, out: torch.Tensor,
+                            eps: float) -> RowScale:
+        """h += sum of the partial products (p None: h is complete), out = bfloat16(h * w), and the returned
+        RowScale completes the RMSNorm of h with weights w: whoever multiplies `out` by a matrix applies it
+        to its results (`in_scale`).  Many small CTAs instead of one per row."""
+        rows, width = h.shape
+        if out.dtype != torch.bfloat16 or h.dtype != torch.float32 or out.shape != h.shape:
+            raise KernelError("reduce_prep reads the float32 residual stream and writes bfloat16 of the same shape")
+        cols = self.lib.braid_streamk_reduce_prep_cols()
+        shares = torch.empty((-(-width // cols), -(-rows // 4) * 4), dtype=torch.float32, device=h.device)
+        if p is not None:
+            if p.in_scale is not None:
+                raise KernelError("this partial product carries a row scale, which the residual sum does not apply")
+            self._close_partial(p)
+        self.launches += 1
+        self._check(self.lib.braid_streamk_reduce_prep(
+            p.workspace.data_ptr() if p is not None else None, p.plan if p is not None else None, rows, h.data_ptr(),
+            w.data_ptr(), dtype_code(w.dtype), out.data_ptr(), shares.data_ptr(), shares.stride(0), width,
+            self._stream()), "streamk_reduce_prep")
+        return RowScale(shares, width, eps)
 
     @staticmethod
     def gemm_tc_eligible(x: torch.Tensor, w: torch.Tensor) -> bool:

@@ -29,7 +29,7 @@ COMMON_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "--expt
 # Sources that do not depend on a model size.
 CORE_SOURCES = ["errors.cu", "elementwise.cu", "attn_simple.cu", "gemm_simt.cu", "gemm_tc.cu", "gemm_tc2.cu",
                 "fused_reduce.cu", "sampling.cu"]
-HEADERS = ["common.cuh", "streamk.cuh", "tcgen05.cuh", "attn_noalloc.h", "page.h", "trace.cuh"]
+HEADERS = ["common.cuh", "rowscale.cuh", "streamk.cuh", "tcgen05.cuh", "attn_noalloc.h", "page.h", "trace.cuh"]
 
 
 class BuildError(RuntimeError):

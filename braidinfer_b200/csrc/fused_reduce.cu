@@ -8,9 +8,14 @@
 //   braid_streamk_reduce_rope_kv  qkv = sum, rotary encoding of the query and key heads,
 //                                 keys and values into the paged cache (what elementwise.cu's
 //                                 rope_kv_kernel does after a plain product).
+//   braid_streamk_reduce_prep     h = h + sum, and what an RMSNorm whose scale is left to the next
+//                                 product needs (rowscale.cuh): bfloat16(h * w) and each CTA's share
+//                                 of the rows' sums of squares.  A CTA owns 512 columns of one row, so
+//                                 a step of 8 rows of 4096 is finished by 64 CTAs, not by 8.
 //
 // Formulas are those of the unfused kernels (elementwise.cu cites the reference lines).
 #include "common.cuh"
+#include "rowscale.cuh"
 #include "streamk.cuh"
 #include "trace.cuh"
 
@@ -144,6 +149,78 @@ extern "C" int braid_streamk_reduce_norm(const float* partial, const int* plan, 
     BRAID_LAUNCH_CHECK();
 }
 
+// ------------------------------------------------------------------ reduce + what a scaled norm needs
+#define PREP_THREADS 128
+#define PREP_COLS (PREP_THREADS * 4)           // columns of a row that one CTA owns
+
+// h[row, c..] += sum of the partial products (k.partial null: h is complete already), hb = bfloat16(h * w),
+// shares[blockIdx.x][row] = sum over the CTA's columns of h^2.  Width a multiple of 4, rows of h and hb
+// start on 16 and 8 bytes.
+template <typename TW>
+__global__ void __launch_bounds__(PREP_THREADS)
+streamk_reduce_prep_kernel(StreamK k, float* __restrict__ h, const TW* __restrict__ w, __nv_bfloat16* __restrict__ hb,
+                           float* __restrict__ shares, long long share_stride, int width) {
+    pdl_trigger();
+    __shared__ float red[PREP_THREADS / 32];
+    const int row = blockIdx.y;
+    const int c = blockIdx.x * PREP_COLS + threadIdx.x * 4;
+    const bool live = c < width;
+    // where the partial sums lie and the norm's weights (no kernel writes them): before the wait
+    StreamKSpan sp = {};
+    float g[4] = {0.f, 0.f, 0.f, 0.f};
+    if (live) {
+        if (k.partial) sp = streamk_span(k, row, c);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) g[e] = to_f32(w[c + e]);
+    }
+    pdl_wait();
+    float ss = 0.f;
+    if (live) {
+        float* hr = h + (size_t)row * width + c;
+        const float4 old = *reinterpret_cast<const float4*>(hr);
+        float4 v = old;
+        if (k.partial) {
+            const float4 s4 = streamk_sum4(k, sp, row, c);
+            v = make_float4(old.x + s4.x, old.y + s4.y, old.z + s4.z, old.w + s4.w);
+            *reinterpret_cast<float4*>(hr) = v;
+        }
+        ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, v.w * v.w)));
+        __nv_bfloat162 lo = __floats2bfloat162_rn(v.x * g[0], v.y * g[1]), hi = __floats2bfloat162_rn(v.z * g[2], v.w * g[3]);
+        uint2 pk;
+        pk.x = *reinterpret_cast<unsigned int*>(&lo);
+        pk.y = *reinterpret_cast<unsigned int*>(&hi);
+        *reinterpret_cast<uint2*>(hb + (size_t)row * width + c) = pk;
+    }
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, d);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    if (threadIdx.x == 0) shares[(size_t)blockIdx.x * share_stride + row] = ((red[0] + red[1]) + red[2]) + red[3];
+}
+
+// `partial` and `plan` null: h is complete and only hb and the shares are made.  shares: [ceil(width / 512)][share_stride].
+extern "C" int braid_streamk_reduce_prep(const float* partial, const int* plan, int n_rows, float* h, const void* w,
+                                         int w_dtype, void* hb, float* shares, long long share_stride, int width,
+                                         void* stream) {
+    if (n_rows <= 0) return BRAID_OK;
+    if (width <= 0 || (width & 3)) BRAID_REFUSE("reduce_prep: width=%d must be a positive multiple of 4", width);
+    if (((uintptr_t)h & 15) || ((uintptr_t)hb & 7)) BRAID_REFUSE("reduce_prep: h and hb must be aligned to 16 and 8 bytes");
+    if (!shares || share_stride < n_rows) BRAID_REFUSE("reduce_prep: shares with a stride of at least %d are required", n_rows);
+    if ((partial == nullptr) != (plan == nullptr)) BRAID_REFUSE("reduce_prep: partial sums come with their plan");
+    if (n_rows > 65535) BRAID_REFUSE("reduce_prep: %d rows exceed the grid limit", n_rows);
+    StreamK k = {};
+    if (partial) k = streamk_from_plan(partial, plan, n_rows);
+    const dim3 grid((width + PREP_COLS - 1) / PREP_COLS, n_rows);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (w_dtype == BRAID_F32)
+        braid_launch(streamk_reduce_prep_kernel<float>, grid, dim3(PREP_THREADS), 0, s, k, h, (const float*)w, (__nv_bfloat16*)hb, shares, share_stride, width);
+    else if (w_dtype == BRAID_BF16)
+        braid_launch(streamk_reduce_prep_kernel<__nv_bfloat16>, grid, dim3(PREP_THREADS), 0, s, k, h, (const __nv_bfloat16*)w, (__nv_bfloat16*)hb, shares, share_stride, width);
+    else BRAID_REFUSE("reduce_prep: unknown dtype code w=%d", w_dtype);
+    BRAID_LAUNCH_CHECK();
+}
+extern "C" int braid_streamk_reduce_prep_cols(void) { return PREP_COLS; }
+
 // ------------------------------------------------------------------ reduce + rotary + cache write
 struct ReduceRopeArgs {
     StreamK k;
@@ -156,6 +233,7 @@ struct ReduceRopeArgs {
     int rows, nqh, nkh, hd, rope_dim, adjacent;
     int page_size, table_cols, num_pages;
     int* error_flag;
+    RowScaleArgs scale;          // a row scale that the product's input still wants (rowscale.cuh), or none
 };
 
 __global__ void streamk_reduce_rope_kv_kernel(ReduceRopeArgs a) {
@@ -196,6 +274,10 @@ __global__ void streamk_reduce_rope_kv_kernel(ReduceRopeArgs a) {
             sp1 = streamk_span(a.k, row, col0 + (a.adjacent ? 2 * p_first + 1 : p_first + half));
         }
         pdl_wait();
+        RowScaleAsked asked;                               // the row scale travels with the first partial sums: one trip
+        row_scale_ask(a.scale, row, asked);
+        float rs = 1.f;
+        bool have_rs = false;
         for (int p = threadIdx.x; p < half; p += blockDim.x) {
             const int i0 = a.adjacent ? 2 * p : p;
             const int i1 = a.adjacent ? 2 * p + 1 : p + half;
@@ -209,16 +291,18 @@ __global__ void streamk_reduce_rope_kv_kernel(ReduceRopeArgs a) {
             // the product is rounded to bfloat16 before it is rotated, as after a plain product
             float f0, f1;
             streamk_sum_pair(a.k, s0, s1, row, col0 + i0, col0 + i1, f0, f1);
-            const float x0 = __bfloat162float(__float2bfloat16_rn(f0));
-            const float x1 = __bfloat162float(__float2bfloat16_rn(f1));
+            if (!have_rs) { rs = row_scale_finish(a.scale, row, asked); have_rs = true; }
+            const float x0 = __bfloat162float(__float2bfloat16_rn(f0 * rs));
+            const float x1 = __bfloat162float(__float2bfloat16_rn(f1 * rs));
             const __nv_bfloat16 y0 = __float2bfloat16_rn(x0 * cs - x1 * sn);
             const __nv_bfloat16 y1 = __float2bfloat16_rn(x0 * sn + x1 * cs);
             dst_row[i0] = y0;
             dst_row[i1] = y1;
             if (dst) { dst[i0] = y0; dst[i1] = y1; }
         }
+        if (!have_rs) rs = row_scale_finish(a.scale, row, asked);
         for (int i = a.rope_dim + threadIdx.x; i < a.hd; i += blockDim.x) {
-            const __nv_bfloat16 y = __float2bfloat16_rn(streamk_sum(a.k, streamk_span(a.k, row, col0 + i), row, col0 + i));
+            const __nv_bfloat16 y = __float2bfloat16_rn(streamk_sum(a.k, streamk_span(a.k, row, col0 + i), row, col0 + i) * rs);
             dst_row[i] = y;
             if (dst) dst[i] = y;
         }
@@ -227,17 +311,24 @@ __global__ void streamk_reduce_rope_kv_kernel(ReduceRopeArgs a) {
         StreamKSpan sp0 = {};
         if (i_first < a.hd) sp0 = streamk_span(a.k, row, col0 + i_first);
         pdl_wait();
+        RowScaleAsked asked;
+        row_scale_ask(a.scale, row, asked);
+        float rs = 1.f;
+        bool have_rs = false;
         for (int i = threadIdx.x; i < a.hd; i += 2 * blockDim.x) {
             const StreamKSpan s0 = (i == i_first) ? sp0 : streamk_span(a.k, row, col0 + i);
             const int i2 = i + blockDim.x;                  // a thread's elements go two at a time
             if (i2 < a.hd) {
                 float f0, f1;
                 streamk_sum_pair(a.k, s0, streamk_span(a.k, row, col0 + i2), row, col0 + i, col0 + i2, f0, f1);
-                const __nv_bfloat16 y0 = __float2bfloat16_rn(f0), y1 = __float2bfloat16_rn(f1);
+                if (!have_rs) { rs = row_scale_finish(a.scale, row, asked); have_rs = true; }
+                const __nv_bfloat16 y0 = __float2bfloat16_rn(f0 * rs), y1 = __float2bfloat16_rn(f1 * rs);
                 dst_row[i] = y0; dst_row[i2] = y1;
                 if (dst) { dst[i] = y0; dst[i2] = y1; }
             } else {
-                const __nv_bfloat16 y = __float2bfloat16_rn(streamk_sum(a.k, s0, row, col0 + i));
+                const float f = streamk_sum(a.k, s0, row, col0 + i);
+                if (!have_rs) { rs = row_scale_finish(a.scale, row, asked); have_rs = true; }
+                const __nv_bfloat16 y = __float2bfloat16_rn(f * rs);
                 dst_row[i] = y;
                 if (dst) dst[i] = y;
             }
@@ -248,14 +339,18 @@ __global__ void streamk_reduce_rope_kv_kernel(ReduceRopeArgs a) {
 extern "C" int braid_streamk_reduce_rope_kv(const float* partial, const int* plan, void* qkv, const float* inv_freq,
                                             const int* positions, const int* token_seq, const int* page_table,
                                             void* cache, int rows, int nqh, int nkh, int hd, int rope_dim, int adjacent,
-                                            int page_size, int table_cols, int num_pages, int* error_flag, void* stream) {
+                                            int page_size, int table_cols, int num_pages, const float* scale_shares,
+                                            int scale_n_shares, long long scale_stride, float scale_width, float scale_eps,
+                                            int* error_flag, void* stream) {
     if (rows <= 0) return BRAID_OK;
     if (nqh <= 0 || nkh <= 0 || hd <= 0) BRAID_REFUSE("reduce_rope_kv: heads/head_dim must be positive");
     if (rope_dim < 0 || rope_dim > hd || (rope_dim & 1)) BRAID_REFUSE("reduce_rope_kv: rope_dim=%d must be even and <= head_dim=%d", rope_dim, hd);
     if (nqh + 2 * nkh > 65535) BRAID_REFUSE("reduce_rope_kv: %d heads exceed the grid limit", nqh + 2 * nkh);
+    const RowScaleArgs scale{scale_shares, scale_n_shares, scale_stride, scale_width, scale_eps};
+    if (const char* why = row_scale_problem(scale, rows)) BRAID_REFUSE("reduce_rope_kv: row scale: %s", why);
     ReduceRopeArgs a{streamk_from_plan(partial, plan, rows),
                      (__nv_bfloat16*)qkv, inv_freq, positions, token_seq, page_table, (__nv_bfloat16*)cache,
-                     rows, nqh, nkh, hd, rope_dim, adjacent, page_size, table_cols, num_pages, error_flag};
+                     rows, nqh, nkh, hd, rope_dim, adjacent, page_size, table_cols, num_pages, error_flag, scale};
     braid_launch(streamk_reduce_rope_kv_kernel, dim3(rows, nqh + 2 * nkh), dim3(hd >= 128 ? 64 : 32), 0, (cudaStream_t)stream, a);
     BRAID_LAUNCH_CHECK();
 }

@@ -21,6 +21,9 @@
 //                    16..31) and pairs them with a shuffle; out = silu(gate) * up,
 //                 3  float32 partial sums of a run of k blocks ("stream-k"), added up
 //                    by a reduce kernel with one of the epilogues above.
+//               The tokens may come with a row scale still to be applied (rowscale.cuh: the RMSNorm
+//               of the tensor they were made from, left to this product): epilogues 0 and 2, here and in
+//               the reduce kernel, multiply each token's results by it.
 //
 // The kernel is persistent: one CTA per SM walks its share of the work units (output tile
 // x slice of k).  The loader runs ahead across units, and with two accumulator buffers
@@ -33,6 +36,7 @@
 // Replaces the reference's per-row GEMV ops (kernels/megakernel_ops.hip:168-276 linear,
 // :1474-1602 feed-forward, :1783-1842 output head), which run on scalar FMA.
 #include "common.cuh"
+#include "rowscale.cuh"
 #include "streamk.cuh"
 #include "tcgen05.cuh"
 #include "trace.cuh"
@@ -57,6 +61,7 @@ struct GemmTcArgs {
     int max_segs;              // mode 3: partial slots per CTA
     int* error_flag;
     int tile_begin, tile_end;  // the tiles of the walk (tc_tile_coords) that this launch covers
+    RowScaleArgs scale;        // modes 0, 2: a row scale of the tokens, or none
 };
 
 template <int BLOCK_N, int MODE>
@@ -149,6 +154,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     uint64_t* acc_empty = acc_full + 2;                    // [kAccBufs]
     uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+    __shared__ float rs_s[BLOCK_N];            // row scale of the tile's tokens (modes 0, 2 with a.scale)
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 #ifdef BRAID_TRACE
@@ -267,11 +274,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         bool ok = true;
         TcWalk<BLOCK_N, MODE> walk(a);
         TcUnit t;
+        // with a row scale the epilogue threads meet at barriers inside a unit: they then agree on whether
+        // a wait ran out, so that none of them waits at a barrier for one that left
+        const bool scaled = (MODE == 0 || MODE == 2) && a.scale.shares != nullptr;
+        int rs_n0 = -1;
         while (ok && walk.next(t)) {
             // mode 2: every 32 weight rows are 16 gate rows then the 16 up rows of the same outputs,
             // so a warp's lanes 0..15 hold gate and lanes 16..31 hold up of outputs [m - lane % 16 ...]
             const int m = (MODE == 2) ? (t.m0 + quarter * 32) / 2 + (lane & 15) : t.m0 + quarter * 32 + lane;
+            if (scaled && t.n0 != rs_n0) {
+                epilogue_sync();                              // the last unit's readers are done
+                for (int j = threadIdx.x - 64; j < BLOCK_N; j += 128)
+                    rs_s[j] = (t.n0 + j < a.n_rows) ? row_scale_of(a.scale, t.n0 + j) : 0.f;
+                epilogue_sync();
+                rs_n0 = t.n0;
+            }
             ok = mbar_wait(&acc_full[buf], (full_phase >> buf) & 1u, abort_flag);
+            if (scaled) ok = epilogue_all(ok);
             if (!ok) break;
             if (warp == 2 && lane == 0) BRAID_STAMP(trace_row, 5);
             tc_fence_after();
@@ -283,6 +302,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 float v[CH];
                 if (CH == 32) tmem_ld32(trow + c0, v);
                 else tmem_ld16(trow + c0, v);
+                if (scaled) {
+#pragma unroll
+                    for (int i = 0; i < CH; ++i) v[i] *= rs_s[c0 + i];
+                }
                 if (MODE == 2) {
                     // The halves of a warp swap values; the gate half then finishes the even
                     // columns and the up half the odd ones, so all lanes compute and store.
@@ -361,7 +384,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 // token; threads are laid over the line's tiles.
 template <int MODE>
 __global__ void streamk_reduce_kernel(StreamK k, void* __restrict__ out, const float* __restrict__ res,
-                                      int m_out, long long ldo, int out_dtype) {
+                                      int m_out, long long ldo, int out_dtype, RowScaleArgs scale) {
     pdl_trigger();
     constexpr int GROUPS = (MODE == 2) ? 16 : 32;          // groups of four outputs that a tile holds per token
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -380,17 +403,23 @@ __global__ void streamk_reduce_kernel(StreamK k, void* __restrict__ out, const f
     // where the partial sums lie is arithmetic only: done before the wait for the product
     const StreamKSpan sp = streamk_span_of_tile(k, in_line);
     pdl_wait();
+    RowScaleAsked asked;                                  // the row scale travels with the partial sums: one trip
+    if (MODE != 1) row_scale_ask(scale, n, asked);
     float v[4];
     if (MODE == 2) {
         float4 g4, u4;
         streamk_sum4_pair(k, sp, n, c0, c0 + 16, g4, u4);
+        const float rs = row_scale_finish(scale, n, asked);
+        g4.x *= rs; g4.y *= rs; g4.z *= rs; g4.w *= rs;
+        u4.x *= rs; u4.y *= rs; u4.z *= rs; u4.w *= rs;
         v[0] = g4.x / (1.f + expf(-g4.x)) * u4.x;
         v[1] = g4.y / (1.f + expf(-g4.y)) * u4.y;
         v[2] = g4.z / (1.f + expf(-g4.z)) * u4.z;
         v[3] = g4.w / (1.f + expf(-g4.w)) * u4.w;
     } else {
         const float4 s4 = streamk_sum4(k, sp, n, c0);
-        v[0] = s4.x; v[1] = s4.y; v[2] = s4.z; v[3] = s4.w;
+        const float rs = (MODE == 1) ? 1.f : row_scale_finish(scale, n, asked);
+        v[0] = s4.x * rs; v[1] = s4.y * rs; v[2] = s4.z * rs; v[3] = s4.w * rs;
     }
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
@@ -403,15 +432,15 @@ __global__ void streamk_reduce_kernel(StreamK k, void* __restrict__ out, const f
 }
 
 static int launch_streamk_reduce(const StreamK& k, void* out, const float* res, int m_out, long long ldo, int out_dtype,
-                                 int mode, cudaStream_t s) {
+                                 int mode, const RowScaleArgs& scale, cudaStream_t s) {
     const long long tiles = k.w / k.total_kb;
     const long long total = tiles * k.block_n * (mode == 2 ? 16 : 32);
     const int threads = 128;
     const long long blocks = (total + threads - 1) / threads;
     if (blocks > 0x7fffffffLL) BRAID_REFUSE("streamk_reduce: %lld outputs exceed one launch", total);
-    if (mode == 0) braid_launch(streamk_reduce_kernel<0>, dim3((int)blocks), dim3(threads), 0, s, k, out, res, m_out, ldo, out_dtype);
-    else if (mode == 1) braid_launch(streamk_reduce_kernel<1>, dim3((int)blocks), dim3(threads), 0, s, k, out, res, m_out, ldo, out_dtype);
-    else braid_launch(streamk_reduce_kernel<2>, dim3((int)blocks), dim3(threads), 0, s, k, out, res, m_out, ldo, out_dtype);
+    if (mode == 0) braid_launch(streamk_reduce_kernel<0>, dim3((int)blocks), dim3(threads), 0, s, k, out, res, m_out, ldo, out_dtype, scale);
+    else if (mode == 1) braid_launch(streamk_reduce_kernel<1>, dim3((int)blocks), dim3(threads), 0, s, k, out, res, m_out, ldo, out_dtype, scale);
+    else braid_launch(streamk_reduce_kernel<2>, dim3((int)blocks), dim3(threads), 0, s, k, out, res, m_out, ldo, out_dtype, scale);
     BRAID_LAUNCH_CHECK();
 }
 
@@ -507,7 +536,8 @@ extern "C" long long braid_gemm_tc_workspace_bytes(int n_rows, int w_rows, int k
 extern "C" int braid_gemm_tc(const void* x, const void* w, void* out, const float* res, void* workspace,
                              long long workspace_bytes, int out_dtype, int mode, int n_rows, int m_out, int k_in,
                              long long ldx, long long ldw, long long ldo, int block_n, int stream_k,
-                             int* plan_out, int* error_flag, void* stream) {
+                             int* plan_out, const float* scale_shares, int scale_n_shares, long long scale_stride,
+                             float scale_width, float scale_eps, int* error_flag, void* stream) {
     if (n_rows <= 0 || m_out <= 0) return BRAID_OK;
     if (mode < 0 || mode > 2) BRAID_REFUSE("gemm_tc: unknown epilogue %d", mode);
     if (k_in <= 0) BRAID_REFUSE("gemm_tc: k=%d must be positive", k_in);
@@ -519,6 +549,10 @@ extern "C" int braid_gemm_tc(const void* x, const void* w, void* out, const floa
     const int w_rows = (mode == 2) ? 2 * ((m_out + 15) / 16) * 16 : m_out;
     if (!valid_block_n(block_n)) BRAID_REFUSE("gemm_tc: token tile %d is not one of 16, 32, 64, 128, 256", block_n);
     if (stream_k && !workspace) BRAID_REFUSE("gemm_tc: the stream-k form needs a workspace");
+    const RowScaleArgs scale{scale_shares, scale_n_shares, scale_stride, scale_width, scale_eps};
+    if (const char* why = row_scale_problem(scale, n_rows)) BRAID_REFUSE("gemm_tc: row scale: %s", why);
+    if (scale.shares && mode == 1) BRAID_REFUSE("gemm_tc: the residual epilogue takes no row scale");
+    if (scale.shares && plan_out) BRAID_REFUSE("gemm_tc: whoever adds the partial sums up applies the row scale");
     if (stream_k) {
         // the partial sums of every CTA's segments must fit: checked here, on the host, for the very
         // plan the kernel will walk
@@ -542,7 +576,7 @@ extern "C" int braid_gemm_tc(const void* x, const void* w, void* out, const floa
     if (stream_k) p = plan_stream_k(n_rows, w_rows, k_in, block_n);
     const int whole_end = stream_k ? p.tile_begin : all_tiles;       // tiles [0, whole_end) run as whole tiles
     if (whole_end > 0) {
-        GemmTcArgs a{out, res, n_rows, m_out, k_in, ldo, out_dtype, m_tiles, n_tiles, 0, error_flag, 0, whole_end};
+        GemmTcArgs a{out, res, n_rows, m_out, k_in, ldo, out_dtype, m_tiles, n_tiles, 0, error_flag, 0, whole_end, scale};
         dim3 grid((unsigned)(whole_end < sm_count() ? whole_end : sm_count()), 1, 1);
         if (mode == 0) rc = dispatch_tc<0>(block_n, mw, mx, a, grid, s);
         else if (mode == 1) rc = dispatch_tc<1>(block_n, mw, mx, a, grid, s);
@@ -551,7 +585,7 @@ extern "C" int braid_gemm_tc(const void* x, const void* w, void* out, const floa
     }
     if (!stream_k || p.tiles == 0) return BRAID_OK;
     GemmTcArgs a{workspace, nullptr, n_rows, w_rows, k_in, 0, BRAID_F32, p.m_tiles, p.n_tiles, p.max_segs, error_flag,
-                 p.tile_begin, p.tile_begin + p.tiles};
+                 p.tile_begin, p.tile_begin + p.tiles, RowScaleArgs{}};
     rc = dispatch_tc<3>(block_n, mw, mx, a, dim3(p.grid, 1, 1), s);
     if (rc) return rc;
     if (plan_out) {
@@ -561,15 +595,20 @@ extern "C" int braid_gemm_tc(const void* x, const void* w, void* out, const floa
         return BRAID_OK;
     }
     StreamK k{(const float*)workspace, p.grid, p.max_segs, p.total_kb, p.n_tiles, n_rows, block_n, p.w, p.m_tiles, p.tile_begin};
-    return launch_streamk_reduce(k, out, res, m_out, ldo, out_dtype, mode, s);
+    return launch_streamk_reduce(k, out, res, m_out, ldo, out_dtype, mode, scale, s);
 }
 
 // Add up the partial products of an earlier stream-k call made with plan_out (the same
 // reduce the fused call runs): mode 0 store, 1 res + sum, 2 silu(gate) * up.
 extern "C" int braid_streamk_reduce(const float* partial, const int* plan, int n_rows, void* out, const float* res,
-                                    int m_out, long long ldo, int out_dtype, int mode, void* stream) {
+                                    int m_out, long long ldo, int out_dtype, int mode, const float* scale_shares,
+                                    int scale_n_shares, long long scale_stride, float scale_width, float scale_eps,
+                                    void* stream) {
     if (n_rows <= 0 || m_out <= 0) return BRAID_OK;
     if (mode < 0 || mode > 2) BRAID_REFUSE("streamk_reduce: unknown epilogue %d", mode);
     if (mode == 1 && (!res || out_dtype != BRAID_F32)) BRAID_REFUSE("streamk_reduce: the residual epilogue writes float32 and needs res");
-    return launch_streamk_reduce(streamk_from_plan(partial, plan, n_rows), out, res, m_out, ldo, out_dtype, mode, (cudaStream_t)stream);
+    const RowScaleArgs scale{scale_shares, scale_n_shares, scale_stride, scale_width, scale_eps};
+    if (const char* why = row_scale_problem(scale, n_rows)) BRAID_REFUSE("streamk_reduce: row scale: %s", why);
+    if (scale.shares && mode == 1) BRAID_REFUSE("streamk_reduce: the residual epilogue takes no row scale");
+    return launch_streamk_reduce(streamk_from_plan(partial, plan, n_rows), out, res, m_out, ldo, out_dtype, mode, scale, (cudaStream_t)stream);
 }

@@ -111,20 +111,6 @@ __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.comm
 // At most one group of stores may still be reading its staging tile.
 __device__ __forceinline__ void bulk_wait_read_1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
-__device__ __forceinline__ void epilogue_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
-// True only if it is true in all 128 epilogue threads: they meet at barriers inside a tile, so
-// they enter a tile together or not at all.
-__device__ __forceinline__ bool epilogue_all(bool ok) {
-    uint32_t r;
-    asm volatile(
-        "{\n\t.reg .pred p, q;\n\t"
-        "setp.ne.u32 q, %1, 0;\n\t"
-        "bar.red.and.pred p, 1, 128, q;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(r) : "r"((uint32_t)ok) : "memory");
-    return r != 0;
-}
-
 struct T2Unit { int m0, n0; };
 
 struct T2Walk {

@@ -130,6 +130,21 @@ __host__ __device__ constexpr uint32_t umma_idesc_bf16_b_mn(int m, int n) {
     return (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
+// The 128 epilogue threads (warps 2..5 of the GEMM kernels) meet at named barrier 1.
+__device__ __forceinline__ void epilogue_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+// True only if it is true in all 128 epilogue threads: where they meet at barriers inside a
+// unit of work, they enter it together or not at all.
+__device__ __forceinline__ bool epilogue_all(bool ok) {
+    uint32_t r;
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t"
+        "setp.ne.u32 q, %1, 0;\n\t"
+        "bar.red.and.pred p, 1, 128, q;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(r) : "r"((uint32_t)ok) : "memory");
+    return r != 0;
+}
+
 // ------------------------------------------------------------------ host side
 // cuTensorMapEncodeTiled through the runtime's driver entry point lookup (no link against libcuda).
 typedef CUresult (*TcEncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,

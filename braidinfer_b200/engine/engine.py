@@ -37,7 +37,7 @@ class Engine:
     def __init__(self, config_dict: Optional[Mapping], tensors_or_folder, *, dtype="bfloat16", max_tokens: int = 8192,
                  max_slots: Optional[int] = None, device: str = "cuda:0", gemm_backend: str = "auto",
                  attention_backend: str = "auto", row_multiple: int = 1, use_graphs: bool = True,
-                 fuse_reduce: bool = True, verbose: bool = True, spec=None) -> None:
+                 fuse_reduce: bool = True, scaled_norm: bool = True, verbose: bool = True, spec=None) -> None:
         """`config_dict` (config.json's content) picks the architecture and its description of
         parts; or pass a `ModelSpec` as `spec` directly (then `config_dict` may be None)."""
         from ..csrc.api import get_kernels
@@ -52,7 +52,8 @@ class Engine:
         else:
             self.arch, self.config, self.spec = None, None, spec
         self.rt = Runtime(act_dtype=self.dtype, device=self.device, kernels=self.kernels,
-                          gemm_backend=gemm_backend, attention_backend=attention_backend, fuse_reduce=fuse_reduce)
+                          gemm_backend=gemm_backend, attention_backend=attention_backend, fuse_reduce=fuse_reduce,
+                          scaled_norm=scaled_norm)
         self.model = DecoderModel(self.spec, self.rt)
         specs = self.model.tensor_specs()
         if isinstance(tensors_or_folder, (str, os.PathLike)):

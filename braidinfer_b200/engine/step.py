@@ -52,6 +52,12 @@ class StepContext:
     # know about this calls `resolve(tensor)` first, or is handed a resolved tensor by the
     # block.  At most one sum is deferred at a time.
     deferred: dict = field(default_factory=dict)
+    # Row scales.  In a step of few tokens a norm may leave its own scale (rsqrt(mean square + eps), one
+    # number a row) to the product that reads its output, if the block says that this reader takes row
+    # scales: the norm's output then holds the rows times the norm's weights only, and `row_scales` maps
+    # it (by data pointer) to the scale (csrc.api.RowScale).  The reader takes it with `take_row_scale`
+    # and owes it to its results; a scale that nobody took by the end of the block is an error.
+    row_scales: dict = field(default_factory=dict)
     kernels: object = None
 
     def defer(self, tensor: torch.Tensor, handle, kind: str) -> None:
@@ -61,6 +67,14 @@ class StepContext:
         """(handle, kind) if `tensor` is waiting for a deferred sum (which the caller now
         owns and must add), else None."""
         return self.deferred.pop(tensor.data_ptr(), None)
+
+    def set_row_scale(self, tensor: torch.Tensor, scale) -> None:
+        self.row_scales[tensor.data_ptr()] = scale
+
+    def take_row_scale(self, tensor: torch.Tensor):
+        """The row scale that `tensor` still wants applied to whatever is computed from it (the caller
+        now owes it), or None."""
+        return self.row_scales.pop(tensor.data_ptr(), None)
 
     def resolve(self, tensor: torch.Tensor) -> torch.Tensor:
         """Complete `tensor` now with the plain reduce kernel, if a sum is deferred on it."""
@@ -82,6 +96,7 @@ class StepContext:
             if self.kernels is not None and self.kernels.pending_partial is handle:
                 self.kernels.pending_partial = None
         self.deferred.clear()
+        self.row_scales.clear()
 
 
 class _Shaped:

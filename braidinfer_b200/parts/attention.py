@@ -59,12 +59,15 @@ class GQAAttention(Mixer):
         kind = "window" if self.window else "full"
         return CacheRequest(kind, self.nkh, self.hd, self.window)
 
+    def takes_row_scale(self) -> bool:
+        return self.qkv.takes_row_scale()
+
     def forward(self, x, residual, ctx, cache, state):
         if cache is None:
             raise RuntimeError("gqa_attention needs a cache view")
         rt = self.rt
         fused = self.pe.accepts_deferred
-        qkv = self.qkv.forward(x, defer_to=ctx if fused else None)
+        qkv = self.qkv.forward(x, defer_to=ctx if fused else None, in_scale=ctx.take_row_scale(x))
         self.pe.encode_and_store(qkv, self.nqh, self.nkh, ctx, cache)
         rows = x.shape[0]
         out = rt.empty(rows, self.nqh * self.hd)

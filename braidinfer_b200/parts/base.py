@@ -27,6 +27,12 @@ class Part:
     # says so here; every other part is handed tensors that are already complete.
     accepts_deferred = False
 
+    def takes_row_scale(self) -> bool:
+        """A mixer or feed-forward that looks up `ctx.take_row_scale(x)` for its input and applies the
+        scale it finds (see StepContext.row_scales) answers True; only then is it ever handed rows whose
+        norm is not complete."""
+        return False
+
     def __init__(self, params: dict, prefix: str, runtime) -> None:
         self.params = dict(params)
         self.prefix = prefix
@@ -47,7 +53,11 @@ class Norm(Part):
 
         As a layer's norm it is called with (x, ctx) and returns every row.  As the model's
         final norm it is called with `row_index` (int32 on the device) and `rows`: it then
-        returns the `rows` rows x[row_index[i]] only, normalised, and leaves x as it is."""
+        returns the `rows` rows x[row_index[i]] only, normalised, and leaves x as it is.
+
+        A norm with `accepts_deferred` is also passed `reader_takes_row_scale=` by the block: if
+        true, it may return its rows without their scale and register the scale with
+        `ctx.set_row_scale(out, scale)` for the reader to apply (StepContext.row_scales)."""
         raise NotImplementedError
 
 

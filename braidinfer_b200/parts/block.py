@@ -15,13 +15,18 @@ class PreNormResidualBlock(Block):
     def forward(self, h, ctx, cache, state):
         # h may still wait for a deferred sum (see StepContext.deferred); a norm that
         # accepts that adds it up in its own kernel, any other part gets h completed first
-        if not self.mixer_norm.accepts_deferred:
-            ctx.resolve(h)
-        x = self.mixer_norm.forward(h, ctx)
+        x = self._norm(self.mixer_norm, h, ctx, self.mixer)
         h = self.mixer.forward(x, h, ctx, cache, state)
         if self.feed_forward is not None:
-            if not self.feed_forward_norm.accepts_deferred:
-                ctx.resolve(h)
-            x = self.feed_forward_norm.forward(h, ctx)
+            x = self._norm(self.feed_forward_norm, h, ctx, self.feed_forward)
             h = self.feed_forward.forward(x, h, ctx)
+        if ctx.row_scales:
+            raise RuntimeError("a part left a row scale unapplied (see StepContext.row_scales)")
         return h
+
+    @staticmethod
+    def _norm(norm, h, ctx, reader):
+        if not norm.accepts_deferred:
+            return norm.forward(ctx.resolve(h), ctx)
+        # a norm that knows deferred sums may also leave its scale to a reader that takes row scales
+        return norm.forward(h, ctx, reader_takes_row_scale=bool(reader.takes_row_scale()))

@@ -35,6 +35,9 @@ class SwiGLU(FeedForward):
         self.gate_up.load(tensors)
         self.down.load(tensors)
 
+    def takes_row_scale(self) -> bool:
+        return self.gate_up.takes_row_scale()
+
     def forward(self, x, residual, ctx):
-        act = self.gate_up.forward(x, swiglu=True)
+        act = self.gate_up.forward(x, swiglu=True, in_scale=ctx.take_row_scale(x) if ctx is not None else None)
         return self.down.forward(act, residual=residual, defer_to=ctx)

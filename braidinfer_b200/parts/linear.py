@@ -43,6 +43,11 @@ def stream_k_pays(rows: int, w_rows: int, k_in: int, sms: Optional[int] = None) 
     return fill < (0.8 if rows <= 32 else 0.7)
 
 
+# Rows up to which a norm may leave its scale to the next product: beyond the token tiles of the
+# one-SM kernel the products run on pairs of SMs, which take no row scale.
+ROW_SCALE_MAX_ROWS = 128
+
+
 class Linear:
     def __init__(self, rt, names: Sequence[str], out_features: Sequence[int], in_features: int,
                  gate_up: bool = False) -> None:
@@ -80,18 +85,32 @@ class Linear:
     def total_out(self) -> int:
         return sum(self.out_features)
 
+    def takes_row_scale(self) -> bool:
+        """Whether `forward` can apply a row scale that its input still wants (`in_scale`): the
+        tensor-core products do, in their epilogues and in the kernels that add up their partial sums."""
+        w = self.weight
+        return (self.rt.gemm_backend == "auto" and self.rt.act_dtype == torch.bfloat16 and w is not None
+                and w.dtype == torch.bfloat16 and self.in_features % 8 == 0 and w.stride(0) % 8 == 0
+                and w.data_ptr() % 16 == 0 and (not self.gate_up or self.interleaved))
+
     def forward(self, x: torch.Tensor, *, out_dtype: Optional[torch.dtype] = None,
-                residual: Optional[torch.Tensor] = None, swiglu: bool = False, defer_to=None) -> torch.Tensor:
+                residual: Optional[torch.Tensor] = None, swiglu: bool = False, defer_to=None,
+                in_scale=None) -> torch.Tensor:
         """x [rows, in].  Plain: returns [rows, out] in `out_dtype` (default x's type).
         `residual` (float32 [rows, out]): returns residual + product, written in place.
         `swiglu`: the weight holds gate rows then up rows; returns silu(gate) * up.
         `defer_to` (a StepContext): when the product runs in its stream-k form, leave the
         adding-up of its partial sums to whoever reads the result next
-        (`StepContext.deferred`); the returned tensor is complete only after that."""
+        (`StepContext.deferred`); the returned tensor is complete only after that.
+        `in_scale` (csrc.api.RowScale): x's rows still want this scale; the product applies it to
+        its results (only where `takes_row_scale()`, and not with a residual)."""
         K = self.rt.kernels
         w = self.weight
         rows = x.shape[0]
         w_rows = w.shape[0]
+        if in_scale is not None and (residual is not None or not self.takes_row_scale() or x.dtype != torch.bfloat16
+                                     or not K.gemm_tc_eligible(x, w)):
+            raise RuntimeError("this product cannot apply a row scale (see Linear.takes_row_scale)")
         if w.dtype == torch.float32 and x.dtype != torch.float32:
             # a weight stored in 32-bit stays so: this product runs in float32
             x32 = torch.empty(x.shape, dtype=torch.float32, device=x.device)
@@ -125,7 +144,7 @@ class Linear:
                 if not use_tc:
                     raise RuntimeError("interleaved gate/up weights need the tensor-core product; its input rows "
                                        "must be 16-byte aligned bfloat16")
-                K.gemm_tc(x, w, out, swiglu=True, stream_k=sk)
+                K.gemm_tc(x, w, out, swiglu=True, stream_k=sk, in_scale=in_scale)
             else:
                 gu = torch.empty((rows, w_rows), dtype=x.dtype, device=x.device)
                 K.gemm_simt(x, w, gu)
@@ -133,9 +152,9 @@ class Linear:
             return out
         out = torch.empty((rows, w_rows), dtype=out_dtype or x.dtype, device=x.device)
         if can_defer:
-            defer_to.defer(out, K.gemm_tc_partial(x, w), "store")
+            defer_to.defer(out, K.gemm_tc_partial(x, w, in_scale=in_scale), "store")
         elif use_tc:
-            K.gemm_tc(x, w, out, stream_k=sk)
+            K.gemm_tc(x, w, out, stream_k=sk, in_scale=in_scale)
         else:
             K.gemm_simt(x, w, out)
         return out

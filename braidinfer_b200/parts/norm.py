@@ -9,6 +9,7 @@ from typing import Dict, Optional
 import torch
 
 from .base import NORMS, Norm
+from .linear import ROW_SCALE_MAX_ROWS
 from .spec import TensorSpec
 
 
@@ -32,10 +33,19 @@ class RMSNorm(Norm):
         self.weight = tensors[self.name]
 
     def forward(self, x: torch.Tensor, ctx=None, row_index: Optional[torch.Tensor] = None,
-                rows: Optional[int] = None) -> torch.Tensor:
+                rows: Optional[int] = None, reader_takes_row_scale: bool = False) -> torch.Tensor:
         n = rows if rows is not None else x.shape[0]
         out = self.rt.empty(n, self.width)
         d = ctx.take_deferred(x) if ctx is not None else None
+        if (reader_takes_row_scale and self.rt.scaled_norm and ctx is not None and row_index is None and out.dtype == torch.bfloat16
+                and n <= ROW_SCALE_MAX_ROWS and self.width % 4 == 0 and self.rt.gemm_backend == "auto"):
+            # a step of few tokens: x is completed, `out` = x * weight, and the scale is left to the reader.
+            # The kernel works on 512 columns of a row per CTA instead of on whole rows.
+            if d is not None and d[1] != "residual":
+                raise RuntimeError("a norm can only complete a deferred residual sum")
+            ctx.set_row_scale(out, self.rt.kernels.streamk_reduce_prep(d[0] if d is not None else None, x, self.weight,
+                                                                       out, self.eps))
+            return out
         if d is not None:
             handle, kind = d
             if kind != "residual":

@@ -20,6 +20,9 @@ class Runtime:
     # Let products of a few tokens leave their partial sums to the next norm or to the
     # rotary encoding, which add them up in their own kernel (fewer launches per step).
     fuse_reduce: bool = True
+    # In steps of up to 128 tokens, let an RMSNorm leave its scale to the product that reads its output
+    # (csrc/rowscale.cuh), so that the kernel before it works on parts of rows instead of whole rows.
+    scaled_norm: bool = True
 
     @property
     def is_f32(self) -> bool:

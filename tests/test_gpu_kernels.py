@@ -489,13 +489,79 @@ def test_stream_k_refuses_a_workspace_that_is_too_small_and_takes_any_token_tile
     ws = torch.empty(need // 4, dtype=torch.float32, device=DEV)
     out = torch.empty(300, 512, device=DEV, dtype=torch.bfloat16)
     args = lambda nbytes, tile: (x.data_ptr(), w.data_ptr(), out.data_ptr(), None, ws.data_ptr(), nbytes, BF16, 0,
-                                 300, 512, 256, 256, 256, 512, tile, 1, None, K._error_flag.data_ptr() + 4, K._stream())
+                                 300, 512, 256, 256, 256, 512, tile, 1, None, None, 0, 0, 0.0, 0.0,
+                                 K._error_flag.data_ptr() + 4, K._stream())
     assert K.lib.braid_gemm_tc(*args(need - 4, 128)) != 0            # refused on the host: nothing is launched
     assert b"bytes of workspace" in K.lib.braid_last_error()
     assert K.lib.braid_gemm_tc(*args(need, 48)) != 0 and b"token tile" in K.lib.braid_last_error()
     assert K.lib.braid_gemm_tc(*args(need, 128)) == 0
     K.check_device_errors()
     assert (out.double() - want).abs().max().item() < want.abs().max().item() / 128
+
+
+def shares_of(t, n_shares):
+    """A tensor's sums of squares by row, cut into shares of unequal size (as a kernel may leave them)."""
+    n, width = t.shape
+    cuts = [0] + sorted(torch.randperm(width - 1, generator=torch.Generator().manual_seed(n_shares))[:n_shares - 1].add(1).tolist()) + [width]
+    shares = torch.zeros(n_shares, -(-n // 4) * 4, device=DEV)
+    for i in range(n_shares):
+        shares[i, :n] = t[:, cuts[i]:cuts[i + 1]].double().pow(2).sum(1).float()
+    return shares
+
+
+@pytest.mark.parametrize("n, width, k", [(8, 4096, 1024), (3, 328, 520), (64, 1000, 256), (1, 72, 64), (20, 5120, 128),
+                                         (128, 516, 192)])
+def test_reduce_and_the_inputs_of_a_scaled_norm(K, n, width, k):
+    """h += partial sums, bfloat16(h * w) and the shares of the rows' sums of squares, by CTAs of 512 columns:
+    float64 beside it, the bits of the plain reduce for h, and the same kernel on a complete h."""
+    x, wt = rnd(n, k, dtype=torch.bfloat16, scale=0.5), rnd(width, k, dtype=torch.bfloat16, scale=0.5, seed=1)
+    gamma = (1 + rnd(width, seed=3, scale=0.3)).to(torch.bfloat16)
+    h0 = rnd(n, width, seed=4)
+    want_h = h0.double() + x.double() @ wt.double().t()
+    h, hb = h0.clone(), torch.full((n, width), 9.0, device=DEV, dtype=torch.bfloat16)
+    scale = K.streamk_reduce_prep(K.gemm_tc_partial(x, wt), h, gamma, hb, 1e-5)
+    assert K.pending_partial is None
+    big = max(1.0, want_h.abs().max().item())
+    assert (h.double() - want_h).abs().max() < 1e-5 * big
+    plain = h0.clone()
+    K.gemm_tc(x, wt, plain, residual=plain, stream_k=True)
+    assert torch.equal(h, plain)
+    want_hb = h.double() * gamma.double()
+    assert ((hb.double() - want_hb).abs() <= want_hb.abs() / 250 + 1e-30).all()          # one bfloat16 rounding
+    want_rs = torch.rsqrt(h.double().pow(2).mean(1) + 1e-5)
+    assert scale.shares.shape[0] == -(-width // 512)
+    assert ((scale.values()[:n].double() - want_rs).abs() / want_rs).max() < 1e-5
+    # a complete h: the same numbers without partial sums
+    hb2 = torch.empty_like(hb)
+    again = K.streamk_reduce_prep(None, h, gamma, hb2, 1e-5)
+    assert torch.equal(hb, hb2) and torch.equal(scale.shares[:, :n], again.shares[:, :n])
+    K.check_device_errors()
+
+
+@pytest.mark.parametrize("n, m, k, sk", [(8, 512, 256, False), (100, 640, 512, False), (40, 328, 264, False),
+                                         (8, 4096, 512, True), (20, 1408, 1024, True), (100, 640, 2048, True)])
+def test_products_apply_a_row_scale(K, n, m, k, sk):
+    """Whole tiles in their epilogue, stream-k products in the kernel that adds them up: store and SwiGLU."""
+    from braidinfer_b200.csrc.api import RowScale, interleave_gate_up
+    x, w = rnd(n, k, dtype=torch.bfloat16, scale=0.5), rnd(m, k, dtype=torch.bfloat16, scale=0.5, seed=1)
+    sc = RowScale(shares_of(rnd(n, 200, seed=5, scale=2.0), 3), 200, 1e-5)
+    rs = sc.values()[:n].double()[:, None]
+    assert ((rs[:, 0] - torch.rsqrt(rnd(n, 200, seed=5, scale=2.0).double().pow(2).mean(1) + 1e-5)).abs() / rs[:, 0]).max() < 1e-5
+    ref = (x.double() @ w.double().t()) * rs
+    big = max(1.0, ref.abs().max().item())
+    out = torch.empty(n, m, device=DEV)
+    K.gemm_tc(x, w, out, stream_k=sk, in_scale=sc)
+    assert (out.double() - ref).abs().max() < 1e-5 * big
+    inter = m // 2
+    g, u = ref[:, :inter], ref[:, inter:2 * inter]
+    want = g / (1 + torch.exp(-g)) * u
+    act = torch.empty(n, inter, device=DEV, dtype=torch.bfloat16)
+    K.gemm_tc(x, interleave_gate_up(w[:inter], w[inter:2 * inter]), act, swiglu=True, stream_k=sk, in_scale=sc)
+    assert ((act.double() - want).abs() <= want.abs() / 100 + 1e-5 * big * (1.1 * u.abs() + g.abs()) + 1e-3).all()
+    with pytest.raises(KernelError, match="row scale"):
+        K.gemm_tc(x, w, out, residual=out, stream_k=sk, in_scale=sc)
+    K.pending_partial = None
+    K.check_device_errors()
 
 
 def test_tensor_core_product_refuses_what_tma_cannot_address(K):
@@ -621,3 +687,12 @@ def test_fused_reduce_rope_cache_write(K, pairing, hd, nqh, nkh):
     K.check_device_errors()
     assert torch.equal(qkv_a[:-2], qkv_b[:-2]) and torch.equal(cache_a, cache_b)
     assert float(qkv_b[-2:].abs().max()) == 0.0              # padding rows are not written
+    # the same with a row scale on the product's input: product + reduce with the scale, then the plain rotation
+    from braidinfer_b200.csrc.api import RowScale
+    sc = RowScale(shares_of(rnd(rows, 200, seed=5, scale=2.0), 3), 200, 1e-5)
+    K.gemm_tc(x, w, qkv_a, stream_k=True, in_scale=sc)
+    K.rope_kv_write(qkv_a, inv, t(pos), t(seq), table, cache_a, nqh, nkh, hd, hd, pairing == "adjacent", 64)
+    K.streamk_reduce_rope_kv(K.gemm_tc_partial(x, w, in_scale=sc), qkv_b, inv, t(pos), t(seq), table, cache_b, nqh, nkh,
+                             hd, hd, pairing == "adjacent", 64)
+    K.check_device_errors()
+    assert torch.equal(qkv_a[:-2], qkv_b[:-2]) and torch.equal(cache_a, cache_b)

@@ -179,18 +179,25 @@ def test_trace_run_as_a_program(tmp_path):
 
 def test_fused_and_unfused_reduces_agree(model):
     """Steps of a few tokens leave the adding-up of their stream-k products to the next norm
-    and to the rotary encoding; switching that off must give the same logits."""
+    and to the rotary encoding; switching that off must give the same logits.  The same steps with
+    the norms' scales applied by the norms themselves (`scaled_norm=False`) round once at another
+    place: the same logits within the bfloat16 tolerance, and again the same with and without fusing."""
     name, folder, orc, prompts = model
-    outs = []
-    for fuse in (True, False):
-        eng = engine(folder, "bfloat16", fuse_reduce=fuse, use_graphs=False)
-        slots = [eng.open() for _ in prompts[:3]]
-        a = eng.step(list(zip(slots, prompts[:3])), want="last")
-        b = eng.step([(s, [7]) for s in slots], want="last")
-        c = eng.step([(s, [9, 11]) for s in slots], want="all")
-        outs.append(torch.cat([a, b, c]).clone())
-        eng.check()
-    assert (outs[0] - outs[1]).abs().max().item() < 1e-6
+    outs = {}
+    for scaled in (True, False):
+        for fuse in (True, False):
+            eng = engine(folder, "bfloat16", fuse_reduce=fuse, scaled_norm=scaled, use_graphs=False)
+            slots = [eng.open() for _ in prompts[:3]]
+            a = eng.step(list(zip(slots, prompts[:3])), want="last")
+            b = eng.step([(s, [7]) for s in slots], want="last")
+            c = eng.step([(s, [9, 11]) for s in slots], want="all")
+            outs[scaled, fuse] = torch.cat([a, b, c]).clone()
+            eng.check()
+        assert (outs[scaled, True] - outs[scaled, False]).abs().max().item() < 1e-6
+    assert 0 < (outs[True, True] - outs[False, True]).abs().max().item() < TOL["bfloat16"]
+    want = torch.stack([orc.logits(p + [7])[-1] for p in prompts[:3]])
+    for scaled in (True, False):
+        assert max_err(outs[scaled, True][3:6], want) < TOL["bfloat16"]
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
