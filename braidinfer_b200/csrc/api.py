@@ -87,9 +87,11 @@ class PartialProduct:
     """Partial products of a stream-k GEMM waiting in the workspace to be added up."""
 
     def __init__(self, workspace: torch.Tensor, plan, n_rows: int, w_rows: int,
-                 in_scale: Optional["RowScale"] = None) -> None:
+                 rs_rows: Optional[torch.Tensor] = None) -> None:
         self.workspace, self.plan, self.n_rows, self.w_rows = workspace, plan, n_rows, w_rows
-        self.in_scale = in_scale      # a row scale of the product's input that the adding-up has to apply
+        # the scale of every row that the product's input still wants (float32 [n_rows], written by the
+        # product's kernel from the RowScale it was given): the adding-up has to apply it
+        self.rs_rows = rs_rows
 
 
 class Kernels:
@@ -137,16 +139,16 @@ class Kernels:
         scale = [c_void_p, c_int, c_longlong, c_float, c_float]        # RowScale.args()
         L.braid_gemm_tc.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int,
                                     c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_int, c_int,
-                                    c_void_p] + scale + [c_void_p, c_void_p]
+                                    c_void_p] + scale + [c_void_p, c_void_p, c_void_p]
         L.braid_streamk_reduce_prep.argtypes = [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                                 c_longlong, c_int, c_void_p]
         L.braid_gemm_tc2.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                      c_longlong, c_longlong, c_longlong, c_int, c_void_p, c_void_p]
         L.braid_streamk_reduce.argtypes = [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_longlong,
-                                           c_int, c_int] + scale + [c_void_p]
+                                           c_int, c_int, c_void_p, c_void_p]
         L.braid_streamk_reduce_norm.argtypes = [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int,
                                                 c_void_p, c_int, c_int, c_float, c_void_p]
-        L.braid_streamk_reduce_rope_kv.argtypes = [c_void_p] * 8 + [c_int] * 9 + scale + [c_void_p, c_void_p]
+        L.braid_streamk_reduce_rope_kv.argtypes = [c_void_p] * 8 + [c_int] * 9 + [c_void_p, c_void_p, c_void_p]
         L.braid_gemm_tc_workspace_bytes.argtypes = [c_int, c_int, c_int, c_int]
         L.braid_gemm_tc_workspace_bytes.restype = c_longlong
         L.braid_argmax.argtypes = [c_void_p, c_longlong, c_void_p, c_int, c_int, c_void_p, c_void_p]
@@ -390,7 +392,13 @@ class Kernels:
                                            ws.numel() * 4 if ws is not None else 0,
                                            dtype_code(out.dtype), mode, n, m, k, x.stride(0), w.stride(0),
                                            out.stride(0), block_n, int(stream_k), None, *_scale_args(in_scale),
+                                           _ptr(self._rs_rows(n, x.device) if stream_k and in_scale is not None else None),
                                            self._error_flag.data_ptr() + 4, self._stream()), "gemm_tc")
+
+    @staticmethod
+    def _rs_rows(n: int, device) -> torch.Tensor:
+        """Room for every row's scale (a stream-k product with a row scale writes them for the adding-up)."""
+        return torch.empty(-(-n // 4) * 4, dtype=torch.float32, device=device)
 
     def gemm_tc_pair(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor,
                      residual: Optional[torch.Tensor] = None, swiglu: bool = False, direct_out: bool = False) -> None:
@@ -423,12 +431,13 @@ class Kernels:
         block_n = token_tile(n)
         ws = self._stream_k_workspace(n, w_rows, k, block_n)
         plan = (c_int * 8)()
+        rs = self._rs_rows(n, x.device) if in_scale is not None else None
         self.launches += 1
         self._check(self.lib.braid_gemm_tc(x.data_ptr(), w.data_ptr(), None, None, ws.data_ptr(), ws.numel() * 4,
                                            F32, 0, n, w_rows, k, x.stride(0), w.stride(0), 0, block_n, 1, plan,
-                                           *_NO_SCALE,          # whoever adds the sums up applies the scale
+                                           *_scale_args(in_scale), _ptr(rs),
                                            self._error_flag.data_ptr() + 4, self._stream()), "gemm_tc_partial")
-        p = PartialProduct(ws, plan, n, w_rows, in_scale)
+        p = PartialProduct(ws, plan, n, w_rows, rs)
         self.pending_partial = p
         return p
 
@@ -444,7 +453,7 @@ class Kernels:
         self._close_partial(p)
         self.launches += 1
         self._check(self.lib.braid_streamk_reduce(p.workspace.data_ptr(), p.plan, p.n_rows, out.data_ptr(), _ptr(residual),
-                                                  m, out.stride(0), dtype_code(out.dtype), mode, *_scale_args(p.in_scale),
+                                                  m, out.stride(0), dtype_code(out.dtype), mode, _ptr(p.rs_rows),
                                                   self._stream()),
                     "streamk_reduce")
 
@@ -453,7 +462,7 @@ class Kernels:
         """h += sum of the partial products (written back unless rows are gathered), then
         out = RMSNorm(h) * w, in one kernel."""
         rows_out, width = out.shape
-        if p.in_scale is not None:
+        if p.rs_rows is not None:
             raise KernelError("this partial product carries a row scale, which reduce + norm does not apply")
         self._close_partial(p)
         self.launches += 1
@@ -474,7 +483,7 @@ class Kernels:
         self._check(self.lib.braid_streamk_reduce_rope_kv(
             p.workspace.data_ptr(), p.plan, qkv.data_ptr(), inv_freq.data_ptr(), positions.data_ptr(),
             token_seq.data_ptr(), _ptr(page_table), _ptr(cache), qkv.shape[0], nqh, nkh, hd, rope_dim, int(adjacent),
-            page_size, cols, num_pages, *_scale_args(p.in_scale), self._error_flag.data_ptr(), self._stream()),
+            page_size, cols, num_pages, _ptr(p.rs_rows), self._error_flag.data_ptr(), self._stream()),
             "streamk_reduce_rope_kv")
 
     def streamk_reduce_prep(self, p: Optional["PartialProduct"], h: torch.Tensor, w: torch.Tensor, out: torch.Tensor,
@@ -488,7 +497,7 @@ class Kernels:
         cols = self.lib.braid_streamk_reduce_prep_cols()
         shares = torch.empty((-(-width // cols), -(-rows // 4) * 4), dtype=torch.float32, device=h.device)
         if p is not None:
-            if p.in_scale is not None:
+            if p.rs_rows is not None:
                 raise KernelError("this partial product carries a row scale, which the residual sum does not apply")
             self._close_partial(p)
         self.launches += 1

@@ -233,7 +233,7 @@ struct ReduceRopeArgs {
     int rows, nqh, nkh, hd, rope_dim, adjacent;
     int page_size, table_cols, num_pages;
     int* error_flag;
-    RowScaleArgs scale;          // a row scale that the product's input still wants (rowscale.cuh), or none
+    const float* rs_rows;        // the scale of every row that the product's input still wants (rowscale.cuh), or null
 };
 
 __global__ void streamk_reduce_rope_kv_kernel(ReduceRopeArgs a) {
@@ -274,10 +274,7 @@ __global__ void streamk_reduce_rope_kv_kernel(ReduceRopeArgs a) {
             sp1 = streamk_span(a.k, row, col0 + (a.adjacent ? 2 * p_first + 1 : p_first + half));
         }
         pdl_wait();
-        RowScaleAsked asked;                               // the row scale travels with the first partial sums: one trip
-        row_scale_ask(a.scale, row, asked);
-        float rs = 1.f;
-        bool have_rs = false;
+        const float rs = a.rs_rows ? a.rs_rows[row] : 1.f;     // asked for with the first partial sums: one trip
         for (int p = threadIdx.x; p < half; p += blockDim.x) {
             const int i0 = a.adjacent ? 2 * p : p;
             const int i1 = a.adjacent ? 2 * p + 1 : p + half;
@@ -291,7 +288,6 @@ __global__ void streamk_reduce_rope_kv_kernel(ReduceRopeArgs a) {
             // the product is rounded to bfloat16 before it is rotated, as after a plain product
             float f0, f1;
             streamk_sum_pair(a.k, s0, s1, row, col0 + i0, col0 + i1, f0, f1);
-            if (!have_rs) { rs = row_scale_finish(a.scale, row, asked); have_rs = true; }
             const float x0 = __bfloat162float(__float2bfloat16_rn(f0 * rs));
             const float x1 = __bfloat162float(__float2bfloat16_rn(f1 * rs));
             const __nv_bfloat16 y0 = __float2bfloat16_rn(x0 * cs - x1 * sn);
@@ -300,7 +296,6 @@ __global__ void streamk_reduce_rope_kv_kernel(ReduceRopeArgs a) {
             dst_row[i1] = y1;
             if (dst) { dst[i0] = y0; dst[i1] = y1; }
         }
-        if (!have_rs) rs = row_scale_finish(a.scale, row, asked);
         for (int i = a.rope_dim + threadIdx.x; i < a.hd; i += blockDim.x) {
             const __nv_bfloat16 y = __float2bfloat16_rn(streamk_sum(a.k, streamk_span(a.k, row, col0 + i), row, col0 + i) * rs);
             dst_row[i] = y;
@@ -311,24 +306,18 @@ __global__ void streamk_reduce_rope_kv_kernel(ReduceRopeArgs a) {
         StreamKSpan sp0 = {};
         if (i_first < a.hd) sp0 = streamk_span(a.k, row, col0 + i_first);
         pdl_wait();
-        RowScaleAsked asked;
-        row_scale_ask(a.scale, row, asked);
-        float rs = 1.f;
-        bool have_rs = false;
+        const float rs = a.rs_rows ? a.rs_rows[row] : 1.f;
         for (int i = threadIdx.x; i < a.hd; i += 2 * blockDim.x) {
             const StreamKSpan s0 = (i == i_first) ? sp0 : streamk_span(a.k, row, col0 + i);
             const int i2 = i + blockDim.x;                  // a thread's elements go two at a time
             if (i2 < a.hd) {
                 float f0, f1;
                 streamk_sum_pair(a.k, s0, streamk_span(a.k, row, col0 + i2), row, col0 + i, col0 + i2, f0, f1);
-                if (!have_rs) { rs = row_scale_finish(a.scale, row, asked); have_rs = true; }
                 const __nv_bfloat16 y0 = __float2bfloat16_rn(f0 * rs), y1 = __float2bfloat16_rn(f1 * rs);
                 dst_row[i] = y0; dst_row[i2] = y1;
                 if (dst) { dst[i] = y0; dst[i2] = y1; }
             } else {
-                const float f = streamk_sum(a.k, s0, row, col0 + i);
-                if (!have_rs) { rs = row_scale_finish(a.scale, row, asked); have_rs = true; }
-                const __nv_bfloat16 y = __float2bfloat16_rn(f * rs);
+                const __nv_bfloat16 y = __float2bfloat16_rn(streamk_sum(a.k, s0, row, col0 + i) * rs);
                 dst_row[i] = y;
                 if (dst) dst[i] = y;
             }
@@ -339,18 +328,15 @@ __global__ void streamk_reduce_rope_kv_kernel(ReduceRopeArgs a) {
 extern "C" int braid_streamk_reduce_rope_kv(const float* partial, const int* plan, void* qkv, const float* inv_freq,
                                             const int* positions, const int* token_seq, const int* page_table,
                                             void* cache, int rows, int nqh, int nkh, int hd, int rope_dim, int adjacent,
-                                            int page_size, int table_cols, int num_pages, const float* scale_shares,
-                                            int scale_n_shares, long long scale_stride, float scale_width, float scale_eps,
+                                            int page_size, int table_cols, int num_pages, const float* rs_rows,
                                             int* error_flag, void* stream) {
     if (rows <= 0) return BRAID_OK;
     if (nqh <= 0 || nkh <= 0 || hd <= 0) BRAID_REFUSE("reduce_rope_kv: heads/head_dim must be positive");
     if (rope_dim < 0 || rope_dim > hd || (rope_dim & 1)) BRAID_REFUSE("reduce_rope_kv: rope_dim=%d must be even and <= head_dim=%d", rope_dim, hd);
     if (nqh + 2 * nkh > 65535) BRAID_REFUSE("reduce_rope_kv: %d heads exceed the grid limit", nqh + 2 * nkh);
-    const RowScaleArgs scale{scale_shares, scale_n_shares, scale_stride, scale_width, scale_eps};
-    if (const char* why = row_scale_problem(scale, rows)) BRAID_REFUSE("reduce_rope_kv: row scale: %s", why);
     ReduceRopeArgs a{streamk_from_plan(partial, plan, rows),
                      (__nv_bfloat16*)qkv, inv_freq, positions, token_seq, page_table, (__nv_bfloat16*)cache,
-                     rows, nqh, nkh, hd, rope_dim, adjacent, page_size, table_cols, num_pages, error_flag, scale};
+                     rows, nqh, nkh, hd, rope_dim, adjacent, page_size, table_cols, num_pages, error_flag, rs_rows};
     braid_launch(streamk_reduce_rope_kv_kernel, dim3(rows, nqh + 2 * nkh), dim3(hd >= 128 ? 64 : 32), 0, (cudaStream_t)stream, a);
     BRAID_LAUNCH_CHECK();
 }

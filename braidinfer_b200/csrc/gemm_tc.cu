@@ -61,7 +61,8 @@ struct GemmTcArgs {
     int max_segs;              // mode 3: partial slots per CTA
     int* error_flag;
     int tile_begin, tile_end;  // the tiles of the walk (tc_tile_coords) that this launch covers
-    RowScaleArgs scale;        // modes 0, 2: a row scale of the tokens, or none
+    RowScaleArgs scale;        // modes 0, 2: a row scale of the tokens, or none; mode 3: see rs_out
+    float* rs_out;             // mode 3 with a scale: CTA 0 writes the scale of every row here, for the kernel that adds up
 };
 
 template <int BLOCK_N, int MODE>
@@ -278,6 +279,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         // a wait ran out, so that none of them waits at a barrier for one that left
         const bool scaled = (MODE == 0 || MODE == 2) && a.scale.shares != nullptr;
         int rs_n0 = -1;
+        if (MODE == 3 && a.rs_out && blockIdx.x == 0) {
+            // the rows' scales from their shares, once, while these warps have nothing else to do: the kernel
+            // that adds the partial sums up then reads one float a row
+            for (int j = threadIdx.x - 64; j < a.n_rows; j += 128) a.rs_out[j] = row_scale_of(a.scale, j);
+        }
         while (ok && walk.next(t)) {
             // mode 2: every 32 weight rows are 16 gate rows then the 16 up rows of the same outputs,
             // so a warp's lanes 0..15 hold gate and lanes 16..31 hold up of outputs [m - lane % 16 ...]
@@ -384,7 +390,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 // token; threads are laid over the line's tiles.
 template <int MODE>
 __global__ void streamk_reduce_kernel(StreamK k, void* __restrict__ out, const float* __restrict__ res,
-                                      int m_out, long long ldo, int out_dtype, RowScaleArgs scale) {
+                                      int m_out, long long ldo, int out_dtype, const float* __restrict__ rs_rows) {
     pdl_trigger();
     constexpr int GROUPS = (MODE == 2) ? 16 : 32;          // groups of four outputs that a tile holds per token
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -403,13 +409,11 @@ __global__ void streamk_reduce_kernel(StreamK k, void* __restrict__ out, const f
     // where the partial sums lie is arithmetic only: done before the wait for the product
     const StreamKSpan sp = streamk_span_of_tile(k, in_line);
     pdl_wait();
-    RowScaleAsked asked;                                  // the row scale travels with the partial sums: one trip
-    if (MODE != 1) row_scale_ask(scale, n, asked);
+    const float rs = (MODE != 1 && rs_rows) ? rs_rows[n] : 1.f;      // asked for with the partial sums: one trip
     float v[4];
     if (MODE == 2) {
         float4 g4, u4;
         streamk_sum4_pair(k, sp, n, c0, c0 + 16, g4, u4);
-        const float rs = row_scale_finish(scale, n, asked);
         g4.x *= rs; g4.y *= rs; g4.z *= rs; g4.w *= rs;
         u4.x *= rs; u4.y *= rs; u4.z *= rs; u4.w *= rs;
         v[0] = g4.x / (1.f + expf(-g4.x)) * u4.x;
@@ -418,7 +422,6 @@ __global__ void streamk_reduce_kernel(StreamK k, void* __restrict__ out, const f
         v[3] = g4.w / (1.f + expf(-g4.w)) * u4.w;
     } else {
         const float4 s4 = streamk_sum4(k, sp, n, c0);
-        const float rs = (MODE == 1) ? 1.f : row_scale_finish(scale, n, asked);
         v[0] = s4.x * rs; v[1] = s4.y * rs; v[2] = s4.z * rs; v[3] = s4.w * rs;
     }
 #pragma unroll
@@ -432,15 +435,15 @@ __global__ void streamk_reduce_kernel(StreamK k, void* __restrict__ out, const f
 }
 
 static int launch_streamk_reduce(const StreamK& k, void* out, const float* res, int m_out, long long ldo, int out_dtype,
-                                 int mode, const RowScaleArgs& scale, cudaStream_t s) {
+                                 int mode, const float* rs_rows, cudaStream_t s) {
     const long long tiles = k.w / k.total_kb;
     const long long total = tiles * k.block_n * (mode == 2 ? 16 : 32);
     const int threads = 128;
     const long long blocks = (total + threads - 1) / threads;
     if (blocks > 0x7fffffffLL) BRAID_REFUSE("streamk_reduce: %lld outputs exceed one launch", total);
-    if (mode == 0) braid_launch(streamk_reduce_kernel<0>, dim3((int)blocks), dim3(threads), 0, s, k, out, res, m_out, ldo, out_dtype, scale);
-    else if (mode == 1) braid_launch(streamk_reduce_kernel<1>, dim3((int)blocks), dim3(threads), 0, s, k, out, res, m_out, ldo, out_dtype, scale);
-    else braid_launch(streamk_reduce_kernel<2>, dim3((int)blocks), dim3(threads), 0, s, k, out, res, m_out, ldo, out_dtype, scale);
+    if (mode == 0) braid_launch(streamk_reduce_kernel<0>, dim3((int)blocks), dim3(threads), 0, s, k, out, res, m_out, ldo, out_dtype, rs_rows);
+    else if (mode == 1) braid_launch(streamk_reduce_kernel<1>, dim3((int)blocks), dim3(threads), 0, s, k, out, res, m_out, ldo, out_dtype, rs_rows);
+    else braid_launch(streamk_reduce_kernel<2>, dim3((int)blocks), dim3(threads), 0, s, k, out, res, m_out, ldo, out_dtype, rs_rows);
     BRAID_LAUNCH_CHECK();
 }
 
@@ -533,11 +536,14 @@ extern "C" long long braid_gemm_tc_workspace_bytes(int n_rows, int w_rows, int k
 // block_n names the token tile: 16, 32, 64, 128 or 256.  With stream_k and plan_out != null only
 // the partial products are computed; plan_out receives {grid, max_segs, total_kb,
 // n_tiles, block_n, w, m_tiles, tile_begin} for the kernel that adds them up (fused_reduce.cu).
+// scale_*: a row scale that x still wants (rowscale.cuh), or null shares.  Whole tiles apply it in their
+// epilogue; the stream-k form writes every row's scale to rs_rows (n_rows floats, required then) and the
+// kernel that adds the partial sums up, here or the caller's, multiplies by it.
 extern "C" int braid_gemm_tc(const void* x, const void* w, void* out, const float* res, void* workspace,
                              long long workspace_bytes, int out_dtype, int mode, int n_rows, int m_out, int k_in,
                              long long ldx, long long ldw, long long ldo, int block_n, int stream_k,
                              int* plan_out, const float* scale_shares, int scale_n_shares, long long scale_stride,
-                             float scale_width, float scale_eps, int* error_flag, void* stream) {
+                             float scale_width, float scale_eps, float* rs_rows, int* error_flag, void* stream) {
     if (n_rows <= 0 || m_out <= 0) return BRAID_OK;
     if (mode < 0 || mode > 2) BRAID_REFUSE("gemm_tc: unknown epilogue %d", mode);
     if (k_in <= 0) BRAID_REFUSE("gemm_tc: k=%d must be positive", k_in);
@@ -552,7 +558,8 @@ extern "C" int braid_gemm_tc(const void* x, const void* w, void* out, const floa
     const RowScaleArgs scale{scale_shares, scale_n_shares, scale_stride, scale_width, scale_eps};
     if (const char* why = row_scale_problem(scale, n_rows)) BRAID_REFUSE("gemm_tc: row scale: %s", why);
     if (scale.shares && mode == 1) BRAID_REFUSE("gemm_tc: the residual epilogue takes no row scale");
-    if (scale.shares && plan_out) BRAID_REFUSE("gemm_tc: whoever adds the partial sums up applies the row scale");
+    if (scale.shares && stream_k && !rs_rows)
+        BRAID_REFUSE("gemm_tc: a stream-k product with a row scale needs rs_rows (n_rows floats) for the rows' scales");
     if (stream_k) {
         // the partial sums of every CTA's segments must fit: checked here, on the host, for the very
         // plan the kernel will walk
@@ -576,7 +583,7 @@ extern "C" int braid_gemm_tc(const void* x, const void* w, void* out, const floa
     if (stream_k) p = plan_stream_k(n_rows, w_rows, k_in, block_n);
     const int whole_end = stream_k ? p.tile_begin : all_tiles;       // tiles [0, whole_end) run as whole tiles
     if (whole_end > 0) {
-        GemmTcArgs a{out, res, n_rows, m_out, k_in, ldo, out_dtype, m_tiles, n_tiles, 0, error_flag, 0, whole_end, scale};
+        GemmTcArgs a{out, res, n_rows, m_out, k_in, ldo, out_dtype, m_tiles, n_tiles, 0, error_flag, 0, whole_end, scale, nullptr};
         dim3 grid((unsigned)(whole_end < sm_count() ? whole_end : sm_count()), 1, 1);
         if (mode == 0) rc = dispatch_tc<0>(block_n, mw, mx, a, grid, s);
         else if (mode == 1) rc = dispatch_tc<1>(block_n, mw, mx, a, grid, s);
@@ -585,7 +592,7 @@ extern "C" int braid_gemm_tc(const void* x, const void* w, void* out, const floa
     }
     if (!stream_k || p.tiles == 0) return BRAID_OK;
     GemmTcArgs a{workspace, nullptr, n_rows, w_rows, k_in, 0, BRAID_F32, p.m_tiles, p.n_tiles, p.max_segs, error_flag,
-                 p.tile_begin, p.tile_begin + p.tiles, RowScaleArgs{}};
+                 p.tile_begin, p.tile_begin + p.tiles, scale, scale.shares ? rs_rows : nullptr};
     rc = dispatch_tc<3>(block_n, mw, mx, a, dim3(p.grid, 1, 1), s);
     if (rc) return rc;
     if (plan_out) {
@@ -595,20 +602,16 @@ extern "C" int braid_gemm_tc(const void* x, const void* w, void* out, const floa
         return BRAID_OK;
     }
     StreamK k{(const float*)workspace, p.grid, p.max_segs, p.total_kb, p.n_tiles, n_rows, block_n, p.w, p.m_tiles, p.tile_begin};
-    return launch_streamk_reduce(k, out, res, m_out, ldo, out_dtype, mode, scale, s);
+    return launch_streamk_reduce(k, out, res, m_out, ldo, out_dtype, mode, scale.shares ? rs_rows : nullptr, s);
 }
 
 // Add up the partial products of an earlier stream-k call made with plan_out (the same
 // reduce the fused call runs): mode 0 store, 1 res + sum, 2 silu(gate) * up.
 extern "C" int braid_streamk_reduce(const float* partial, const int* plan, int n_rows, void* out, const float* res,
-                                    int m_out, long long ldo, int out_dtype, int mode, const float* scale_shares,
-                                    int scale_n_shares, long long scale_stride, float scale_width, float scale_eps,
-                                    void* stream) {
+                                    int m_out, long long ldo, int out_dtype, int mode, const float* rs_rows, void* stream) {
     if (n_rows <= 0 || m_out <= 0) return BRAID_OK;
     if (mode < 0 || mode > 2) BRAID_REFUSE("streamk_reduce: unknown epilogue %d", mode);
     if (mode == 1 && (!res || out_dtype != BRAID_F32)) BRAID_REFUSE("streamk_reduce: the residual epilogue writes float32 and needs res");
-    const RowScaleArgs scale{scale_shares, scale_n_shares, scale_stride, scale_width, scale_eps};
-    if (const char* why = row_scale_problem(scale, n_rows)) BRAID_REFUSE("streamk_reduce: row scale: %s", why);
-    if (scale.shares && mode == 1) BRAID_REFUSE("streamk_reduce: the residual epilogue takes no row scale");
-    return launch_streamk_reduce(streamk_from_plan(partial, plan, n_rows), out, res, m_out, ldo, out_dtype, mode, scale, (cudaStream_t)stream);
+    if (rs_rows && mode == 1) BRAID_REFUSE("streamk_reduce: the residual epilogue takes no row scale");
+    return launch_streamk_reduce(streamk_from_plan(partial, plan, n_rows), out, res, m_out, ldo, out_dtype, mode, rs_rows, (cudaStream_t)stream);
 }

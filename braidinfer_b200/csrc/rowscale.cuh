@@ -5,7 +5,9 @@
 // partial sums, see fused_reduce.cu) can therefore work on a few columns of many rows per CTA instead of
 // on whole rows: it writes h, bfloat16(h * g), and its columns' share of each row's sum of squares, and
 // whoever multiplies bfloat16(h * g) by a matrix multiplies its results by rs, which it gets from the
-// shares.  The sum of squares and rs are float32, the shares are added in ascending order.
+// shares: a product of whole tiles in its epilogue; a stream-k product has its first CTA turn the shares
+// into one float a row (rs_rows) for the kernel that adds its partial sums up.  The sum of squares and rs
+// are float32, the shares are added in ascending order.
 #pragma once
 #include "common.cuh"
 
@@ -21,33 +23,6 @@ struct RowScaleArgs {
 // The shares are read with ordinary loads, through L1: every thread of a kernel that applies a scale reads
 // the same few floats, and loads that go to L2 each time (ld.global.cg) queue up on those few lines
 // (measured: a step of 8 rows 1.7 % slower instead of 1.7 % faster).
-
-// In two steps, for a kernel that has other loads to ask for meanwhile: `row_scale_ask` asks for the first
-// ROWSCALE_BATCH shares and touches none of them, `row_scale_finish` adds them (and any further ones) up.
-// What is asked for between the two travels at the same time.
-struct RowScaleAsked { float p[ROWSCALE_BATCH]; };
-
-__device__ __forceinline__ void row_scale_ask(const RowScaleArgs& r, int row, RowScaleAsked& a) {
-#pragma unroll
-    for (int i = 0; i < ROWSCALE_BATCH; ++i)
-        a.p[i] = (r.shares && i < r.n_shares) ? r.shares[(size_t)i * r.stride + row] : 0.f;
-}
-
-__device__ __forceinline__ float row_scale_finish(const RowScaleArgs& r, int row, const RowScaleAsked& a) {
-    if (!r.shares) return 1.f;
-    float ss = 0.f;
-#pragma unroll
-    for (int i = 0; i < ROWSCALE_BATCH; ++i) ss += a.p[i];
-    for (int t0 = ROWSCALE_BATCH; t0 < r.n_shares; t0 += ROWSCALE_BATCH) {
-        float p[ROWSCALE_BATCH];
-#pragma unroll
-        for (int i = 0; i < ROWSCALE_BATCH; ++i)
-            p[i] = (t0 + i < r.n_shares) ? r.shares[(size_t)(t0 + i) * r.stride + row] : 0.f;
-#pragma unroll
-        for (int i = 0; i < ROWSCALE_BATCH; ++i) ss += p[i];
-    }
-    return rsqrtf(ss / r.width + r.eps);
-}
 
 __device__ __forceinline__ float row_scale_of(const RowScaleArgs& r, int row) {
     if (!r.shares) return 1.f;

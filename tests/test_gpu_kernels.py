@@ -489,7 +489,7 @@ def test_stream_k_refuses_a_workspace_that_is_too_small_and_takes_any_token_tile
     ws = torch.empty(need // 4, dtype=torch.float32, device=DEV)
     out = torch.empty(300, 512, device=DEV, dtype=torch.bfloat16)
     args = lambda nbytes, tile: (x.data_ptr(), w.data_ptr(), out.data_ptr(), None, ws.data_ptr(), nbytes, BF16, 0,
-                                 300, 512, 256, 256, 256, 512, tile, 1, None, None, 0, 0, 0.0, 0.0,
+                                 300, 512, 256, 256, 256, 512, tile, 1, None, None, 0, 0, 0.0, 0.0, None,
                                  K._error_flag.data_ptr() + 4, K._stream())
     assert K.lib.braid_gemm_tc(*args(need - 4, 128)) != 0            # refused on the host: nothing is launched
     assert b"bytes of workspace" in K.lib.braid_last_error()
