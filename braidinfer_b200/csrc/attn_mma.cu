@@ -138,13 +138,21 @@ attn_mma_kernel(AttnMmaArgs a) {
     };
     // the first tiles of the ring; those that hold only positions cached before this step
     // are asked for at once, the others after the wait
-    bool early[ST - 1];
+    bool early[ST];                                      // every stage of the ring is free at the start
 #pragma unroll
-    for (int s = 0; s < ST - 1; ++s) {
+    for (int s = 0; s < ST; ++s) {
         early[s] = s < n_tiles && (t_lo + s + 1) * BN <= kv_before;
         if (early[s]) load_tile(t_lo + s, s);
     }
     pdl_wait();
+
+    // the tiles of the ring that had to wait (they hold this step's own keys) are asked for first: the trip
+    // for the queries, next, then runs beside theirs
+#pragma unroll
+    for (int s = 0; s < ST; ++s) {
+        if (s < n_tiles && !early[s]) load_tile(t_lo + s, s);
+        cp_async_commit();                               // one group a stage, as the loop below counts them
+    }
 
     // ---- queries into shared memory (rows of absent tokens or heads are zero)
     for (int i = tid; i < C::BM * CH; i += NW * 32) {
@@ -156,11 +164,6 @@ attn_mma_kernel(AttnMmaArgs a) {
         *reinterpret_cast<uint4*>(sQ + r * C::ROW + c * 16) = v;
     }
 
-#pragma unroll
-    for (int s = 0; s < ST - 1; ++s) {
-        if (s < n_tiles && !early[s]) load_tile(t_lo + s, s);
-        cp_async_commit();                               // one group a stage, as the loop below counts them
-    }
 
     // per-thread rows: r0 = lane / 4 and r0 + 8 of this warp's 16
     const int row_a = warp * 16 + (lane >> 2), row_b = row_a + 8;
@@ -180,9 +183,11 @@ attn_mma_kernel(AttnMmaArgs a) {
     float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
 
     for (int it = 0; it < n_tiles; ++it) {
-        const int pre = it + ST - 1;
-        if (pre < n_tiles) load_tile(t_lo + pre, pre % ST);
-        cp_async_commit();
+        if (it > 0) {                                    // the stage that tile it - 1 has left takes tile it + ST - 1
+            const int pre = it + ST - 1;
+            if (pre < n_tiles) load_tile(t_lo + pre, pre % ST);
+            cp_async_commit();
+        }
         cp_async_wait<ST - 1>();
         __syncthreads();
         const uint8_t* sK = sKV + (it % ST) * 2 * C::TILE_BYTES;
