@@ -23,7 +23,7 @@ def stream_k_pays(rows: int, w_rows: int, k_in: int, sms: Optional[int] = None) 
     (rows x w_rows floats a CTA that shares a tile) are small beside the weights (w_rows x k_in).
     Measured on the 7B layer sizes at 1 to 2,048 tokens.  Up to 128 tokens whole tiles are [128 x token
     tile] on single SMs: stream-k when the last round of tiles would be less than 70 % full (80 % for up
-    to 32 tokens).  Beyond, whole tiles are [256 x 256] on pairs of SMs: stream-k when their last round
+    to 48 tokens: at 33 tokens gate+up is 2.6 % of a step faster so, at 64 it is a tie).  Beyond, whole tiles are [256 x 256] on pairs of SMs: stream-k when their last round
     would be less than 70 % full and rows <= min(k_in / 16, 512): at 256 tokens every product of width
     4096 but gate+up, at 512 only down (k_in = 14336), from 513 on none."""
     from ..csrc.api import PAIR_TOKEN_TILE, token_tile
@@ -40,7 +40,7 @@ def stream_k_pays(rows: int, w_rows: int, k_in: int, sms: Optional[int] = None) 
         return units / (-(-units // pairs) * pairs) < 0.7
     tiles = -(-w_rows // 128) * -(-rows // tile)
     fill = tiles / (-(-tiles // sms) * sms)
-    return fill < (0.8 if rows <= 32 else 0.7)
+    return fill < (0.8 if rows <= 48 else 0.7)
 
 
 # Rows up to which a norm may leave its scale to the next product: beyond the token tiles of the

@@ -168,7 +168,7 @@ def test_where_a_product_is_spread_along_k():
     qkv, o, gate_up, down, head = (6144, 4096), (4096, 4096), (2 * 14336, 4096), (4096, 14336), (32768, 4096)
     for rows in (1, 8, 32, 64, 128, 160, 256):
         assert pays(rows, qkv) and pays(rows, o) and pays(rows, down)
-    assert pays(8, gate_up) and pays(32, gate_up)                                    # 224 tiles: 76 % full
+    assert pays(8, gate_up) and pays(32, gate_up) and pays(48, gate_up)              # 224 tiles: 76 % full
     assert not any(pays(r, gate_up) for r in (64, 128, 160, 256, 512))
     assert not any(pays(r, head) for r in (1, 8, 64, 512))                           # 256 tiles: 86 % full
     assert not pays(384, qkv) and not pays(384, o) and pays(384, down)               # the sums outweigh k = 4096
