@@ -91,7 +91,6 @@ __device__ __forceinline__ int block_exclusive_iscan(int v, int* sh /* [32] */) 
     return base + inc - v;
 }
 
-// Lowest index of the largest value of x[0..n); a NaN anywhere raises *nan_flag.
 // A row of logits.  In shared memory it is laid out with one float of padding after every 32: the chain
 // reads it both with consecutive threads on consecutive elements and with every thread on a run of
 // elements of its own (the sums along the index), and without the padding the runs of a warp's threads
@@ -102,15 +101,14 @@ struct Row {
     __device__ __forceinline__ float& operator[](int i) const { return p[padded ? i + (i >> 5) : i]; }
 };
 
-__device__ int block_argmax(Row x, int n, float* shf, int* shi, int* nan_flag) {
-    float best = -INFINITY;
-    int best_i = 0x7fffffff;
-    bool saw_nan = false;
-    for (int i = threadIdx.x; i < n; i += blockDim.x) {
-        const float v = x[i];
-        if (v != v) saw_nan = true;
-        if (v > best || (v == best && i < best_i)) { best = v; best_i = i; }
-    }
+// One thread's candidate after looking at (v, i): the largest value, the lowest index among equals.
+__device__ __forceinline__ void argmax_take(float v, int i, float& best, int& best_i, bool& saw_nan) {
+    if (v != v) saw_nan = true;
+    if (v > best || (v == best && i < best_i)) { best = v; best_i = i; }
+}
+
+// The block's winner from every thread's candidate.
+__device__ __forceinline__ int argmax_finish(float best, int best_i, bool saw_nan, float* shf, int* shi, int* nan_flag) {
     if (saw_nan && nan_flag) atomicExch(nan_flag, 1);
     const float m = block_reduce_max(best, shf);
     const int cand = (best == m) ? best_i : 0x7fffffff;
@@ -119,13 +117,54 @@ __device__ int block_argmax(Row x, int n, float* shf, int* shi, int* nan_flag) {
     return r;
 }
 
+// Lowest index of the largest value of x[0..n); a NaN anywhere raises *nan_flag.
+__device__ int block_argmax(Row x, int n, float* shf, int* shi, int* nan_flag) {
+    float best = -INFINITY;
+    int best_i = 0x7fffffff;
+    bool saw_nan = false;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) argmax_take(x[i], i, best, best_i, saw_nan);
+    return argmax_finish(best, best_i, saw_nan, shf, shi, nan_flag);
+}
+
+// The same over a row in global memory that starts on 16 bytes: 16-byte loads, four of them in flight a thread.
+__device__ int block_argmax_vec(const float* __restrict__ x, int n, float* shf, int* shi, int* nan_flag) {
+    float best = -INFINITY;
+    int best_i = 0x7fffffff;
+    bool saw_nan = false;
+    const int n4 = n >> 2;
+    const float4* x4 = reinterpret_cast<const float4*>(x);
+    constexpr int U = 4;
+    for (int base = threadIdx.x; base < n4; base += blockDim.x * U) {
+        float4 v[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int g = base + u * (int)blockDim.x;
+            v[u] = g < n4 ? x4[g] : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int i = (base + u * (int)blockDim.x) * 4;
+            if (i < n4 * 4) {
+                argmax_take(v[u].x, i, best, best_i, saw_nan);
+                argmax_take(v[u].y, i + 1, best, best_i, saw_nan);
+                argmax_take(v[u].z, i + 2, best, best_i, saw_nan);
+                argmax_take(v[u].w, i + 3, best, best_i, saw_nan);
+            }
+        }
+    }
+    for (int i = n4 * 4 + threadIdx.x; i < n; i += blockDim.x) argmax_take(x[i], i, best, best_i, saw_nan);
+    return argmax_finish(best, best_i, saw_nan, shf, shi, nan_flag);
+}
+
 __global__ void __launch_bounds__(SAMP_THREADS)
 argmax_kernel(const float* __restrict__ logits, long long ld, int* __restrict__ out, int vocab, int* nan_flag) {
     pdl_trigger();
     pdl_wait();
     __shared__ float shf[32];
     __shared__ int shi[32];
-    const int r = block_argmax(Row{const_cast<float*>(logits) + (size_t)blockIdx.x * ld, 0}, vocab, shf, shi, nan_flag);
+    const float* row = logits + (size_t)blockIdx.x * ld;
+    const int r = (((uintptr_t)row & 15) == 0) ? block_argmax_vec(row, vocab, shf, shi, nan_flag)
+                                                : block_argmax(Row{const_cast<float*>(row), 0}, vocab, shf, shi, nan_flag);
     if (threadIdx.x == 0) out[blockIdx.x] = r;
 }
 
