@@ -24,6 +24,18 @@ __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict_
     const bool valid = (id >= 0 && id < vocab);
     const T* row = table + (size_t)(valid ? id : 0) * hidden;
     float* o = out + (size_t)t * hidden;
+    // rows that start on 16 bytes and hold a whole number of 16-byte groups go group by group
+    constexpr int VEC = 16 / sizeof(T);
+    if (valid && hidden % VEC == 0 && (((uintptr_t)row | (uintptr_t)o) & 15) == 0) {
+        for (int g = threadIdx.x; g < hidden / VEC; g += blockDim.x) {
+            T v[VEC];
+            *reinterpret_cast<uint4*>(v) = *reinterpret_cast<const uint4*>(row + g * VEC);
+#pragma unroll
+            for (int e = 0; e < VEC; e += 4)
+                *reinterpret_cast<float4*>(o + g * VEC + e) = make_float4(to_f32(v[e]), to_f32(v[e + 1]), to_f32(v[e + 2]), to_f32(v[e + 3]));
+        }
+        return;
+    }
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = valid ? to_f32(row[i]) : 0.f;
 }
 
