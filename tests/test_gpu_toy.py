@@ -266,6 +266,80 @@ def test_toy_routed_feed_forward_and_toy_position_encoding():
 
 
 # ---------------------------------------------------------------------------------------------
+# A toy feed-forward that takes row scales: in steps of few tokens the library's norm hands it rows that
+# are multiplied by the norm's weights only, and the scale that is still owed (StepContext.row_scales).
+class ScaleAwarePerceptron(FeedForward):
+    graph_safe = False
+    scales_seen = 0
+
+    def __init__(self, params, prefix, runtime):
+        super().__init__(params, prefix, runtime)
+        self.width, self.inner, self.prefix = int(params["width"]), int(params["inner"]), prefix
+
+    def tensor_specs(self):
+        return {self.prefix + "toy.w1.weight": TensorSpec((self.inner, self.width)),
+                self.prefix + "toy.w2.weight": TensorSpec((self.width, self.inner))}
+
+    def load(self, tensors):
+        self.w1 = tensors[self.prefix + "toy.w1.weight"].float()
+        self.w2 = tensors[self.prefix + "toy.w2.weight"].float()
+
+    def takes_row_scale(self):
+        return True
+
+    def forward(self, x, residual, ctx):
+        xf = x.float()
+        scale = ctx.take_row_scale(x)
+        if scale is not None:
+            type(self).scales_seen += 1
+            xf = xf * scale.values()[:x.shape[0], None]
+        return residual + torch.tanh(xf @ self.w1.t()) @ self.w2.t()
+
+
+def test_toy_feed_forward_that_takes_row_scales(tmp_path):
+    from braidinfer_b200.engine import Engine
+    from braidinfer_b200.models import architecture_for
+    from tiny import TINY_A, random_prompts
+    import plain_mistral as P
+    FEED_FORWARDS.register("toy_scale_aware", ScaleAwarePerceptron)
+    try:
+        arch = architecture_for(TINY_A)
+        cfg = arch.config_from_dict(TINY_A)
+        base = arch.build_spec(cfg)
+        layers = tuple(dataclasses.replace(ls, feed_forward=PartSpec("toy_scale_aware", {"width": cfg.hidden_size, "inner": 48}))
+                       for ls in base.layers)
+        spec = dataclasses.replace(base, layers=layers)
+        eng = Engine.from_spec(spec, 4, dtype="bfloat16", max_tokens=512, max_slots=2, verbose=False)
+        w = {n_: t.double() for n_, t in eng.drawn.items()}
+
+        pcfg = P.PlainConfig(TINY_A)
+
+        def plain(tokens):
+            pos = torch.arange(len(tokens))
+            h = P.embedding(w["model.embed_tokens.weight"], tokens, torch.float64)
+            for layer in range(cfg.num_hidden_layers):
+                pre = f"model.layers.{layer}."
+                h = h + P.attention_block(h, w, pre, pcfg, layer, pos)
+                n = P.rmsnorm(h, w[pre + "post_attention_layernorm.weight"], cfg.rms_norm_eps)
+                h = h + torch.tanh(n @ w[pre + "toy.w1.weight"].t()) @ w[pre + "toy.w2.weight"].t()
+            return P.linear(P.rmsnorm(h, w["model.norm.weight"], cfg.rms_norm_eps), w["lm_head.weight"])
+
+        toks = random_prompts(cfg.vocab_size, [40], seed=5)[0]
+        want = plain(toks)
+        s = eng.open()
+        ScaleAwarePerceptron.scales_seen = 0
+        got = [eng.step([(s, toks[:30])], want="last")]
+        for t in toks[30:]:
+            got.append(eng.step([(s, [t])], want="last"))
+        got = torch.cat(got)
+        assert ScaleAwarePerceptron.scales_seen >= 2 * 11          # every feed-forward call of the steps of few tokens
+        assert (got.double().cpu() - want[29:]).abs().max() < 1.5e-2
+        eng.check()
+    finally:
+        FEED_FORWARDS.unregister("toy_scale_aware")
+
+
+# ---------------------------------------------------------------------------------------------
 # The parts nobody had swapped yet, each written to the interface that braidinfer_b200/parts/base.py
 # documents and registered from here: a norm with a mean and a bias (also as the model's final norm,
 # where it is handed the wanted rows only), a block that runs mixer and feed-forward side by side
