@@ -275,6 +275,20 @@ def run_ours(args):
         model.generate(prompts_for(B), warm, stop_tokens=(), max_new_tokens=min(steps, gen_len) + 1)
         st = model.last_stats
         points["decode_b8_temperature"] = st.decode_tokens / st.decode_seconds if st.decode_seconds > 0 else 0.0
+        # a short prompt by itself (time to its first logits): such steps go through CUDA graphs from the
+        # third step of a shape on
+        short = prompts_for(1, 64)[0]
+        ms = []
+        for i in range(6):
+            slot = engine.open()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            engine.step([(slot, short)], want="last")
+            e1.record()
+            torch.cuda.synchronize()
+            engine.close(slot)
+            ms.append(e0.elapsed_time(e1))
+        points["prompt_64_tokens_ms"] = statistics.median(ms[3:])
         after_prefill = steps_after_a_prefill(engine, prompts_for(B))
 
     line = {

@@ -19,6 +19,11 @@ from ..parts.runtime import Runtime
 from ..weights import draw_tensors, load_tensors, tensor_specs_of
 from .step import StepContext, StepPacker
 
+# Steps of up to this many tokens in all are given a shape that CUDA graphs can be keyed on (see Engine.step):
+# beyond, the device takes longer over a step than the host over its launches.
+GRAPH_PROMPT_ROWS = 256
+
+
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32,
            "f32": torch.float32}
 
@@ -189,18 +194,27 @@ class Engine:
         n_new = [len(t) for t in tokens]
         tables = self.cache.begin_step(slots, n_new)
         one_each = all(n == 1 for n in n_new)
-        graphable = self.use_graphs and one_each and tap is None
+        # Steps of few tokens are bound by the host when it launches them kernel by kernel (some 330
+        # launches take it 6 ms, the device 3): they go through CUDA graphs, which can depend on a
+        # step's shape only.  So such a step is given a shape that a few numbers name: its rows are
+        # padded to a token tile (short prompts; a one-token step has one row a sequence), its page
+        # tables widened, and its launches sized by the bounds that follow from these, not by the
+        # lengths themselves.  A step launched kernel by kernel takes the same shape, so that it
+        # gives the same bits.
+        from ..csrc.api import token_tile
+        short_prompt = not one_each and sum(n_new) <= GRAPH_PROMPT_ROWS
+        shaped = one_each or short_prompt
+        graphable = self.use_graphs and shaped and tap is None
         if device_tokens is not None and not one_each:
             raise ValueError("device_tokens needs a step of one token a sequence")
-        ctx = self.packer.pack(slots, tokens, before, want_l, tables, bucket_tables=one_each,
-                               token_source_rows=device_tokens[1] if device_tokens is not None else None)
+        ctx = self.packer.pack(slots, tokens, before, want_l, tables, bucket_tables=shaped,
+                               token_source_rows=device_tokens[1] if device_tokens is not None else None,
+                               pad_rows_to=token_tile(sum(n_new)) if short_prompt else 0)
         ctx.kernels = self.kernels
-        if one_each and ctx.page_tables:
-            # A one-token step shapes its launches (how the context is sliced) by the bound that
-            # the widened page tables give, not by the lengths themselves: a CUDA graph can
-            # depend on the step's shape only, and a step launched kernel by kernel takes the
-            # same shape so that it gives the same bits.
+        if shaped and ctx.page_tables:
             ctx.max_kv_len = max(t.shape[1] for t in ctx.page_tables) * PAGE_SIZE
+        if short_prompt:
+            ctx.max_q_len = ctx.rows              # no sequence brings more tokens than the step has rows
         if device_tokens is not None:
             self.kernels.gather_i32(device_tokens[0], self.packer.token_source_view, ctx.token_ids)
         try:
@@ -221,7 +235,7 @@ class Engine:
         return logits
 
     def _graph_step(self, ctx: StepContext) -> Optional[torch.Tensor]:
-        """Run a one-token-per-sequence step through a CUDA graph.  The graph holds kernel
+        """Run a step of few tokens (one a sequence, or short prompts) through a CUDA graph.  The graph holds kernel
         launches only; the step's tables were copied to fixed device addresses before it.
         Launch shapes depend on the step's shape alone (see `step`).  The graph writes its
         logits into its own memory; the caller gets a copy."""
@@ -230,7 +244,7 @@ class Engine:
             self._graphs.clear()
             self._graph_seen.clear()
             self._graph_generation = generation
-        key = (ctx.rows, ctx.n_seqs, ctx.n_want, tuple(tuple(t.shape) for t in ctx.page_tables))
+        key = (ctx.rows, ctx.n_seqs, ctx.n_want, ctx.max_q_len, tuple(tuple(t.shape) for t in ctx.page_tables))
         entry = self._graphs.get(key)
         if entry is None:
             seen = self._graph_seen.get(key, 0)

@@ -128,9 +128,10 @@ class StepPacker:
 
     def pack(self, slots: Sequence[int], tokens: Sequence[Sequence[int]], kv_before: Sequence[int],
              want: Sequence[Sequence[int]], tables: Sequence[np.ndarray], bucket_tables: bool = False,
-             token_source_rows: Optional[Sequence[int]] = None) -> StepContext:
+             token_source_rows: Optional[Sequence[int]] = None, pad_rows_to: int = 0) -> StepContext:
         """`bucket_tables` widens every page table to a power-of-two number of columns (at
-        least 8), so that steps of the same shape lay their tables out identically."""
+        least 8), so that steps of the same shape lay their tables out identically.
+        `pad_rows_to`: at least this many rows (the rows past the step's tokens are padding)."""
         n_seqs = len(slots)
         if bucket_tables and all(len(t) == 1 for t in tokens) and all(len(w) <= 1 for w in want):
             return self._pack_one_token_each(slots, tokens, kv_before, want, tables, token_source_rows)
@@ -146,7 +147,7 @@ class StepPacker:
             tables = wide
         q_len = [len(t) for t in tokens]
         n_tokens = sum(q_len)
-        rows = -(-n_tokens // self.row_multiple) * self.row_multiple
+        rows = -(-max(n_tokens, int(pad_rows_to)) // self.row_multiple) * self.row_multiple
         token_ids = np.zeros(rows, dtype=np.int32)
         positions = np.zeros(rows, dtype=np.int32)
         token_seq = np.full(rows, -1, dtype=np.int32)

@@ -49,6 +49,44 @@ def test_graph_steps_past_the_first_table_widths(name, dtype, tmp_path):
     assert torch.equal(with_graphs, without)
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_short_prompts_through_graphs(dtype, tmp_path):
+    """Steps of up to 256 tokens are given a shape (rows padded to a token tile, tables widened) and replayed
+    from CUDA graphs from the third step of a shape on.  Three rounds of the same shapes with other tokens:
+    two unequal prompts in one step, then a chunk that continues each, then single tokens; every logit
+    beside the plain implementation, and the same bits as the steps launched kernel by kernel."""
+    folder = sharpen(make_folder(tmp_path, "B"), 4.0)
+    orc = Oracle(folder)
+    results = {}
+    for use_graphs in (True, False):
+        eng = engine(folder, dtype, max_tokens=64 * 24, max_slots=4, use_graphs=use_graphs)
+        outs = []
+        for rnd in range(3):
+            seqs = random_prompts(orc.cfg.vocab_size, [33 + 9 + 2, 7 + 20 + 2], seed=40 + rnd)
+            cuts = [(33, 9), (7, 20)]
+            slots = [eng.open() for _ in seqs]
+            a = eng.step([(sl, s[:c[0]]) for sl, s, c in zip(slots, seqs, cuts)], want="all")
+            b = eng.step([(sl, s[c[0]:c[0] + c[1]]) for sl, s, c in zip(slots, seqs, cuts)], want="last")
+            c1 = eng.step([(sl, [s[c[0] + c[1]]]) for sl, s, c in zip(slots, seqs, cuts)], want="last")
+            c2 = eng.step([(sl, [s[c[0] + c[1] + 1]]) for sl, s, c in zip(slots, seqs, cuts)], want="last")
+            eng.check()
+            want = [orc.logits(s) for s in seqs]
+            assert max_err(a[:33], want[0][:33]) < TOL[dtype] and max_err(a[33:], want[1][:7]) < TOL[dtype]
+            for j, (s, c) in enumerate(zip(seqs, cuts)):
+                assert max_err(b[j], want[j][c[0] + c[1] - 1]) < TOL[dtype]
+                assert max_err(c1[j], want[j][c[0] + c[1]]) < TOL[dtype]
+                assert max_err(c2[j], want[j][c[0] + c[1] + 1]) < TOL[dtype]
+            outs.append(torch.cat([a, b, c1, c2]).clone())
+            for sl in slots:
+                eng.close(sl)
+        results[use_graphs] = torch.cat(outs)
+        if use_graphs:
+            assert eng.graph_replays >= 3          # the third round's prompt steps and single tokens at least
+        else:
+            assert eng.graph_replays == 0
+    assert torch.equal(results[True], results[False])
+
+
 WIDE = {
     # the measured model's layer: width 4096, 32 query and 8 kv heads of 128, feed-forward 14336
     "7b": dict(hidden_size=4096, num_attention_heads=32, num_key_value_heads=8, head_dim=128, intermediate_size=14336,
