@@ -77,6 +77,7 @@ class RowScale:
 
 
 _NO_SCALE = (None, 0, 0, 0.0, 0.0)
+_RAW_STREAM = getattr(torch._C, "_cuda_getCurrentRawStream", None)      # torch's own quick way to the stream handle
 
 
 def _scale_args(scale: Optional["RowScale"]):
@@ -109,6 +110,7 @@ class Kernels:
         self.path = str(path)
         self.launches = 0          # kernels launched through this object (for measurements)
         self._declare()
+        self._device_index = torch.cuda.current_device()
         self._error_flag = torch.zeros(8, dtype=torch.int32, device="cuda")
         self._tc_workspace: Optional[torch.Tensor] = None
         self._attn_libs = {}
@@ -166,8 +168,11 @@ class Kernels:
             msg = self.lib.braid_last_error().decode(errors="replace")
             raise KernelError(f"{what}: {msg} (code {rc})")
 
-    @staticmethod
-    def _stream():
+    def _stream(self):
+        """The current stream's handle (inside a graph capture: the capturing stream).  Asked for at every
+        launch, so through the quick route where this torch has it."""
+        if _RAW_STREAM is not None:
+            return _RAW_STREAM(self._device_index)
         return torch.cuda.current_stream().cuda_stream
 
     def check_device_errors(self) -> None:

@@ -10,6 +10,7 @@ library, an unchanged one is reused.
 from __future__ import annotations
 
 import hashlib
+import functools
 import os
 import shutil
 import subprocess
@@ -36,6 +37,7 @@ class BuildError(RuntimeError):
     pass
 
 
+@functools.lru_cache(maxsize=None)
 def page_size() -> int:
     """Positions per cache page: read from page.h, the one place the number is written."""
     import re
