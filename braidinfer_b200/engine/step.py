@@ -104,6 +104,11 @@ class _Shaped:
         self.shape = shape
 
 
+class _Sized:                              # what `StepPacker._context` needs of a table: its size
+    def __init__(self, size):
+        self.size = size
+
+
 class StepPacker:
     """Builds a step's integer tables on the host and moves them to the device in one copy."""
 
@@ -235,8 +240,6 @@ class StepPacker:
         self.h2d_bytes_last = total * 4
         self.token_source_view = dev[offs[src_k]:offs[src_k] + n]
 
-        class _Sized:                      # what `_context` needs of the parts: their sizes
-            def __init__(self, size): self.size = size
         parts = [_Sized(sz) for sz in sizes]
         return self._context(dev, parts, offs, [_Shaped(s) for s in shapes], rows, n, n, [1] * n, kv_before, slots,
                              want_rows)
