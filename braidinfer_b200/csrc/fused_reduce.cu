@@ -195,7 +195,12 @@ streamk_reduce_prep_kernel(StreamK k, float* __restrict__ h, const TW* __restric
     for (int d = 16; d > 0; d >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, d);
     if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
     __syncthreads();
-    if (threadIdx.x == 0) shares[(size_t)blockIdx.x * share_stride + row] = ((red[0] + red[1]) + red[2]) + red[3];
+    if (threadIdx.x == 0) {
+        float total = red[0];
+#pragma unroll
+        for (int i = 1; i < PREP_THREADS / 32; ++i) total += red[i];
+        shares[(size_t)blockIdx.x * share_stride + row] = total;
+    }
 }
 
 // `partial` and `plan` null: h is complete and only hb and the shares are made.  shares: [ceil(width / 512)][share_stride].
