@@ -22,6 +22,7 @@ from .step import StepContext, StepPacker
 # Steps of up to this many tokens in all are given a shape that CUDA graphs can be keyed on (see Engine.step):
 # beyond, the device takes longer over a step than the host over its launches.
 GRAPH_PROMPT_ROWS = 256
+FEW_TOKENS = 8            # up to so many tokens a sequence the attention part slices the context (parts/attention.py)
 
 
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32,
@@ -214,7 +215,9 @@ class Engine:
         if shaped and ctx.page_tables:
             ctx.max_kv_len = max(t.shape[1] for t in ctx.page_tables) * PAGE_SIZE
         if short_prompt:
-            ctx.max_q_len = ctx.rows              # no sequence brings more tokens than the step has rows
+            # no sequence brings more tokens than the step has rows; steps of a few tokens a sequence keep the
+            # attention kernel that slices the context (it is chosen by this bound)
+            ctx.max_q_len = FEW_TOKENS if max(n_new) <= FEW_TOKENS else ctx.rows
         if device_tokens is not None:
             self.kernels.gather_i32(device_tokens[0], self.packer.token_source_view, ctx.token_ids)
         try:

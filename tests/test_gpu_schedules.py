@@ -53,7 +53,7 @@ def test_graph_steps_past_the_first_table_widths(name, dtype, tmp_path):
 def test_short_prompts_through_graphs(dtype, tmp_path):
     """Steps of up to 256 tokens are given a shape (rows padded to a token tile, tables widened) and replayed
     from CUDA graphs from the third step of a shape on.  Three rounds of the same shapes with other tokens:
-    two unequal prompts in one step, then a chunk that continues each, then single tokens; every logit
+    two unequal prompts in one step, then a chunk that continues each, then single tokens, then three tokens each; every logit
     beside the plain implementation, and the same bits as the steps launched kernel by kernel."""
     folder = sharpen(make_folder(tmp_path, "B"), 4.0)
     orc = Oracle(folder)
@@ -62,21 +62,24 @@ def test_short_prompts_through_graphs(dtype, tmp_path):
         eng = engine(folder, dtype, max_tokens=64 * 24, max_slots=4, use_graphs=use_graphs)
         outs = []
         for rnd in range(3):
-            seqs = random_prompts(orc.cfg.vocab_size, [33 + 9 + 2, 7 + 20 + 2], seed=40 + rnd)
+            seqs = random_prompts(orc.cfg.vocab_size, [33 + 9 + 2 + 3, 7 + 20 + 2 + 3], seed=40 + rnd)
             cuts = [(33, 9), (7, 20)]
             slots = [eng.open() for _ in seqs]
             a = eng.step([(sl, s[:c[0]]) for sl, s, c in zip(slots, seqs, cuts)], want="all")
             b = eng.step([(sl, s[c[0]:c[0] + c[1]]) for sl, s, c in zip(slots, seqs, cuts)], want="last")
             c1 = eng.step([(sl, [s[c[0] + c[1]]]) for sl, s, c in zip(slots, seqs, cuts)], want="last")
             c2 = eng.step([(sl, [s[c[0] + c[1] + 1]]) for sl, s, c in zip(slots, seqs, cuts)], want="last")
+            # three tokens a sequence: few enough for the attention kernel that slices the context
+            f = eng.step([(sl, s[c[0] + c[1] + 2:]) for sl, s, c in zip(slots, seqs, cuts)], want="all")
             eng.check()
             want = [orc.logits(s) for s in seqs]
             assert max_err(a[:33], want[0][:33]) < TOL[dtype] and max_err(a[33:], want[1][:7]) < TOL[dtype]
+            assert max_err(f[:3], want[0][-3:]) < TOL[dtype] and max_err(f[3:], want[1][-3:]) < TOL[dtype]
             for j, (s, c) in enumerate(zip(seqs, cuts)):
                 assert max_err(b[j], want[j][c[0] + c[1] - 1]) < TOL[dtype]
                 assert max_err(c1[j], want[j][c[0] + c[1]]) < TOL[dtype]
                 assert max_err(c2[j], want[j][c[0] + c[1] + 1]) < TOL[dtype]
-            outs.append(torch.cat([a, b, c1, c2]).clone())
+            outs.append(torch.cat([a, b, c1, c2, f]).clone())
             for sl in slots:
                 eng.close(sl)
         results[use_graphs] = torch.cat(outs)
