@@ -500,3 +500,123 @@ def test_toy_norm_block_embedding_head_and_no_position_encoding(dtype):
         BLOCKS.unregister("toy_side_by_side")
         EMBEDDINGS.unregister("toy_scaled_embedding")
         HEADS.unregister("toy_capped_head")
+
+
+# ---------------------------------------------------------------------------------------------
+# A whole toy architecture, defined and registered here only: its own config.json keys, its own
+# typed configuration, its own recipe of parts (the running-mean mixer above in layer 0, attention
+# in layer 1).  The library's files stay as they are: the random-weights writer, the loader, the
+# cache, the step function, the generation loop and the trace replay all find it through the
+# registry, by the name in config.json.
+@dataclasses.dataclass(frozen=True)
+class ToyConfig:
+    width: int
+    heads: int
+    groups: int
+    head_size: int
+    inner: int
+    words: int
+    wavelength: float
+    eps: float
+    longest: int
+    end_word: int
+
+    @classmethod
+    def from_dict(cls, d):
+        return cls(int(d["width"]), int(d["heads"]), int(d["groups"]), int(d["head_size"]), int(d["inner"]),
+                   int(d["words"]), float(d["wavelength"]), float(d["eps"]), int(d["longest"]), int(d["end_word"]))
+
+
+def build_toy_spec(c: ToyConfig):
+    from braidinfer_b200.parts.spec import ModelSpec, ScheduleEntry
+
+    def norm(name):
+        return PartSpec("rmsnorm", {"width": c.width, "eps": c.eps, "name": name})
+
+    rope = PartSpec("rope", {"head_dim": c.head_size, "theta": c.wavelength, "rope_dim": c.head_size, "pairing": "half"})
+    mixers = [PartSpec("toy_running_mean", {"width": c.width}),
+              PartSpec("gqa_attention", {"hidden_size": c.width, "num_heads": c.heads, "num_kv_heads": c.groups,
+                                         "head_dim": c.head_size, "window": 0, "position_encoding": rope})]
+    layers = tuple(LayerSpec(block="prenorm_residual", prefix=f"model.layers.{i}.", mixer=m,
+                             mixer_norm=norm("input_layernorm.weight"),
+                             feed_forward=PartSpec("swiglu", {"hidden_size": c.width, "intermediate_size": c.inner}),
+                             feed_forward_norm=norm("post_attention_layernorm.weight"))
+                   for i, m in enumerate(mixers))
+    return ModelSpec(hidden_size=c.width, vocab_size=c.words,
+                     embedding=PartSpec("token_embedding", {"vocab_size": c.words, "hidden_size": c.width,
+                                                            "name": "model.embed_tokens.weight"}),
+                     layers=layers, schedule=(ScheduleEntry(0), ScheduleEntry(1)), final_norm=norm("model.norm.weight"),
+                     head=PartSpec("linear_head", {"vocab_size": c.words, "hidden_size": c.width,
+                                                   "name": "lm_head.weight", "tied": False}),
+                     max_position=c.longest, eos_token_ids=(c.end_word,), bos_token_id=None)
+
+
+TOY_CONFIG_JSON = {"architectures": ["ToyRunningMeanLM"], "width": 64, "heads": 4, "groups": 2, "head_size": 16,
+                   "inner": 176, "words": 256, "wavelength": 10000.0, "eps": 1e-5, "longest": 512, "end_word": 2}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_architecture_from_config_json_to_generation_and_replay(dtype, tmp_path):
+    import json
+    import numpy as np
+    import braidinfer_b200 as lib
+    from braidinfer_b200.config.errors import UnknownArchitectureError
+    from braidinfer_b200.models import architecture_for
+    from braidinfer_b200.models.registry import ARCHITECTURES, Architecture, register_architecture
+    from braidinfer_b200.weights import write_random_model
+    from tiny import TINY_A, random_prompts, read_weights
+    folder = str(tmp_path / "toy")
+    with pytest.raises(UnknownArchitectureError):
+        write_random_model(TOY_CONFIG_JSON, folder, 3)
+    MIXERS.register("toy_running_mean", RunningMeanMixer)
+    register_architecture(Architecture("ToyRunningMeanLM", ToyConfig.from_dict, build_toy_spec))
+    try:
+        write_random_model(TOY_CONFIG_JSON, folder, 3)
+        model = lib.load(folder, dtype=dtype, max_seq_len=128, max_batch=3, verbose=False)
+        assert isinstance(model.config, ToyConfig) and model.engine.use_graphs is False
+        # the oracle: the same arithmetic, whole sequences, float64; its layer 1 is the plain Mistral layer
+        # at the sizes the toy keys give
+        plain_cfg = architecture_for(TINY_A).config_from_dict(TINY_A)
+        assert (plain_cfg.hidden_size, plain_cfg.num_attention_heads, plain_cfg.num_key_value_heads, plain_cfg.head_dim,
+                plain_cfg.intermediate_size, plain_cfg.vocab_size) == (64, 4, 2, 16, 176, 256)
+        w64 = {n: t.double() for n, t in read_weights(folder).items()}
+        tol = 2e-5 if dtype == "float32" else 1.5e-2
+
+        def plain(tokens):
+            return plain_running_mean_model(w64, plain_cfg, list(tokens), TOY_CONFIG_JSON["eps"])
+
+        # trace replay: two requests of unequal length start together, go on token by token, the shorter ends first
+        prompts = random_prompts(256, [11, 5], seed=4)
+        lines = [{"step": 0, "entries": [{"id": "a", "tokens": prompts[0][:8], "want": [0, 7]},
+                                         {"id": "b", "tokens": prompts[1][:3], "want": [2]}], "end": []},
+                 {"step": 1, "entries": [{"id": "a", "tokens": [prompts[0][8]], "want": [0]},
+                                         {"id": "b", "tokens": [prompts[1][3]], "want": [0]}], "end": []},
+                 {"step": 2, "entries": [{"id": "a", "tokens": [prompts[0][9]], "want": [0]},
+                                         {"id": "b", "tokens": [prompts[1][4]], "want": [0]}], "end": ["b"]},
+                 {"step": 3, "entries": [{"id": "a", "tokens": [prompts[0][10]], "want": [0]}], "end": ["a"]}]
+        out = str(tmp_path / "out")
+        assert model.replay(lines, out) == len(lines)
+        wa, wb = plain(prompts[0]), plain(prompts[1])
+        want = {0: [wa[0], wa[7], wb[2]], 1: [wa[8], wb[3]], 2: [wa[9], wb[4]], 3: [wa[10]]}
+        for step, rows in want.items():
+            got = torch.from_numpy(np.fromfile(f"{out}/{step}.f32", dtype="<f4").reshape(len(rows), 256))
+            assert (got.double() - torch.stack(rows)).abs().max() < tol
+        assert model.engine.cache.pages_in_use() == [0]
+        # greedy generation through the entry point: token by token the plain model's argmax, and the toy's own
+        # end word stops a sequence
+        starts = random_prompts(256, [6, 3, 9], seed=5)
+        outs = model.generate(starts, lib.SamplingParams.greedy(), max_new_tokens=5)
+        for start, o in zip(starts, outs):
+            seq = list(start)
+            for tok in o.tokens:
+                lg = plain(seq)[-1]
+                top2 = torch.topk(lg, 2).values
+                if (top2[0] - top2[1]).item() > 4 * tol:          # a near tie may fall either way in bfloat16
+                    assert tok == int(lg.argmax())
+                seq.append(tok)
+            assert TOY_CONFIG_JSON["end_word"] not in o.tokens
+            assert o.finish_reason in ("stop", "length") and (o.finish_reason == "stop" or len(o.tokens) == 5)
+        model.engine.check()
+    finally:
+        ARCHITECTURES.pop("ToyRunningMeanLM", None)
+        MIXERS.unregister("toy_running_mean")
