@@ -9,7 +9,7 @@ from __future__ import annotations
 
 import ctypes
 from ctypes import c_int, c_longlong, c_float, c_void_p, c_char_p
-from typing import Optional
+from typing import List, Optional
 
 import torch
 
@@ -153,6 +153,8 @@ class Kernels:
         L.braid_streamk_reduce_rope_kv.argtypes = [c_void_p] * 8 + [c_int] * 9 + [c_void_p, c_void_p, c_void_p]
         L.braid_gemm_tc_workspace_bytes.argtypes = [c_int, c_int, c_int, c_int]
         L.braid_gemm_tc_workspace_bytes.restype = c_longlong
+        L.braid_logit_hash.argtypes = [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p]
+        L.braid_logit_hash.restype = c_int
         L.braid_argmax.argtypes = [c_void_p, c_longlong, c_void_p, c_int, c_int, c_void_p, c_void_p]
         L.braid_sample.argtypes = [c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_int] + [c_void_p] * 12 + \
                                   [c_void_p, c_void_p]
@@ -191,6 +193,19 @@ class Kernels:
             raise KernelError("device error: " + "; ".join(n for n, f in zip(names, flags) if f))
 
     # ------------------------------------------------------------------ row-wise kernels
+    def logit_hash(self, logits: torch.Tensor) -> List[int]:
+        """One 64-bit hash a row of float32 logits (FNV-1a over the elements' 32-bit patterns, the hash the
+        reference logs under BRAIDINFER_LOGIT_TRACE): equal logits, equal hash, so the first step at which
+        two runs part is found by comparing two short text files.  Synchronises."""
+        if logits.dtype != torch.float32 or logits.dim() != 2 or logits.stride(1) != 1:
+            raise KernelError("logit_hash wants float32 rows [n, vocab] with contiguous elements")
+        n, vocab = logits.shape
+        out = torch.empty(max(n, 1), dtype=torch.int64, device=logits.device)
+        self.launches += 1
+        self._check(self.lib.braid_logit_hash(logits.data_ptr(), logits.stride(0), n, vocab, out.data_ptr(),
+                                              self._stream()), "logit_hash")
+        return [v & 0xFFFFFFFFFFFFFFFF for v in out[:n].tolist()]
+
     def embed(self, table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> None:
         n, hidden = out.shape
         self.launches += 1

@@ -433,3 +433,36 @@ extern "C" int braid_gather_i32(const int* src, const int* index, int* dst, int 
     braid_launch(gather_i32_kernel, dim3((n + 127) / 128), dim3(128), 0, (cudaStream_t)stream, src, index, dst, n);
     BRAID_LAUNCH_CHECK();
 }
+
+// ------------------------------------------------------------------ logit hash
+// One 64-bit hash a row of float32 logits, for finding the first step at which two runs part: for every
+// element in order, h ^= its 32 bits; h *= 0x100000001b3, from h = 0xcbf29ce484222325 (the hash that the
+// reference writes under BRAIDINFER_LOGIT_TRACE, crates/braidinfer-runtime/src/generate.rs:383-396).
+// The chain is sequential, so one thread a row walks it; the block stages the row through shared memory.
+#define HASH_CHUNK 4096
+__global__ void logit_hash_kernel(const float* __restrict__ logits, long long ld, int vocab, unsigned long long* __restrict__ out) {
+    __shared__ float chunk[HASH_CHUNK];
+    pdl_trigger();
+    pdl_wait();
+    const float* row = logits + (size_t)blockIdx.x * ld;
+    unsigned long long h = 0xcbf29ce484222325ull;
+    for (int c0 = 0; c0 < vocab; c0 += HASH_CHUNK) {
+        const int n = min(HASH_CHUNK, vocab - c0);
+        for (int i = threadIdx.x; i < n; i += blockDim.x) chunk[i] = row[c0 + i];
+        __syncthreads();
+        if (threadIdx.x == 0)
+            for (int i = 0; i < n; ++i) {
+                h ^= (unsigned long long)__float_as_uint(chunk[i]);
+                h *= 0x100000001b3ull;
+            }
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) out[blockIdx.x] = h;
+}
+
+extern "C" int braid_logit_hash(const float* logits, long long ld, int rows, int vocab, unsigned long long* out, void* stream) {
+    if (rows <= 0) return BRAID_OK;
+    if (vocab <= 0 || ld < vocab) BRAID_REFUSE("logit_hash: vocab=%d, row stride=%lld", vocab, ld);
+    braid_launch(logit_hash_kernel, dim3(rows), dim3(256), 0, (cudaStream_t)stream, logits, ld, vocab, out);
+    BRAID_LAUNCH_CHECK();
+}

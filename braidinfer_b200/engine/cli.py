@@ -10,6 +10,8 @@ environment, the prompt from the arguments.
   MAX_SEQ_LEN=<n>                    cap on context; sizes the cache (generate.rs:56-58)
   prompt                             the remaining arguments joined by spaces, default
                                      "Hello, world!" (generate.rs:36-40)
+  BRAIDINFER_LOGIT_TRACE=<file>      append `step= tok= logit_hash=` a chosen token, to find the step where
+                                     two runs part (generate.rs:380-396; see engine/generate.py)
 This library's own: TEMPERATURE (default 0 = greedy, as the reference's binary is),
 TOP_K, TOP_P, MIN_P, REPETITION_PENALTY, SEED, DTYPE=bfloat16|float32, BATCH_FILE=<file
 with one prompt a line>.

@@ -296,6 +296,10 @@ class Engine:
         torch.cuda.current_stream().wait_stream(stream)
         return graph, static_logits
 
+    def logit_hash(self, logits: torch.Tensor) -> List[int]:
+        """One 64-bit hash a row of logits, for `BRAIDINFER_LOGIT_TRACE` (see engine/generate.py)."""
+        return self.kernels.logit_hash(logits.float().contiguous())
+
     def check(self) -> None:
         """Raise if a kernel flagged an error since the last check (synchronises)."""
         self.kernels.check_device_errors()

@@ -11,9 +11,16 @@ to the cache, and the next batch starts when the last sequence of this one has e
 
 The loop talks to an engine (`open`, `close`, `step`) and a sampler (`choose`) only
 through those calls, so its decisions are tested on the CPU with stand-ins.
+
+`BRAIDINFER_LOGIT_TRACE=<file>` (the reference's name and meaning, generate.rs:380-396) appends a line
+`step=<k> tok=<token> logit_hash=<16 hex digits> seq=<request>` for every token chosen: k counts the
+request's tokens from 0, the hash is over the float32 logits the token was chosen from
+(`Engine.logit_hash`).  Two runs that should agree are compared by these files, and the first line that
+differs names the step to look at.  Tracing runs the loop unpipelined.
 """
 from __future__ import annotations
 
+import os
 import time
 from dataclasses import dataclass, field
 from typing import Callable, List, Optional, Sequence, Union
@@ -76,7 +83,10 @@ def plan_batches(prompt_lens: Sequence[int], max_new_tokens: Sequence[int], capa
 
 
 class GenerationLoop:
-    def __init__(self, engine, sampler, max_batch: int = 64, pipeline: bool = True) -> None:
+    def __init__(self, engine, sampler, max_batch: int = 64, pipeline: bool = True,
+                 logit_trace: Optional[str] = None) -> None:
+        self._logit_trace_arg = logit_trace       # None: ask the environment at every call of generate
+        self.logit_trace: Optional[str] = logit_trace
         self.engine = engine
         self.sampler = sampler
         self.max_batch = max_batch
@@ -88,6 +98,8 @@ class GenerationLoop:
                  max_new_tokens: Union[int, Sequence[int]] = 64,
                  stop_tokens: Sequence[int] = ()) -> List[Completion]:
         n = len(prompts)
+        self.logit_trace = (self._logit_trace_arg if self._logit_trace_arg is not None
+                            else (os.environ.get("BRAIDINFER_LOGIT_TRACE") or None))
         if params is None:
             params = SamplingParams.greedy()
         plist = [params] * n if isinstance(params, SamplingParams) else list(params)
@@ -109,7 +121,7 @@ class GenerationLoop:
         capacity = getattr(self.engine, "max_tokens")
         batches = plan_batches([len(prompts[i]) for i in todo], [mlist[i] for i in todo], capacity,
                                min(self.max_batch, getattr(self.engine, "max_slots", self.max_batch)))
-        pipelined = (self.pipeline and hasattr(self.sampler, "choose_async")
+        pipelined = (self.pipeline and not self.logit_trace and hasattr(self.sampler, "choose_async")
                      and all(p.repetition_penalty == 1.0 for p in plist))
         for b in batches:
             run = self._run_batch_pipelined if pipelined else self._run_batch
@@ -178,6 +190,12 @@ class GenerationLoop:
             for s in slots.values():
                 eng.close(s)
 
+    def _trace_logits(self, ids, steps, toks, logits) -> None:
+        hashes = self.engine.logit_hash(logits)
+        with open(self.logit_trace, "a") as f:
+            for i, k, tok, h in zip(ids, steps, toks, hashes):
+                f.write(f"step={k} tok={int(tok)} logit_hash={h:016x} seq={i}\n")
+
     def _run_batch(self, ids, prompts, plist, seeds, mlist, stop, results) -> None:
         eng = self.engine
         self.stats.batches += 1
@@ -193,6 +211,8 @@ class GenerationLoop:
                 toks = self.sampler.choose(logits, [plist[i] for i in live], [seeds[i] for i in live],
                                            live, [len(generated[i]) for i in live],
                                            lambda: [list(prompts[i]) + generated[i] for i in now_live])
+                if self.logit_trace:
+                    self._trace_logits(live, [len(generated[i]) for i in live], toks, logits)
                 now = time.perf_counter()
                 self.stats.steps += 1
                 if first:

@@ -175,3 +175,24 @@ def test_where_a_product_is_spread_along_k():
     assert not pays(512, o) and pays(512, down) and not pays(512, qkv)
     assert not any(pays(768, s) for s in (qkv, o, down))
     assert not pays(769, o) and not pays(2048, down)
+
+
+def test_logit_trace_lines(tmp_path, monkeypatch):
+    """BRAIDINFER_LOGIT_TRACE: a line per chosen token, counted per request from 0, with the hash the engine
+    gives for the logits the token was chosen from; the loop then runs unpipelined, with the same results."""
+    class HashingEngine(DeviceTokenEngine):
+        def logit_hash(self, logits):
+            return [int(row.argmax()) * 0x100000001 for row in logits]
+
+    path = tmp_path / "trace.txt"
+    monkeypatch.setenv("BRAIDINFER_LOGIT_TRACE", str(path))
+    eng = HashingEngine()
+    out = GenerationLoop(eng, AsyncArgmaxSampler()).generate([[3, 4], [20]], max_new_tokens=[3, 2], stop_tokens=[7])
+    assert [o.tokens for o in out] == [[5, 6], [21, 22]] and out[0].finish_reason == "stop"
+    lines = path.read_text().splitlines()
+    assert lines == [f"step=0 tok=5 logit_hash={5 * 0x100000001:016x} seq=0", f"step=0 tok=21 logit_hash={21 * 0x100000001:016x} seq=1",
+                     f"step=1 tok=6 logit_hash={6 * 0x100000001:016x} seq=0", f"step=1 tok=22 logit_hash={22 * 0x100000001:016x} seq=1",
+                     f"step=2 tok=7 logit_hash={7 * 0x100000001:016x} seq=0"]
+    monkeypatch.delenv("BRAIDINFER_LOGIT_TRACE")
+    GenerationLoop(HashingEngine(), AsyncArgmaxSampler()).generate([[3]], max_new_tokens=1)
+    assert len(path.read_text().splitlines()) == 5            # no variable, no lines

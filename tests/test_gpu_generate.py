@@ -208,3 +208,46 @@ def test_command_line_with_a_tokenizer_prepends_bos(tmp_path):
     q = run_cli(["w7 w200 w31"], MODEL=folder, MAX_TOKENS=4, DTYPE="float32")
     first = P.argmax_lowest(orc.logits([7, 200, 31])[-1])
     assert q.returncode == 0 and (q.stdout.split()[:1] == [f"w{first}"] or first == 2)
+
+
+def fnv_of_float32(row: torch.Tensor) -> int:
+    """The hash of crates/braidinfer-runtime/src/generate.rs:385-389, element by element."""
+    h = 0xcbf29ce484222325
+    for bits in row.contiguous().view(torch.int32).tolist():
+        h ^= bits & 0xFFFFFFFF
+        h = (h * 0x100000001b3) & 0xFFFFFFFFFFFFFFFF
+    return h
+
+
+def test_logit_trace_file_names_every_step(tmp_path, monkeypatch):
+    """BRAIDINFER_LOGIT_TRACE: the hashes are those of the logits a replay of the same tokens gives (so equal runs
+    write equal files), the kernel's hash is the reference's, and with the variable set the tokens stay the same."""
+    folder = make_folder(tmp_path, "A")
+    m = lib.load(folder, dtype="bfloat16", max_seq_len=128, max_batch=2, verbose=False)
+    prompts = random_prompts(m.config.vocab_size, [7, 3], seed=8)
+    plain = m.generate(prompts, SamplingParams.greedy(), stop_tokens=(), max_new_tokens=4)
+    path = tmp_path / "logits.txt"
+    monkeypatch.setenv("BRAIDINFER_LOGIT_TRACE", str(path))
+    traced = m.generate(prompts, SamplingParams.greedy(), stop_tokens=(), max_new_tokens=4)
+    first = path.read_text()
+    m.generate(prompts, SamplingParams.greedy(), stop_tokens=(), max_new_tokens=4)
+    monkeypatch.delenv("BRAIDINFER_LOGIT_TRACE")
+    assert [o.tokens for o in traced] == [o.tokens for o in plain]
+    assert path.read_text() == first + first                        # appended, and the same bits again
+    lines = first.splitlines()
+    assert len(lines) == 8
+    # the same tokens through the step function: prompt, then one token each
+    slots = [m.open(), m.open()]
+    logits = [m.step(list(zip(slots, prompts)), want="last")]
+    for t in range(3):
+        logits.append(m.step([(s, [o.tokens[t]]) for s, o in zip(slots, plain)], want="last"))
+    for s in slots:
+        m.close(s)
+    for k in range(4):
+        for i in range(2):
+            row = logits[k][i].float().cpu()
+            assert lines[2 * k + i] == f"step={k} tok={plain[i].tokens[k]} logit_hash={fnv_of_float32(row):016x} seq={i}"
+    # the kernel by itself, at a width that is no multiple of its chunk
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(3, 4096 + 37, generator=g).cuda()
+    assert m.engine.kernels.logit_hash(x) == [fnv_of_float32(r) for r in x.cpu()]
