@@ -5,8 +5,10 @@
 //
 // One block per row of logits; all arithmetic float32.  Where the reference sorts,
 // this finds the cut value on the bit pattern of the floats (top-k: the k-th largest key
-// digit by digit, eight bits a pass, from counts in shared memory; top-p: bisection on
-// the probability mass), and keeps the lowest indices of a tie at the cut (the
+// digit by digit, eight bits a pass, from counts in shared memory; top-p: the same walk
+// over a histogram of probability mass in fixed point, four passes over a whole row, or a
+// bisection bit by bit when top-k has left a block's worth of candidates), and keeps the
+// lowest indices of a tie at the cut (the
 // reference's unstable sort leaves that order open).  When top-k leaves at most a
 // block's worth of candidates, they are gathered into shared memory in index order and
 // the rest of the chain runs on them alone.  Argmax returns the lowest index of the maximum.
@@ -268,6 +270,88 @@ __device__ unsigned int kth_largest_key(Row x, int n, int k, int* hist /* [256] 
     return prefix;
 }
 
+// Probability mass in fixed point (48 fractional bits): sums of integers do not depend on the order in which the
+// threads add, so a histogram of mass may be built with atomics and still give the same cut every time.
+#define MASS_ONE 281474976710656.f            // 2^48
+__device__ __forceinline__ unsigned long long mass_of(float p) { return __float2ull_rd(p * MASS_ONE); }
+// A 64-bit sum kept as two 32-bit words, so that the adds are the shared-memory atomics the hardware has
+// (a 64-bit add would be a compare-and-swap loop, which queues when many threads meet on a few counters).
+__device__ __forceinline__ void mass_add(unsigned int* lo, unsigned int* hi, unsigned long long q) {
+    const unsigned int ql = (unsigned int)q, qh = (unsigned int)(q >> 32);
+    const unsigned int old = atomicAdd(lo, ql);
+    const unsigned int carry = (old + ql < old) ? 1u : 0u;
+    if (qh + carry) atomicAdd(hi, qh + carry);
+}
+
+// The cut of top-p: the largest key c such that the mass of the elements with key >= c reaches `target`
+// (0 if even the whole row does not).  `*above` receives the mass of the keys strictly greater than the cut.
+// Most significant digit first, eight bits a pass, as kth_largest_key, with mass in the place of counts:
+// four passes over the row instead of the thirty-two of a bisection bit by bit.
+// p(x) = expf(x - m) / total, as the rest of the chain computes it.
+__device__ unsigned int top_p_cut(Row x, int n, float m, float total, unsigned long long target,
+                                  unsigned int* mhist /* [512]: low words, then high words */,
+                                  unsigned long long* shl /* [1] */, int* shi, unsigned long long* above) {
+    unsigned int prefix = 0;
+    unsigned long long carried = 0;          // mass of the keys above every key that shares the prefix
+    bool any = true;
+    for (int shift = 24; shift >= 0 && any; shift -= 8) {
+        for (int i = threadIdx.x; i < 512; i += blockDim.x) mhist[i] = 0;
+        __syncthreads();
+        const unsigned int mask = (shift == 24) ? 0u : (0xffffffffu << (shift + 8));
+        // a thread adds up runs of equal digits by itself before it goes to the histogram: the top digits of a
+        // row are nearly all the same, and a thousand threads on one counter would queue
+        int run_digit = -1;
+        unsigned long long run = 0;
+        for (int i = threadIdx.x; i < n; i += blockDim.x) {
+            const float v = x[i];
+            const unsigned int key = float_key(v);
+            if ((key & mask) != prefix) continue;
+            const int d = (int)((key >> shift) & 255u);
+            const unsigned long long q = mass_of(expf(v - m) / total);
+            if (d == run_digit) { run += q; continue; }
+            if (run) mass_add(&mhist[run_digit], &mhist[256 + run_digit], run);
+            run_digit = d;
+            run = q;
+        }
+        if (run) mass_add(&mhist[run_digit], &mhist[256 + run_digit], run);
+        __syncthreads();
+        // the highest digit d with carried + mass(digits >= d) >= target: one warp walks the 256 sums from the top
+        if (threadIdx.x < 32) {
+            unsigned long long acc = carried, before = carried;
+            int digit = -1;
+            for (int base = 224; base >= 0 && digit < 0; base -= 32) {
+                const int d = base + 31 - (int)threadIdx.x;                           // lane 0 holds the highest digit of the group
+                const unsigned long long c = ((unsigned long long)mhist[256 + d] << 32) + mhist[d];
+                unsigned long long inc = c;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const unsigned long long t = __shfl_up_sync(0xffffffffu, inc, o);
+                    if ((int)threadIdx.x >= o) inc += t;
+                }
+                const unsigned int hit = __ballot_sync(0xffffffffu, acc + inc >= target);
+                if (hit) {
+                    const int lane = __ffs(hit) - 1;
+                    digit = base + 31 - lane;
+                    before = acc + __shfl_sync(0xffffffffu, inc, lane) - __shfl_sync(0xffffffffu, c, lane);
+                } else {
+                    acc += __shfl_sync(0xffffffffu, inc, 31);
+                }
+            }
+            if (threadIdx.x == 0) { shi[0] = digit; shl[0] = before; }
+        }
+        __syncthreads();
+        const int digit = shi[0];
+        if (digit < 0) any = false;           // the whole row does not reach the target: keep everything
+        else {
+            prefix |= ((unsigned int)digit) << shift;
+            carried = shl[0];
+        }
+        __syncthreads();
+    }
+    *above = carried;
+    return any ? prefix : 0u;
+}
+
 // The rest of the chain after top-k, on at most blockDim.x candidates held in shared memory in
 // index order (cv: values, ci: indices; thread t owns candidate t).  Same steps, same order of
 // sums along the index as the full-row form below.
@@ -334,7 +418,7 @@ sample_kernel(SampleArgs a) {
     __shared__ int shi[32];
     __shared__ int found;
     __shared__ int hist[256];
-    __shared__ float cand_v[SAMP_THREADS];
+    __shared__ __align__(8) float cand_v[SAMP_THREADS];
     __shared__ int cand_i[SAMP_THREADS];
     extern __shared__ float row_s[];                     // the row itself, when it fits (a.row_in_smem)
     const int row = blockIdx.x, n = a.vocab;
@@ -434,23 +518,20 @@ sample_kernel(SampleArgs a) {
         float s = 0.f;
         for (int i = threadIdx.x; i < n; i += blockDim.x) s += expf(x[i] - m);
         const float total = block_reduce_sum(s, shf);
-        unsigned int cut = 0;
-        for (int bit = 31; bit >= 0; --bit) {
-            const unsigned int cand = cut | (1u << bit);
-            float ms = 0.f;
-            for (int i = threadIdx.x; i < n; i += blockDim.x)
-                if (float_key(x[i]) >= cand) ms += expf(x[i] - m) / total;
-            if (block_reduce_sum(ms, shf) >= tp) cut = cand;
-        }
+        // the histogram of mass lives where the candidates of the few-candidates form would: that form has returned
+        unsigned int* mhist = reinterpret_cast<unsigned int*>(cand_v);
+        unsigned long long* shl = reinterpret_cast<unsigned long long*>(mhist + 512);
+        static_assert(sizeof(float) * SAMP_THREADS >= 4 * 512 + 8, "the mass histogram outgrows the candidates' array");
+        unsigned long long above_q = 0;
+        const unsigned int cut = top_p_cut(x, n, m, total, (unsigned long long)((double)tp * (double)MASS_ONE), mhist, shl,
+                                           shi, &above_q);
         // mass strictly above the cut, and the size of one member of the tie at the cut
-        float ms = 0.f, pv = 0.f;
-        for (int i = threadIdx.x; i < n; i += blockDim.x) {
-            const unsigned int key = float_key(x[i]);
-            if (key > cut) ms += expf(x[i] - m) / total;
-            else if (key == cut) pv = expf(x[i] - m) / total;
+        const float above = (float)((double)above_q / (double)MASS_ONE);
+        float pv = 0.f;
+        if (cut != 0) {
+            const unsigned int b = (cut & 0x80000000u) ? (cut & 0x7fffffffu) : ~cut;      // float_key backwards
+            pv = expf(__uint_as_float(b) - m) / total;
         }
-        const float above = block_reduce_sum(ms, shf);
-        pv = block_reduce_max(pv, shf);
         int keep = 1;
         if (pv > 0.f) {
             float c = above;

@@ -594,14 +594,18 @@ def test_argmax(K, vocab):
 
 @pytest.mark.parametrize("vocab", [331, 5000, 32768, 53600, 53700])      # rows of up to 53,6xx logits stay in shared memory
 def test_sampling_chain(K, vocab):
-    rows = 12
+    rows = 18
     lg = rnd(rows, vocab, scale=2.5, seed=4)
     g = torch.Generator().manual_seed(0)
     cases = []
+    # the last three patterns keep the whole row in play when top-p comes: no top-k, or one of more candidates than a
+    # block has threads (the cut of top-p is then found over the whole row, by passes over the probability mass)
     for i in range(rows):
-        cases.append(dict(temperature=[0.8, 1.0, 0.0, 1.5, 0.3, 2.0][i % 6], top_k=[0, 50, 0, 5, 1, 200][i % 6],
-                          top_p=[1.0, 0.9, 1.0, 0.5, 1.0, 0.95][i % 6], min_p=[0.0, 0.0, 0.0, 0.05, 0.0, 0.01][i % 6],
-                          repetition_penalty=[1.0, 1.3, 1.2, 1.0, 1.0, 1.1][i % 6],
+        cases.append(dict(temperature=[0.8, 1.0, 0.0, 1.5, 0.3, 2.0, 0.8, 1.2, 0.6][i % 9],
+                          top_k=[0, 50, 0, 5, 1, 200, 0, 2000, 0][i % 9],
+                          top_p=[1.0, 0.9, 1.0, 0.5, 1.0, 0.95, 0.9, 0.8, 0.3][i % 9],
+                          min_p=[0.0, 0.0, 0.0, 0.05, 0.0, 0.01, 0.0, 0.0, 0.001][i % 9],
+                          repetition_penalty=[1.0, 1.3, 1.2, 1.0, 1.0, 1.1, 1.0, 1.1, 1.0][i % 9],
                           u=float(torch.rand((), generator=g))))
     hist = [[int(t) for t in torch.randint(0, vocab, (20,), generator=g)] + [3, 3, 3] for _ in range(rows)]
     bias = [[(5, 2.5), (9, -1.0), (5, 0.5)] if i % 3 == 0 else [] for i in range(rows)]
