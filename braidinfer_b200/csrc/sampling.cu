@@ -103,6 +103,61 @@ struct Row {
     __device__ __forceinline__ float& operator[](int i) const { return p[padded ? i + (i >> 5) : i]; }
 };
 
+// Every element of the row once, the block's threads in stride: f(value, index).  A row in global memory (one
+// too long for shared memory) that starts on 16 bytes is read 16 bytes at a time, four loads in flight a thread:
+// with one 4-byte load at a time a thread, a row of 512 KB is 128 round trips to L2 a pass, and the chain
+// makes a dozen passes.  (A thread then meets its elements in another order than in the plain loop; rows in
+// shared memory keep the plain loop, and their sums the order they had.)
+template <typename F>
+__device__ __forceinline__ void row_each(const Row& x, int n, F f) {
+    if (!x.padded && (((uintptr_t)x.p & 15) == 0)) {
+        const int n4 = n >> 2;
+        const float4* x4 = reinterpret_cast<const float4*>(x.p);
+        constexpr int U = 4;
+        for (int base = threadIdx.x; base < n4; base += blockDim.x * U) {
+            float4 v[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int g = base + u * (int)blockDim.x;
+                v[u] = g < n4 ? x4[g] : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int g = base + u * (int)blockDim.x;
+                if (g < n4) { f(v[u].x, 4 * g); f(v[u].y, 4 * g + 1); f(v[u].z, 4 * g + 2); f(v[u].w, 4 * g + 3); }
+            }
+        }
+        for (int i = n4 * 4 + threadIdx.x; i < n; i += blockDim.x) f(x.p[i], i);
+        return;
+    }
+    for (int i = threadIdx.x; i < n; i += blockDim.x) f(x[i], i);
+}
+// The same with a new value for every element: x[i] = f(x[i], i).
+template <typename F>
+__device__ __forceinline__ void row_update(const Row& x, int n, F f) {
+    if (!x.padded && (((uintptr_t)x.p & 15) == 0)) {
+        const int n4 = n >> 2;
+        float4* x4 = reinterpret_cast<float4*>(x.p);
+        constexpr int U = 4;
+        for (int base = threadIdx.x; base < n4; base += blockDim.x * U) {
+            float4 v[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int g = base + u * (int)blockDim.x;
+                v[u] = g < n4 ? x4[g] : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int g = base + u * (int)blockDim.x;
+                if (g < n4) x4[g] = make_float4(f(v[u].x, 4 * g), f(v[u].y, 4 * g + 1), f(v[u].z, 4 * g + 2), f(v[u].w, 4 * g + 3));
+            }
+        }
+        for (int i = n4 * 4 + threadIdx.x; i < n; i += blockDim.x) x.p[i] = f(x.p[i], i);
+        return;
+    }
+    for (int i = threadIdx.x; i < n; i += blockDim.x) x[i] = f(x[i], i);
+}
+
 // One thread's candidate after looking at (v, i): the largest value, the lowest index among equals.
 __device__ __forceinline__ void argmax_take(float v, int i, float& best, int& best_i, bool& saw_nan) {
     if (v != v) saw_nan = true;
@@ -124,7 +179,7 @@ __device__ int block_argmax(Row x, int n, float* shf, int* shi, int* nan_flag) {
     float best = -INFINITY;
     int best_i = 0x7fffffff;
     bool saw_nan = false;
-    for (int i = threadIdx.x; i < n; i += blockDim.x) argmax_take(x[i], i, best, best_i, saw_nan);
+    row_each(x, n, [&](float v, int i) { argmax_take(v, i, best, best_i, saw_nan); });
     return argmax_finish(best, best_i, saw_nan, shf, shi, nan_flag);
 }
 
@@ -203,9 +258,59 @@ struct SampleArgs {
     int row_in_smem;         // the launch has vocab floats of dynamic shared memory for the row
 };
 
+// The passes that go along the index (ranks among equal keys, the gathering of candidates, the cumulative
+// sum) give every thread a run of elements of its own where the row lies in shared memory.  In global memory
+// such runs put the 32 loads of a warp on 32 lines, so there a warp owns a span of the row instead
+// ([warp * span, (warp + 1) * span), span a multiple of 32), reads it 32 consecutive elements at a time, and
+// ranks and running sums go across the lanes by ballot and shuffle.
+struct Span { int b, e, lane, warp; };
+__device__ __forceinline__ Span span_of(int n) {
+    const int nw = blockDim.x >> 5, warp = threadIdx.x >> 5;
+    const int len = ((n + nw - 1) / nw + 31) / 32 * 32;
+    Span s;
+    s.b = min(n, warp * len);
+    s.e = min(n, s.b + len);
+    s.lane = threadIdx.x & 31;
+    s.warp = warp;
+    return s;
+}
+__device__ __forceinline__ int warp_isum(int v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+// The sum of the warps' values before this warp's (sh: one int a warp).
+__device__ __forceinline__ int warps_before(int v, int* sh, const Span& sp) {
+    __syncthreads();
+    if (sp.lane == 0) sh[sp.warp] = v;
+    __syncthreads();
+    int before = 0;
+    for (int w = 0; w < sp.warp; ++w) before += sh[w];
+    return before;
+}
+
+__device__ void apply_cut_span(float* x, int n, unsigned int cut, int keep_equal, int* shi) {
+    const Span sp = span_of(n);
+    int eq = 0;
+    for (int i = sp.b + sp.lane; i < sp.e; i += 32) eq += (float_key(x[i]) == cut);
+    int before = warps_before(warp_isum(eq), shi, sp);
+    for (int i0 = sp.b; i0 < sp.e; i0 += 32) {
+        const int i = i0 + sp.lane;
+        const bool in = i < sp.e;
+        const unsigned int key = float_key(in ? x[i] : 0.f);
+        const bool is_eq = in && key == cut;
+        const unsigned int bal = __ballot_sync(0xffffffffu, is_eq);
+        const int rank = before + __popc(bal & ((1u << sp.lane) - 1u));
+        if (in && (key < cut || (is_eq && rank >= keep_equal))) x[i] = -INFINITY;
+        before += __popc(bal);
+    }
+    __syncthreads();
+}
+
 // Keep the `keep` lowest-index elements whose key equals `cut` and everything above
 // it; set the rest to -inf.
 __device__ void apply_cut(Row x, int n, unsigned int cut, int keep_equal, int* shi) {
+    if (!x.padded) { apply_cut_span(x.p, n, cut, keep_equal, shi); return; }
     const int chunk = (n + blockDim.x - 1) / blockDim.x;
     const int b = min(n, (int)threadIdx.x * chunk), e = min(n, b + chunk);
     int eq = 0;
@@ -232,10 +337,10 @@ __device__ unsigned int kth_largest_key(Row x, int n, int k, int* hist /* [256] 
         for (int i = threadIdx.x; i < 256; i += blockDim.x) hist[i] = 0;
         __syncthreads();
         const unsigned int mask = (shift == 24) ? 0u : (0xffffffffu << (shift + 8));
-        for (int i = threadIdx.x; i < n; i += blockDim.x) {
-            const unsigned int key = float_key(x[i]);
+        row_each(x, n, [&](float v, int) {
+            const unsigned int key = float_key(v);
             if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 255u], 1);
-        }
+        });
         __syncthreads();
         // the highest digit d with count(digits >= d) >= want: one warp walks the 256 counts from the top
         if (threadIdx.x < 32) {
@@ -302,17 +407,16 @@ __device__ unsigned int top_p_cut(Row x, int n, float m, float total, unsigned l
         // row are nearly all the same, and a thousand threads on one counter would queue
         int run_digit = -1;
         unsigned long long run = 0;
-        for (int i = threadIdx.x; i < n; i += blockDim.x) {
-            const float v = x[i];
+        row_each(x, n, [&](float v, int) {
             const unsigned int key = float_key(v);
-            if ((key & mask) != prefix) continue;
+            if ((key & mask) != prefix) return;
             const int d = (int)((key >> shift) & 255u);
             const unsigned long long q = mass_of(expf(v - m) / total);
-            if (d == run_digit) { run += q; continue; }
+            if (d == run_digit) { run += q; return; }
             if (run) mass_add(&mhist[run_digit], &mhist[256 + run_digit], run);
             run_digit = d;
             run = q;
-        }
+        });
         if (run) mass_add(&mhist[run_digit], &mhist[256 + run_digit], run);
         __syncthreads();
         // the highest digit d with carried + mass(digits >= d) >= target: one warp walks the 256 sums from the top
@@ -426,8 +530,22 @@ sample_kernel(SampleArgs a) {
     // The chain passes over the row a dozen times; a row that fits in shared memory is copied there
     // once and never touches global memory again.  Longer rows live in the caller's scratch.
     const Row x{a.row_in_smem ? row_s : a.work + (size_t)row * n, a.row_in_smem};
-    if (x.p != in)
-        for (int i = threadIdx.x; i < n; i += blockDim.x) x[i] = in[i];
+    const Row src{const_cast<float*>(in), 0};            // read 16 bytes at a time where it starts on 16 (row_each)
+    const float temp = a.temperature[row];
+    const float rp = a.rep_penalty ? a.rep_penalty[row] : 1.f;
+    const bool biased = a.bias_off && a.bias_off[row + 1] > a.bias_off[row];
+    const bool penalised = rp != 1.f && a.hist_off && a.hist_off[row + 1] > a.hist_off[row];
+    if (!biased && !penalised) {
+        // nothing touches single logits before the temperature: no copy of the row for an argmax, and the copy and
+        // the division in one pass otherwise
+        if (temp == 0.f) {                               // sampling.rs:82-84
+            const int r = block_argmax(src, n, shf, shi, a.nan_flag);
+            if (threadIdx.x == 0) a.out[row] = r;
+            return;
+        }
+        row_each(src, n, [&](float v, int i) { x[i] = v / temp; });
+    } else {
+    if (x.p != in) row_each(src, n, [&](float v, int i) { x[i] = v; });
     __syncthreads();
     // logit bias: additive, one entry after another (sampling.rs:57-65)
     if (a.bias_off && threadIdx.x == 0)
@@ -437,7 +555,6 @@ sample_kernel(SampleArgs a) {
         }
     __syncthreads();
     // repetition penalty, once per occurrence in the history (sampling.rs:68-79)
-    const float rp = a.rep_penalty ? a.rep_penalty[row] : 1.f;
     if (rp != 1.f && a.hist_off) {
         for (int i = a.hist_off[row] + threadIdx.x; i < a.hist_off[row + 1]; i += blockDim.x) {
             const int t = a.hist_tok[i];
@@ -448,13 +565,13 @@ sample_kernel(SampleArgs a) {
         }
     }
     __syncthreads();
-    const float temp = a.temperature[row];
     if (temp == 0.f) {                                   // sampling.rs:82-84
         const int r = block_argmax(x, n, shf, shi, a.nan_flag);
         if (threadIdx.x == 0) a.out[row] = r;
         return;
     }
-    for (int i = threadIdx.x; i < n; i += blockDim.x) x[i] = x[i] / temp;
+    row_update(x, n, [&](float v, int) { return v / temp; });
+    }
     __syncthreads();
 
     // top-k (sampling.rs:90-104): the k-th largest key by bisection
@@ -462,11 +579,44 @@ sample_kernel(SampleArgs a) {
     if (k > 0 && k < n) {
         const unsigned int cut = kth_largest_key(x, n, k, hist, shi);
         int c = 0;
-        for (int i = threadIdx.x; i < n; i += blockDim.x) c += (float_key(x[i]) > cut);
+        row_each(x, n, [&](float v, int) { c += (float_key(v) > cut); });
         const int above = block_reduce_isum(c, shi);
         if (k <= (int)blockDim.x) {
             // few candidates: gather them in index order (those above the cut, and the lowest
             // indices of the tie at it), and finish the chain on them alone
+            const int keep_equal = k - above;
+            if (!x.padded) {
+                const Span sp = span_of(n);
+                int eq = 0, gt = 0;
+                for (int i = sp.b + sp.lane; i < sp.e; i += 32) {
+                    const unsigned int key = float_key(x.p[i]);
+                    eq += (key == cut);
+                    gt += (key > cut);
+                }
+                eq = warp_isum(eq);
+                gt = warp_isum(gt);
+                int eq_before = warps_before(eq, shi, sp);
+                const int kept_eq = max(0, min(eq, keep_equal - eq_before));
+                int at = warps_before(gt + kept_eq, shi, sp);
+                for (int i0 = sp.b; i0 < sp.e; i0 += 32) {
+                    const int i = i0 + sp.lane;
+                    const bool in = i < sp.e;
+                    const float v = in ? x.p[i] : 0.f;
+                    const unsigned int key = float_key(v);
+                    const bool is_eq = in && key == cut;
+                    const unsigned int bal_eq = __ballot_sync(0xffffffffu, is_eq);
+                    const int rank = eq_before + __popc(bal_eq & ((1u << sp.lane) - 1u));
+                    const bool keep = in && (key > cut || (is_eq && rank < keep_equal));
+                    const unsigned int bal = __ballot_sync(0xffffffffu, keep);
+                    if (keep) {
+                        const int pos = at + __popc(bal & ((1u << sp.lane) - 1u));
+                        cand_v[pos] = v;
+                        cand_i[pos] = i;
+                    }
+                    eq_before += __popc(bal_eq);
+                    at += __popc(bal);
+                }
+            } else {
             const int chunk = (n + blockDim.x - 1) / blockDim.x;
             const int b = min(n, (int)threadIdx.x * chunk), e = min(n, b + chunk);
             int eq = 0, gt = 0;
@@ -477,7 +627,6 @@ sample_kernel(SampleArgs a) {
             }
             int eq_before = block_exclusive_iscan(eq, shi);
             __syncthreads();
-            const int keep_equal = k - above;
             const int kept_eq = max(0, min(eq, keep_equal - eq_before));
             int at = block_exclusive_iscan(gt + kept_eq, shi);
             for (int i = b; i < e; ++i) {
@@ -486,6 +635,7 @@ sample_kernel(SampleArgs a) {
                 bool keep = key > cut;
                 if (key == cut) { keep = eq_before < keep_equal; ++eq_before; }
                 if (keep) { cand_v[at] = v; cand_i[at] = i; ++at; }
+            }
             }
             __syncthreads();
             const int r = sample_few(cand_v, cand_i, k, a.min_p ? a.min_p[row] : 0.f, a.top_p ? a.top_p[row] : 1.f,
@@ -500,12 +650,9 @@ sample_kernel(SampleArgs a) {
     const float mp = a.min_p ? a.min_p[row] : 0.f;
     if (mp > 0.f) {
         float m = -INFINITY;
-        for (int i = threadIdx.x; i < n; i += blockDim.x) m = fmaxf(m, x[i]);
+        row_each(x, n, [&](float v, int) { m = fmaxf(m, v); });
         m = block_reduce_max(m, shf);
-        for (int i = threadIdx.x; i < n; i += blockDim.x) {
-            const float v = x[i];
-            if (v > -INFINITY && expf(v - m) < mp) x[i] = -INFINITY;
-        }
+        row_update(x, n, [&](float v, int) { return (v > -INFINITY && expf(v - m) < mp) ? -INFINITY : v; });
         __syncthreads();
     }
 
@@ -513,10 +660,10 @@ sample_kernel(SampleArgs a) {
     const float tp = a.top_p ? a.top_p[row] : 1.f;
     if (tp < 1.f) {
         float m = -INFINITY;
-        for (int i = threadIdx.x; i < n; i += blockDim.x) m = fmaxf(m, x[i]);
+        row_each(x, n, [&](float v, int) { m = fmaxf(m, v); });
         m = block_reduce_max(m, shf);
         float s = 0.f;
-        for (int i = threadIdx.x; i < n; i += blockDim.x) s += expf(x[i] - m);
+        row_each(x, n, [&](float v, int) { s += expf(v - m); });
         const float total = block_reduce_sum(s, shf);
         // the histogram of mass lives where the candidates of the few-candidates form would: that form has returned
         unsigned int* mhist = reinterpret_cast<unsigned int*>(cand_v);
@@ -543,15 +690,46 @@ sample_kernel(SampleArgs a) {
 
     // softmax and inverse CDF in index order (sampling.rs:154-170)
     float m = -INFINITY;
-    for (int i = threadIdx.x; i < n; i += blockDim.x) {
-        const float v = x[i];
+    row_each(x, n, [&](float v, int) {
         if (v != v && a.nan_flag) atomicExch(a.nan_flag, 1);
         m = fmaxf(m, v);
-    }
+    });
     m = block_reduce_max(m, shf);
     float s = 0.f;
-    for (int i = threadIdx.x; i < n; i += blockDim.x) s += expf(x[i] - m);
+    row_each(x, n, [&](float v, int) { s += expf(v - m); });
     const float total = block_reduce_sum(s, shf);
+    const float u = a.uniform[row];
+    if (!x.padded) {
+        // a warp's share of the sum, the shares before it, then along its span with a running sum across the lanes
+        const Span sp = span_of(n);
+        float mine = 0.f;
+        for (int i = sp.b + sp.lane; i < sp.e; i += 32) mine += expf(x.p[i] - m) / total;
+        mine = warp_sum(mine);
+        __syncthreads();
+        if (sp.lane == 0) shf[sp.warp] = mine;
+        if (threadIdx.x == 0) found = 0x7fffffff;
+        __syncthreads();
+        float c = 0.f;
+        for (int w = 0; w < sp.warp; ++w) c += shf[w];
+        if (u <= c + mine * 1.001f + 1e-6f) {              // the draw may fall in this span (the walk adds in another order)
+            for (int i0 = sp.b; i0 < sp.e; i0 += 32) {
+                const int i = i0 + sp.lane;
+                float inc = i < sp.e ? expf(x.p[i] - m) / total : 0.f;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const float t = __shfl_up_sync(0xffffffffu, inc, o);
+                    if (sp.lane >= o) inc += t;
+                }
+                const unsigned int hit = __ballot_sync(0xffffffffu, i < sp.e && u <= c + inc);
+                if (hit) {
+                    if (sp.lane == 0) atomicMin(&found, i0 + __ffs(hit) - 1);
+                    break;
+                }
+                c += __shfl_sync(0xffffffffu, inc, 31);
+            }
+        }
+        __syncthreads();
+    } else {
     const int chunk = (n + blockDim.x - 1) / blockDim.x;
     const int b = min(n, (int)threadIdx.x * chunk), e = min(n, b + chunk);
     float mine = 0.f;
@@ -559,12 +737,12 @@ sample_kernel(SampleArgs a) {
     float c = block_exclusive_scan(mine, shf);
     if (threadIdx.x == 0) found = 0x7fffffff;
     __syncthreads();
-    const float u = a.uniform[row];
     for (int i = b; i < e; ++i) {
         c += expf(x[i] - m) / total;
         if (u <= c) { atomicMin(&found, i); break; }
     }
     __syncthreads();
+    }
     int r = found;
     if (r == 0x7fffffff) {
         __syncthreads();

@@ -592,7 +592,7 @@ def test_argmax(K, vocab):
     assert out.tolist() == [P.argmax_lowest(lg[i].cpu()) for i in range(6)] and out[2] == 7
 
 
-@pytest.mark.parametrize("vocab", [331, 5000, 32768, 53600, 53700])      # rows of up to 53,6xx logits stay in shared memory
+@pytest.mark.parametrize("vocab", [331, 5000, 32768, 53600, 53700, 131072])      # rows of up to 53,6xx logits stay in shared memory
 def test_sampling_chain(K, vocab):
     rows = 18
     lg = rnd(rows, vocab, scale=2.5, seed=4)
