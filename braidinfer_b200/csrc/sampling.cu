@@ -574,7 +574,7 @@ sample_kernel(SampleArgs a) {
     }
     __syncthreads();
 
-    // top-k (sampling.rs:90-104): the k-th largest key by bisection
+    // top-k (sampling.rs:90-104): the k-th largest key, digit by digit
     const int k = a.top_k ? a.top_k[row] : 0;
     if (k > 0 && k < n) {
         const unsigned int cut = kth_largest_key(x, n, k, hist, shi);
