@@ -500,6 +500,61 @@ def run_timeline(args):
     return 0
 
 
+def run_prompt_timeline(args):
+    """Where a prompt's time goes, by prompt length: for each length given (--prompt-timeline 256,512,...), one prompt
+    step of the default layer sizes (8 layers unless --layers says otherwise) under the torch profiler, and for the
+    kernels of one layer in the middle the time from the end of the kernel before to the end of this one, as
+    run_timeline does for a decode step.  Lengths up to 256 go through a CUDA graph from the third step on, as they
+    do in generation.  One JSON line a length.  Not the contract's line."""
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+    from braidinfer_b200.config import preset
+    from braidinfer_b200.engine import Engine
+    cfg_dict = preset("mistral_7b_v03")
+    cfg_dict["num_hidden_layers"] = args.layers or 8
+    lengths = [int(t) for t in args.prompt_timeline.split(",")]
+    engine = Engine.from_random(cfg_dict, seed=0, dtype="bfloat16", on_device=True,
+                                max_tokens=2 * max(max(lengths), 4096), max_slots=2, verbose=True)
+    c = engine.config
+    per_token = 2 * (c.hidden_size * (c.num_attention_heads + 2 * c.num_key_value_heads) * c.head_dim
+                     + c.num_attention_heads * c.head_dim * c.hidden_size + 3 * c.hidden_size * c.intermediate_size)
+    pk = peaks()
+    g = torch.Generator().manual_seed(0)
+    for T in lengths:
+        prompt = torch.randint(0, c.vocab_size, (T,), generator=g).tolist()
+        for _ in range(3):
+            s = engine.open()
+            engine.step([(s, prompt)])
+            engine.close(s)
+        torch.cuda.synchronize()
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            s = engine.open()
+            engine.step([(s, prompt)])
+            engine.close(s)
+            torch.cuda.synchronize()
+        with tempfile.TemporaryDirectory() as d:
+            path = os.path.join(d, "trace.json")
+            prof.export_chrome_trace(path)
+            with open(path) as f:
+                ev = [e for e in json.load(f)["traceEvents"] if e.get("cat") == "kernel"]
+        ev.sort(key=lambda e: e["ts"])
+        att = [i for i, e in enumerate(ev) if "attn_" in e["name"] and "combine" not in e["name"]]
+        mid = len(att) // 2
+        start, per_layer = att[mid], att[mid + 1] - att[mid]
+        rows, prev_end = [], ev[start - 1]["ts"] + ev[start - 1]["dur"]
+        for e in ev[start:start + per_layer]:
+            end = e["ts"] + e["dur"]
+            rows.append({"kernel": e["name"].split("(")[0][:48], "until_its_end_us": round(end - prev_end, 2)})
+            prev_end = end
+        layer_us = sum(r["until_its_end_us"] for r in rows)
+        print(json.dumps({"metric": "one prompt step under the profiler, Mistral-7B-v0.3 layer sizes, bf16", "impl": "ours",
+                          "tokens": T, "layers": cfg_dict["num_hidden_layers"], "layer_us": round(layer_us, 1),
+                          "layer_flops_over_burst_peak_us": round(T * per_token / (pk["bf16_tflops"] * 1e12) * 1e6, 1),
+                          "frac_of_burst": round(T * per_token / (pk["bf16_tflops"] * 1e12) * 1e6 / layer_us, 3),
+                          "step_us": round(ev[-1]["ts"] + ev[-1]["dur"] - ev[0]["ts"], 1), "one_layer": rows}), flush=True)
+    return 0
+
+
 def run_chain(args):
     """What the chain of dependent kernels of a decode step costs, at the default sizes: products alone chained to
     themselves, and product + reducer pairs, each six times over distinct weights in one CUDA graph, timed with
@@ -630,6 +685,9 @@ def main() -> int:
     ap.add_argument("--chain", action="store_true",
                     help="what chains of decode-step kernels cost, with phase time stamps under BRAIDINFER_TRACE=1 "
                          "(see run_chain)")
+    ap.add_argument("--prompt-timeline", default="", metavar="T1,T2,...",
+                    help="a prompt step of each length under the torch profiler: a layer's kernels with their share "
+                         "(see run_prompt_timeline)")
     ap.add_argument("--timeline", action="store_true",
                     help="one decode step under the torch profiler: a layer's kernels with their share (see run_timeline)")
     args = ap.parse_args()
@@ -640,6 +698,8 @@ def main() -> int:
         return 2
     if args.sweep:
         return run_sweep(args)
+    if args.prompt_timeline:
+        return run_prompt_timeline(args)
     if args.timeline:
         return run_timeline(args)
     if args.chain:
